@@ -1,0 +1,1008 @@
+// The recurrent KDA step on B200 (sm_100a): decode, draft verification, commit replay.
+//
+// One persistent, warp-specialised block per SM walks a list of units, unit = (request, head) of one layer (or
+// (request, layer, head) for the commit replay).  Four roles, connected by mbarrier rings in shared memory:
+//
+//   mover (1 warp)      bulk-copies (cp.async.bulk) each unit's 128x128 state and each row's raw inputs from global
+//                       memory into shared-memory rings, several units ahead of the arithmetic;
+//   prologue (4 warps)  turns a row's raw inputs into q, k, v, the decay multipliers, beta and sigmoid(gate)
+//                       (short conv + SiLU, L2 norms, gates for the layer entry points; exp(g) for the core ones);
+//   recurrence (16 warps) keeps the unit's state in registers across its rows: warp w owns value rows 8w..8w+7,
+//                       lane l key columns 4l..4l+3; per row the delta rule and the read-out; afterwards each warp
+//                       bulk-stores its own 8 rows;
+//   epilogue (1 warp)   gated RMSNorm, bf16 outputs, replay saves.
+//
+// The state therefore crosses HBM once in each direction as 16-byte-aligned bulk transfers that are always
+// several units deep in flight, and no role ever waits on a global load.
+//
+// Arithmetic contract (what makes this a drop-in for the reference's kernels/kda.cu): every sum over the 128 key
+// channels is formed as the reference forms it -- a lane's four consecutive channels added in order from zero,
+// then the five-step xor butterfly over 32 lanes -- and nothing is contracted into an FMA (this file is compiled
+// with --fmad=false --ftz=false --prec-div=true --prec-sqrt=true, the reference's build.rs flags).  The butterfly
+// is evaluated as a reduce-scatter (kda.cu:30-33 applied to eight rows at once): the same additions in the same
+// pairing, so the same bits, with 9 shuffles for eight rows instead of 40.  decode, verify and replay share
+// `delta_rule`, so a replayed prefix of a window has the bits of serial single-row steps
+// (reference kernels/glm53f_kda.h:111-116, 166-168).
+//
+// Reference lines restated here: kernels/kda.cu:38-53 (update), 98-210 (chain_kernel), 214-253 (replay_kernel),
+// 290-460 (argument checks and entry points).
+
+#include "common.cuh"
+#include "glm53f_kda.h"
+#include "kda_internal.h"
+
+namespace kda {
+
+__device__ int g_status = 0;
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            n = v;
+        else {
+            cudaGetLastError();
+            return 1;
+        }
+    }
+    return n;
+}
+
+namespace {
+
+enum Mode : int { kLayer = 0, kCore = 1, kReplay = 2 };
+
+constexpr int kRecWarps = 16, kProWarps = 4;
+constexpr int kRecThreads = kRecWarps * 32, kProThreads = kProWarps * 32;
+constexpr int kThreads = kRecThreads + kProThreads + 64;  // + epilogue warp + mover warp
+constexpr int kRowsPerLane = DV / kRecWarps;              // 8
+constexpr unsigned FULL = 0xffffffffu;
+
+struct Params {
+    int H, layers;
+    long long units;
+    const int32_t* cu_rows;
+    const int32_t* keep;
+    int rows1;
+    // layer entry points
+    const uint16_t* P;
+    long long p_stride, b_off;
+    const uint16_t* A;
+    long long a_stride;
+    const uint16_t* G;  // output-gate rows (layer: stride g_stride; core: dense, may be null)
+    long long g_stride;
+    const uint16_t* conv;
+    const long long* conv_off;
+    const uint16_t* cw;
+    const float* a_log;
+    const float* dt_bias;
+    const uint16_t* norm_w;
+    float eps, lower;
+    // core entry points
+    const uint16_t *q, *k, *v;
+    const float* glog;
+    const float* beta;
+    int flags;
+    // states
+    const void* state_in;
+    void* state_out;
+    long long state_stride;
+    const long long* state_off;
+    // outputs (for the replay the saves are inputs)
+    uint16_t* out;
+    long long out_stride;
+    float* k_save;
+    uint16_t* v_save;
+    float* g_save;
+    float* b_save;
+    long long kv_stride, b_stride;
+};
+
+// Raw-row slot layouts, byte offsets.
+struct RawLayer {
+    static constexpr int X = 0;                 // bf16 [4 taps][3 parts][128]
+    static constexpr int W = X + 4 * 3 * 256;   // bf16 [3 parts][128][4]
+    static constexpr int A = W + 3 * 1024;      // bf16 [128]
+    static constexpr int GATE = A + 256;        // bf16 [128]
+    static constexpr int DTB = GATE + 256;      // f32 [128]
+    static constexpr int B = DTB + 512;         // the 16 aligned bytes that hold the beta logit
+    static constexpr int BYTES = B + 16;
+};
+struct RawCore {
+    static constexpr int Q = 0, K = 256, V = 512;  // bf16 [128] each
+    static constexpr int GLOG = 768;               // f32 [128]
+    static constexpr int GATE = GLOG + 512;        // bf16 [128]
+    static constexpr int B = GATE + 256;           // the 16 aligned bytes that hold beta (f32)
+    static constexpr int BYTES = B + 16;
+};
+struct RawReplay {
+    static constexpr int K = 0, G = 512;  // f32 [128] each
+    static constexpr int V = 1024;        // bf16 [128]
+    static constexpr int B = V + 256;     // the 16 aligned bytes that hold beta (f32)
+    static constexpr int BYTES = B + 16;
+};
+template <int MODE>
+struct RawOf;
+template <>
+struct RawOf<kLayer> { using T = RawLayer; };
+template <>
+struct RawOf<kCore> { using T = RawCore; };
+template <>
+struct RawOf<kReplay> { using T = RawReplay; };
+
+constexpr int align_up(int x, int a) { return (x + a - 1) / a * a; }
+
+// A cooked row: what the recurrence and the epilogue read.
+struct Cooked {
+    float q[DK], k[DK], v[DV], g[DK], sg[DV], ys[DV];
+    float beta;
+    int pad[3];
+};
+
+template <typename S, int MODE>
+struct Smem {
+    static constexpr int kStateBytes = DV * DK * (int)sizeof(S);
+    static constexpr int kStateSlots = sizeof(S) == 4 ? 3 : 5;
+    static constexpr int kRawSlots = sizeof(S) == 4 ? 3 : 4;  // raw-row ring depth
+    static constexpr int kRowSlots = sizeof(S) == 4 ? 3 : 4;  // cooked-row ring depth
+    static constexpr int kRawBytes = align_up(RawOf<MODE>::T::BYTES, 128);
+    static constexpr int oState = 0;
+    static constexpr int oRaw = oState + kStateSlots * kStateBytes;
+    static constexpr int oCooked = oRaw + kRawSlots * kRawBytes;
+    static constexpr int oScratch = oCooked + kRowSlots * (int)sizeof(Cooked);  // prologue scratch: q, k before norm
+    static constexpr int oBars = oScratch + 2 * DK * 4;
+    // barriers: st_full[S], st_empty[S], raw_full[R], raw_empty[R], row_full[C], y_full[C], row_empty[C]
+    static constexpr int kBars = 2 * kStateSlots + 2 * kRawSlots + 3 * kRowSlots;
+    static constexpr int oCtl = oBars + kBars * 8;  // progress, abort
+    static constexpr int kBytes = oCtl + 16;
+};
+
+struct Unit {
+    int b, h, layer, rows;
+    long long row0;
+    long long s_elem;  // element offset of this head's state inside state_in / state_out
+};
+
+template <int MODE>
+__device__ __forceinline__ Unit unit_of(const Params& p, long long u) {
+    Unit x;
+    if (MODE == kReplay) {
+        const long long per = (long long)p.layers * p.H;
+        x.b = (int)(u / per);
+        const int rem = (int)(u % per);
+        x.layer = rem / p.H;
+        x.h = rem % p.H;
+        x.row0 = p.cu_rows ? p.cu_rows[x.b] : 0;
+        x.rows = p.keep ? p.keep[x.b] : p.rows1;
+    } else {
+        x.b = (int)(u / p.H);
+        x.h = (int)(u % p.H);
+        x.layer = 0;
+        if (p.cu_rows) {
+            const int r0 = p.cu_rows[x.b];
+            x.row0 = r0;
+            x.rows = p.cu_rows[x.b + 1] - r0;
+        } else {
+            x.row0 = 0;
+            x.rows = p.rows1;
+        }
+    }
+    if (x.rows < 0) x.rows = 0;
+    x.s_elem = (long long)x.layer * p.state_stride + (p.state_off ? p.state_off[x.b] : 0) + (long long)x.h * DV * DK;
+    return x;
+}
+
+// Whether a unit without rows still has to move its state (out of place copy).
+__device__ __forceinline__ bool copies_state(const Params& p) { return p.state_out != nullptr && p.state_out != p.state_in; }
+
+struct Ring {
+    int idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void next(int n) {
+        if (++idx == n) {
+            idx = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+// ---- state registers <-> shared memory -----------------------------------------------------------------------
+template <typename S>
+__device__ __forceinline__ void load_rows(const unsigned char* slot, int warp, int lane, float (&s)[kRowsPerLane][4]) {
+#pragma unroll
+    for (int j = 0; j < kRowsPerLane; ++j) {
+        const int row = warp * kRowsPerLane + j;
+        if constexpr (sizeof(S) == 4) {
+            const float4 x = *reinterpret_cast<const float4*>(slot + ((size_t)row * DK + lane * 4) * 4);
+            s[j][0] = x.x; s[j][1] = x.y; s[j][2] = x.z; s[j][3] = x.w;
+        } else {
+            const uint2 x = *reinterpret_cast<const uint2*>(slot + ((size_t)row * DK + lane * 4) * 2);
+            s[j][0] = __uint_as_float(x.x << 16);
+            s[j][1] = __uint_as_float(x.x & 0xffff0000u);
+            s[j][2] = __uint_as_float(x.y << 16);
+            s[j][3] = __uint_as_float(x.y & 0xffff0000u);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+template <typename S>
+__device__ __forceinline__ void store_rows(unsigned char* slot, int warp, int lane, const float (&s)[kRowsPerLane][4]) {
+#pragma unroll
+    for (int j = 0; j < kRowsPerLane; ++j) {
+        const int row = warp * kRowsPerLane + j;
+        if constexpr (sizeof(S) == 4) {
+            *reinterpret_cast<float4*>(slot + ((size_t)row * DK + lane * 4) * 4) = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
+        } else {
+            *reinterpret_cast<uint2*>(slot + ((size_t)row * DK + lane * 4) * 2) =
+                make_uint2(pack_bf16x2(s[j][0], s[j][1]), pack_bf16x2(s[j][2], s[j][3]));
+        }
+    }
+}
+
+// The 32-lane xor butterfly (offsets 16, 8, 4, 2, 1) of eight independent values per lane, evaluated as a
+// reduce-scatter.  Lane l returns the butterfly's result for value (l >> 2); the additions and their pairing are
+// those of `x += shfl_xor(x, o)` applied to each value, so the bits are the same.
+__device__ __forceinline__ float butterfly8(const float (&p)[kRowsPerLane], int lane) {
+    float r[4], t[2];
+    {
+        const bool up = (lane & 16) != 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float mine = up ? p[4 + j] : p[j];
+            const float give = up ? p[j] : p[4 + j];
+            r[j] = mine + __shfl_xor_sync(FULL, give, 16);
+        }
+    }
+    {
+        const bool up = (lane & 8) != 0;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float mine = up ? r[2 + j] : r[j];
+            const float give = up ? r[j] : r[2 + j];
+            t[j] = mine + __shfl_xor_sync(FULL, give, 8);
+        }
+    }
+    const bool up = (lane & 4) != 0;
+    float x = (up ? t[1] : t[0]) + __shfl_xor_sync(FULL, up ? t[0] : t[1], 4);
+    x = x + __shfl_xor_sync(FULL, x, 2);
+    x = x + __shfl_xor_sync(FULL, x, 1);
+    return x;
+}
+
+// The plain butterfly for one value per lane (norms).
+__device__ __forceinline__ float butterfly1(float x) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) x = x + __shfl_xor_sync(FULL, x, o);
+    return x;
+}
+
+// One delta-rule step on a lane's 8 x 4 tile (reference kda.cu:38-53): decay, read with k, correct toward v.
+__device__ __forceinline__ void delta_rule(float (&s)[kRowsPerLane][4], const float (&kk)[4], const float (&gg)[4],
+                                           const float* vrow, int warp, int lane, float beta) {
+    float part[kRowsPerLane];
+#pragma unroll
+    for (int j = 0; j < kRowsPerLane; ++j) {
+        float kv = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s[j][i] = s[j][i] * gg[i];
+            kv = kv + s[j][i] * kk[i];
+        }
+        part[j] = kv;
+    }
+    const float kv = butterfly8(part, lane);
+    const float mine = (vrow[warp * kRowsPerLane + (lane >> 2)] - kv) * beta;
+#pragma unroll
+    for (int j = 0; j < kRowsPerLane; ++j) {
+        const float delta = __shfl_sync(FULL, mine, 4 * j);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[j][i] = s[j][i] + kk[i] * delta;
+    }
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ---- the mover -----------------------------------------------------------------------------------------------
+// Calls f(dst_offset, src, bytes, is_scalar_chunk) for every piece of a row's raw inputs.  Pieces are 16-byte
+// multiples except the "scalar chunk" (beta or its logit): for that one `src` is the element's own address and the
+// mover copies the aligned 16 bytes around it, so the element lands at dst_offset + (address & 15).
+template <int MODE, typename F>
+__device__ __forceinline__ void for_each_piece(const Params& p, const Unit& u, int r, F&& f) {
+    const long long gr = u.row0 + r;
+    if constexpr (MODE == kLayer) {
+        const long long C = 3LL * p.H * DK;
+        const uint16_t* cs = p.conv + (p.conv_off ? p.conv_off[u.b] : 0);
+#pragma unroll
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const int at = r + tap;
+            const uint16_t* src_row = at < WINDOW ? cs + (long long)at * C : p.P + (u.row0 + at - WINDOW) * p.p_stride;
+#pragma unroll
+            for (int part = 0; part < 3; ++part)
+                f(RawLayer::X + (tap * 3 + part) * 256, src_row + ((long long)part * p.H + u.h) * DK, 256, false);
+        }
+#pragma unroll
+        for (int part = 0; part < 3; ++part)
+            f(RawLayer::W + part * 1024, p.cw + (((long long)part * p.H + u.h) * DK) * TAPS, 1024, false);
+        f(RawLayer::A, p.A + gr * p.a_stride + (long long)u.h * DK, 256, false);
+        f(RawLayer::GATE, p.G + gr * p.g_stride + (long long)u.h * DV, 256, false);
+        f(RawLayer::DTB, p.dt_bias + (long long)u.h * DK, 512, false);
+        f(RawLayer::B, p.P + gr * p.p_stride + p.b_off + u.h, 2, true);
+    } else if constexpr (MODE == kCore) {
+        const long long at = (gr * p.H + u.h) * DK;
+        f(RawCore::Q, p.q + at, 256, false);
+        f(RawCore::K, p.k + at, 256, false);
+        f(RawCore::V, p.v + at, 256, false);
+        f(RawCore::GLOG, p.glog + at, 512, false);
+        if (p.G) f(RawCore::GATE, p.G + at, 256, false);
+        f(RawCore::B, p.beta + gr * p.H + u.h, 4, true);
+    } else {
+        const long long at = (gr * p.H + u.h) * DK;
+        f(RawReplay::K, p.k_save + u.layer * p.kv_stride + at, 512, false);
+        f(RawReplay::G, p.g_save + u.layer * p.kv_stride + at, 512, false);
+        f(RawReplay::V, p.v_save + u.layer * p.kv_stride + at, 256, false);
+        f(RawReplay::B, p.b_save + u.layer * p.b_stride + gr * p.H + u.h, 4, true);
+    }
+}
+
+template <typename S, int MODE>
+__device__ void mover_role(const Params& p, unsigned char* smem, uint64_t* bars, const WaitCtx& ctx, int lane) {
+    using L = Smem<S, MODE>;
+    uint64_t* st_full = bars;
+    uint64_t* st_empty = st_full + L::kStateSlots;
+    uint64_t* raw_full = st_empty + L::kStateSlots;
+    uint64_t* raw_empty = raw_full + L::kRawSlots;
+    Ring st, raw;
+    const bool copy0 = copies_state(p);
+    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
+        const Unit un = unit_of<MODE>(p, u);
+        if (un.rows == 0 && !copy0) continue;
+        // The unit's state.
+        if (!mbar_wait(&st_empty[st.idx], st.phase ^ 1u, ctx, kStatusWaitStateEmpty)) return;
+        {
+            unsigned char* dst = smem + L::oState + st.idx * L::kStateBytes;
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(p.state_in) + un.s_elem * (long long)sizeof(S);
+            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&st_full[st.idx], L::kStateBytes);
+                    bulk_load(dst, src, L::kStateBytes, &st_full[st.idx]);
+                }
+            } else {  // a state that is not 16-byte aligned: element-wise copy by the whole warp
+                const S* s = reinterpret_cast<const S*>(src);
+                S* d = reinterpret_cast<S*>(dst);
+                for (int e = lane; e < DV * DK; e += 32) d[e] = s[e];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&st_full[st.idx]);
+            }
+        }
+        st.next(L::kStateSlots);
+        // Its rows' raw inputs.
+        for (int r = 0; r < un.rows; ++r) {
+            if (!mbar_wait(&raw_empty[raw.idx], raw.phase ^ 1u, ctx, kStatusWaitRawEmpty)) return;
+            unsigned char* dst = smem + L::oRaw + raw.idx * L::kRawBytes;
+            uintptr_t low = 0;
+            uint32_t bytes = 0;
+            for_each_piece<MODE>(p, un, r, [&](int, const void* src, int n, bool scalar) {
+                if (!scalar) low |= reinterpret_cast<uintptr_t>(src);
+                bytes += scalar ? 16 : n;
+            });
+            if ((low & 15) == 0) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&raw_full[raw.idx], bytes);
+                    for_each_piece<MODE>(p, un, r, [&](int off, const void* src, int n, bool scalar) {
+                        if (scalar)
+                            bulk_load(dst + off, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(src) & ~uintptr_t(15)), 16,
+                                      &raw_full[raw.idx]);
+                        else
+                            bulk_load(dst + off, src, n, &raw_full[raw.idx]);
+                    });
+                }
+            } else {  // unaligned rows: 2-byte copies by the whole warp
+                for_each_piece<MODE>(p, un, r, [&](int off, const void* src, int n, bool scalar) {
+                    const uint16_t* s = reinterpret_cast<const uint16_t*>(src);
+                    uint16_t* d = reinterpret_cast<uint16_t*>(dst + off + (scalar ? (int)(reinterpret_cast<uintptr_t>(src) & 15) : 0));
+                    for (int e = lane; e < n / 2; e += 32) d[e] = s[e];
+                });
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&raw_full[raw.idx]);
+            }
+            raw.next(L::kRawSlots);
+            if (lane == 0) atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
+        }
+    }
+}
+
+// ---- the prologue --------------------------------------------------------------------------------------------
+// L2 norm of scratch[0..127] by one warp in the reference's order (kda.cu:151-165): lane partial over 4
+// consecutive channels from zero, butterfly, times 1/sqrt(ss + 1e-6), q also times 128^-0.5.
+__device__ __forceinline__ void l2norm_warp(const float* x, float* y, int lane, bool is_q) {
+    float v4[4], ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v4[i] = x[lane * 4 + i];
+        ss = ss + v4[i] * v4[i];
+    }
+    ss = butterfly1(ss);
+    const float inv = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float t = v4[i] * inv;
+        if (is_q) t = t * (1.0f / sqrtf((float)DK));
+        y[lane * 4 + i] = t;
+    }
+}
+
+template <typename S, int MODE>
+__device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* bars, const WaitCtx& ctx, int t) {
+    using L = Smem<S, MODE>;
+    uint64_t* raw_full = bars + 2 * L::kStateSlots;
+    uint64_t* raw_empty = raw_full + L::kRawSlots;
+    uint64_t* row_full = raw_empty + L::kRawSlots;
+    uint64_t* row_empty = row_full + 2 * L::kRowSlots;
+    float* scratch = reinterpret_cast<float*>(smem + L::oScratch);
+    const int warp = t >> 5, lane = t & 31;
+    Ring raw, row;
+    const bool copy0 = copies_state(p);
+    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
+        const Unit un = unit_of<MODE>(p, u);
+        if (un.rows == 0 && !copy0) continue;
+        float decay_rate = 0.0f;
+        if constexpr (MODE == kLayer) decay_rate = expf(p.a_log[un.h]);
+        for (int r = 0; r < un.rows; ++r) {
+            if (!mbar_wait(&raw_full[raw.idx], raw.phase, ctx, kStatusWaitRawFull)) return;
+            if (!mbar_wait(&row_empty[row.idx], row.phase ^ 1u, ctx, kStatusWaitRowEmpty)) return;
+            const unsigned char* in = smem + L::oRaw + raw.idx * L::kRawBytes;
+            Cooked& ck = *reinterpret_cast<Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
+            const long long gr = un.row0 + r;
+            bool normalise = true;
+            if constexpr (MODE == kLayer) {
+                // Short conv + SiLU, one bf16 rounding (kda.cu:129-142): thread t owns channel t of q, k and v.
+                const uint16_t* x = reinterpret_cast<const uint16_t*>(in + RawLayer::X);
+                const uint16_t* w = reinterpret_cast<const uint16_t*>(in + RawLayer::W);
+#pragma unroll
+                for (int part = 0; part < 3; ++part) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int tap = 0; tap < TAPS; ++tap)
+                        acc = acc + bf16_bits_to_f32(w[(part * DK + t) * TAPS + tap]) * bf16_bits_to_f32(x[(tap * 3 + part) * DK + t]);
+                    const float act = bf16_round(acc / (1.0f + expf(-acc)));
+                    if (part == 0) scratch[t] = act;
+                    else if (part == 1) scratch[DK + t] = act;
+                    else ck.v[t] = act;
+                }
+                // Decay multiplier (kda.cu:143-146) and sigmoid of the output gate (kda.cu:199-200).
+                const float a = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::A)[t]) +
+                                reinterpret_cast<const float*>(in + RawLayer::DTB)[t];
+                ck.g[t] = expf(p.lower * sigmoidf_(decay_rate * a));
+                ck.sg[t] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::GATE)[t]));
+                if (t == 0) {
+                    const uintptr_t addr = reinterpret_cast<uintptr_t>(p.P + gr * p.p_stride + p.b_off + un.h);
+                    const uint16_t logit = *reinterpret_cast<const uint16_t*>(in + RawLayer::B + (addr & 15));
+                    ck.beta = bf16_round(sigmoidf_(bf16_bits_to_f32(logit)));  // kda.cu:147-149
+                }
+            } else if constexpr (MODE == kCore) {
+                normalise = (p.flags & GLM53F_KDA_CORE_L2NORM) != 0;
+                const float qv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::Q)[t]);
+                const float kv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::K)[t]);
+                if (normalise) {
+                    scratch[t] = qv;
+                    scratch[DK + t] = kv;
+                } else {
+                    ck.q[t] = qv;
+                    ck.k[t] = kv;
+                }
+                ck.v[t] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::V)[t]);
+                ck.g[t] = expf(reinterpret_cast<const float*>(in + RawCore::GLOG)[t]);
+                if (p.G) ck.sg[t] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::GATE)[t]));
+                if (t == 0) {
+                    const uintptr_t addr = reinterpret_cast<uintptr_t>(p.beta + gr * p.H + un.h);
+                    ck.beta = *reinterpret_cast<const float*>(in + RawCore::B + (addr & 15));
+                }
+            } else {
+                normalise = false;
+                ck.k[t] = reinterpret_cast<const float*>(in + RawReplay::K)[t];
+                ck.g[t] = reinterpret_cast<const float*>(in + RawReplay::G)[t];
+                ck.v[t] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawReplay::V)[t]);
+                if (t == 0) {
+                    const uintptr_t addr = reinterpret_cast<uintptr_t>(p.b_save + un.layer * p.b_stride + gr * p.H + un.h);
+                    ck.beta = *reinterpret_cast<const float*>(in + RawReplay::B + (addr & 15));
+                }
+            }
+            if (MODE != kReplay && normalise) {
+                named_bar_sync(1, kProThreads);
+                if (warp == 0) l2norm_warp(scratch, ck.q, lane, true);
+                else if (warp == 1) l2norm_warp(scratch + DK, ck.k, lane, false);
+                named_bar_sync(2, kProThreads);  // scratch may be overwritten by the next row
+            }
+            mbar_arrive(&row_full[row.idx]);   // 128 arrivals: every thread's writes are released
+            mbar_arrive(&raw_empty[raw.idx]);  // 128 arrivals
+            raw.next(L::kRawSlots);
+            row.next(L::kRowSlots);
+        }
+    }
+}
+
+// ---- the recurrence ------------------------------------------------------------------------------------------
+template <typename S, int MODE>
+__device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* bars, const WaitCtx& ctx, int warp, int lane) {
+    using L = Smem<S, MODE>;
+    uint64_t* st_full = bars;
+    uint64_t* st_empty = st_full + L::kStateSlots;
+    uint64_t* row_full = st_empty + L::kStateSlots + 2 * L::kRawSlots;
+    uint64_t* y_full = row_full + L::kRowSlots;
+    uint64_t* row_empty = y_full + L::kRowSlots;
+    Ring st, row;
+    const bool copy0 = copies_state(p);
+    int pending = -1;  // lane 0: a state slot whose bulk store may still be reading shared memory
+    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
+        const Unit un = unit_of<MODE>(p, u);
+        if (un.rows == 0 && !copy0) continue;
+        if (!mbar_wait(&st_full[st.idx], st.phase, ctx, kStatusWaitStateFull)) return;
+        unsigned char* slot = smem + L::oState + st.idx * L::kStateBytes;
+        float s[kRowsPerLane][4];
+        if (un.rows > 0) load_rows<S>(slot, warp, lane, s);
+        const bool writes = p.state_out != nullptr;
+        if (!writes) {  // verify: the slot is free as soon as the registers hold the state
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&st_empty[st.idx]);
+        }
+        for (int r = 0; r < un.rows; ++r) {
+            if (!mbar_wait(&row_full[row.idx], row.phase, ctx, kStatusWaitRowFull)) return;
+            Cooked& ck = *reinterpret_cast<Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
+            float kk[4], gg[4];
+            {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ck.k[lane * 4]);
+                const float4 g4 = *reinterpret_cast<const float4*>(&ck.g[lane * 4]);
+                kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
+                gg[0] = g4.x; gg[1] = g4.y; gg[2] = g4.z; gg[3] = g4.w;
+            }
+            delta_rule(s, kk, gg, ck.v, warp, lane, ck.beta);
+            if constexpr (MODE != kReplay) {
+                // Read-out y = S q, rounded to bf16 (kda.cu:172-179).
+                const float4 q4 = *reinterpret_cast<const float4*>(&ck.q[lane * 4]);
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+                float part[kRowsPerLane];
+#pragma unroll
+                for (int j = 0; j < kRowsPerLane; ++j) {
+                    float o = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o = o + s[j][i] * qq[i];
+                    part[j] = o;
+                }
+                const float o = butterfly8(part, lane);
+                if ((lane & 3) == 0) ck.ys[warp * kRowsPerLane + (lane >> 2)] = bf16_round(o);
+            }
+            if constexpr (sizeof(S) == 2) {  // a bf16 state is rounded after every row, after its read-out
+#pragma unroll
+                for (int j = 0; j < kRowsPerLane; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[j][i] = bf16_round(s[j][i]);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                if (MODE != kReplay) mbar_arrive(&y_full[row.idx]);
+                else mbar_arrive(&row_empty[row.idx]);
+                if (warp == 0) atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
+            }
+            row.next(L::kRowSlots);
+        }
+        if (writes) {
+            if (un.rows > 0) store_rows<S>(slot, warp, lane, s);
+            constexpr int kWarpBytes = kRowsPerLane * DK * (int)sizeof(S);
+            unsigned char* dst = reinterpret_cast<unsigned char*>(p.state_out) + un.s_elem * (long long)sizeof(S) + (size_t)warp * kWarpBytes;
+            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    bulk_store(dst, slot + (size_t)warp * kWarpBytes, kWarpBytes);
+                    bulk_commit();
+                    if (pending >= 0) {
+                        bulk_wait_read<1>();
+                        mbar_arrive(&st_empty[pending]);
+                    }
+                    pending = st.idx;
+                }
+            } else {  // an unaligned destination: element-wise stores
+                __syncwarp();
+                const S* src = reinterpret_cast<const S*>(slot + (size_t)warp * kWarpBytes);
+                S* d = reinterpret_cast<S*>(dst);
+                for (int e = lane; e < kRowsPerLane * DK; e += 32) d[e] = src[e];
+                __syncwarp();
+                if (lane == 0) {
+                    if (pending >= 0) {
+                        bulk_wait_read<0>();
+                        mbar_arrive(&st_empty[pending]);
+                        pending = -1;
+                    }
+                    mbar_arrive(&st_empty[st.idx]);
+                }
+            }
+        }
+        st.next(L::kStateSlots);
+    }
+    if (lane == 0) bulk_wait_read<0>();
+}
+
+// ---- the epilogue --------------------------------------------------------------------------------------------
+template <typename S, int MODE>
+__device__ void epilogue_role(const Params& p, unsigned char* smem, uint64_t* bars, const WaitCtx& ctx, int lane) {
+    using L = Smem<S, MODE>;
+    uint64_t* y_full = bars + 2 * L::kStateSlots + 2 * L::kRawSlots + L::kRowSlots;
+    uint64_t* row_empty = y_full + L::kRowSlots;
+    Ring row;
+    const bool copy0 = copies_state(p);
+    const bool gated = MODE == kLayer || p.G != nullptr;
+    float nw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (gated)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) nw[i] = bf16_bits_to_f32(p.norm_w[lane * 4 + i]);
+    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
+        const Unit un = unit_of<MODE>(p, u);
+        if (un.rows == 0 && !copy0) continue;
+        for (int r = 0; r < un.rows; ++r) {
+            if (!mbar_wait(&y_full[row.idx], row.phase, ctx, kStatusWaitYFull)) return;
+            const Cooked& ck = *reinterpret_cast<const Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
+            const long long gr = un.row0 + r;
+            float y[4];
+            {
+                const float4 y4 = *reinterpret_cast<const float4*>(&ck.ys[lane * 4]);
+                y[0] = y4.x; y[1] = y4.y; y[2] = y4.z; y[3] = y4.w;
+            }
+            uint16_t o[4];
+            if (gated) {  // kda.cu:188-201
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ss = ss + y[i] * y[i];
+                ss = butterfly1(ss);
+                const float rinv = 1.0f / sqrtf(ss / (float)DV + p.eps);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float yn = y[i] * rinv;
+                    const float yw = nw[i] * yn;
+                    o[i] = f32_to_bf16_bits(yw * ck.sg[lane * 4 + i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = f32_to_bf16_bits(y[i]);
+            }
+            uint16_t* dst = p.out + gr * p.out_stride + (long long)un.h * DV + lane * 4;
+            if ((reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)o[0] | ((uint32_t)o[1] << 16), (uint32_t)o[2] | ((uint32_t)o[3] << 16));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = o[i];
+            }
+            if (p.k_save != nullptr) {  // kda.cu:181-186
+                const long long base = (gr * p.H + un.h) * DK + lane * 4;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    p.k_save[base + i] = ck.k[lane * 4 + i];
+                    p.g_save[base + i] = ck.g[lane * 4 + i];
+                    p.v_save[base + i] = f32_to_bf16_bits(ck.v[lane * 4 + i]);
+                }
+                if (lane == 0) p.b_save[gr * p.H + un.h] = ck.beta;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&row_empty[row.idx]);
+            row.next(L::kRowSlots);
+        }
+    }
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------------------
+template <typename S, int MODE>
+__global__ void __launch_bounds__(kThreads, 1) recurrent_kernel(const __grid_constant__ Params p) {
+    using L = Smem<S, MODE>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::oBars);
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + L::oCtl);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        uint64_t* b = bars;
+        for (int i = 0; i < L::kStateSlots; ++i) mbar_init(b++, 1);                                // st_full
+        for (int i = 0; i < L::kStateSlots; ++i) mbar_init(b++, kRecWarps);                        // st_empty
+        for (int i = 0; i < L::kRawSlots; ++i) mbar_init(b++, 1);                                     // raw_full
+        for (int i = 0; i < L::kRawSlots; ++i) mbar_init(b++, kProThreads);                           // raw_empty
+        for (int i = 0; i < L::kRowSlots; ++i) mbar_init(b++, kProThreads);                           // row_full
+        for (int i = 0; i < L::kRowSlots; ++i) mbar_init(b++, kRecWarps);                             // y_full
+        for (int i = 0; i < L::kRowSlots; ++i) mbar_init(b++, MODE == kReplay ? kRecWarps : 1);       // row_empty
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const WaitCtx ctx{ctl, ctl + 1, &g_status};
+    if (warp < kRecWarps) {
+        recurrence_role<S, MODE>(p, smem, bars, ctx, warp, lane);
+    } else if (warp < kRecWarps + kProWarps) {
+        prologue_role<S, MODE>(p, smem, bars, ctx, tid - kRecThreads);
+    } else if (warp == kRecWarps + kProWarps) {
+        if (MODE != kReplay) epilogue_role<S, MODE>(p, smem, bars, ctx, lane);
+    } else {
+        mover_role<S, MODE>(p, smem, bars, ctx, lane);
+    }
+    // No thread leaves while bulk loads into this block's shared memory may still be in flight: the mover issues a
+    // load only after its consumers freed the slot, and every consumer role waits for every load before it ends,
+    // except after an abort -- then give outstanding loads a bounded time to land.
+    if (ctl[1]) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+    }
+    __syncthreads();
+}
+
+template <typename S, int MODE>
+int launch(const Params& p, cudaStream_t stream) {
+    using L = Smem<S, MODE>;
+    static bool configured = false;  // per process; the attribute is per device, so set it on every device change
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured || configured_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(recurrent_kernel<S, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+        configured_dev = dev;
+    }
+    const long long sms = sm_count();
+    const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
+    recurrent_kernel<S, MODE><<<grid, kThreads, L::kBytes, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+template <int MODE>
+int launch_typed(const Params& p, bool bf16_state, cudaStream_t stream) {
+    return bf16_state ? launch<__nv_bfloat16, MODE>(p, stream) : launch<float, MODE>(p, stream);
+}
+
+bool saves_ok(const void* k, const void* v, const void* g, const void* b) {
+    const int n = (k != nullptr) + (v != nullptr) + (g != nullptr) + (b != nullptr);
+    return n == 0 || n == 4;
+}
+
+// Reference kda.cu:290-299, 310-312, 329-332.
+int chain_entry(int32_t heads, int32_t batch, bool batched, const int32_t* cu_rows, int32_t rows, const glm53f_bf16* p,
+                int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g,
+                int64_t g_stride, const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w,
+                const void* state_in, void* state_out, const int64_t* state_off, bool bf16_state, const float* a_log,
+                const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower, glm53f_bf16* out,
+                int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save,
+                glm53f_stream_t stream) {
+    if (heads < 1 || heads > 65535) return kInvalid;
+    if (!p || !a || !g || !conv || !conv_w || !state_in || !a_log || !dt_bias || !norm_w || !out) return kInvalid;
+    if (!saves_ok(k_save, v_save, g_save, b_save)) return kInvalid;
+    if (batched) {
+        if (batch < 1 || batch > 65535 || !cu_rows || !conv_off || !state_off) return kInvalid;
+    } else if (rows < 1) {
+        return kInvalid;
+    }
+    Params q{};
+    q.H = heads;
+    q.layers = 1;
+    q.units = (long long)heads * batch;
+    q.cu_rows = cu_rows;
+    q.rows1 = rows;
+    q.P = p; q.p_stride = p_stride; q.b_off = b_off;
+    q.A = a; q.a_stride = a_stride;
+    q.G = g; q.g_stride = g_stride;
+    q.conv = conv; q.conv_off = reinterpret_cast<const long long*>(conv_off); q.cw = conv_w;
+    q.a_log = a_log; q.dt_bias = dt_bias; q.norm_w = norm_w; q.eps = eps; q.lower = lower;
+    q.state_in = state_in; q.state_out = state_out; q.state_stride = 0;
+    q.state_off = reinterpret_cast<const long long*>(state_off);
+    q.out = out; q.out_stride = out_stride;
+    q.k_save = k_save; q.v_save = v_save; q.g_save = g_save; q.b_save = b_save;
+    return launch_typed<kLayer>(q, bf16_state, (cudaStream_t)stream);
+}
+
+// Reference kda.cu:381-383, 412, 424.
+int replay_entry(int32_t heads, int32_t layers, int32_t batch, bool batched, const int32_t* cu_rows, const int32_t* keep,
+                 int32_t rows, const void* state_in, void* state_out, int64_t state_stride, const int64_t* state_off,
+                 bool bf16_state, const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                 const float* b_save, int64_t kv_stride, int64_t b_stride, glm53f_stream_t stream) {
+    if (batched && (!cu_rows || !keep || !state_off)) return kInvalid;
+    if (heads < 1 || layers < 1 || batch < 1 || batch > 65535 || (long long)heads * layers > 0x7fffffffLL || !state_in ||
+        !state_out || !k_save || !v_save || !g_save || !b_save || rows < 0)
+        return kInvalid;
+    Params q{};
+    q.H = heads;
+    q.layers = layers;
+    q.units = (long long)heads * layers * batch;
+    q.cu_rows = cu_rows;
+    q.keep = keep;
+    q.rows1 = rows;
+    q.state_in = state_in; q.state_out = state_out; q.state_stride = state_stride;
+    q.state_off = reinterpret_cast<const long long*>(state_off);
+    q.k_save = const_cast<float*>(k_save); q.v_save = const_cast<glm53f_bf16*>(v_save);
+    q.g_save = const_cast<float*>(g_save); q.b_save = const_cast<float*>(b_save);
+    q.kv_stride = kv_stride; q.b_stride = b_stride;
+    return launch_typed<kReplay>(q, bf16_state, (cudaStream_t)stream);
+}
+
+int core_entry(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+               const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
+               const int64_t* state_off, int32_t state_bf16, int32_t flags, const glm53f_bf16* gate,
+               const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, float* k_save, glm53f_bf16* v_save,
+               float* g_save, float* b_save, glm53f_stream_t stream) {
+    if (heads < 1 || heads > 65535 || batch < 1 || batch > 65535) return kInvalid;
+    if (!cu_rows || !q || !k || !v || !g || !beta || !state_in || !state_off || !out) return kInvalid;
+    if (gate && !norm_w) return kInvalid;
+    if (flags & ~GLM53F_KDA_CORE_L2NORM) return kInvalid;
+    if (!saves_ok(k_save, v_save, g_save, b_save)) return kInvalid;
+    Params x{};
+    x.H = heads;
+    x.layers = 1;
+    x.units = (long long)heads * batch;
+    x.cu_rows = cu_rows;
+    x.q = q; x.k = k; x.v = v; x.glog = g; x.beta = beta; x.flags = flags;
+    x.G = gate; x.norm_w = norm_w; x.eps = eps;
+    x.state_in = state_in; x.state_out = state_out;
+    x.state_off = reinterpret_cast<const long long*>(state_off);
+    x.out = out; x.out_stride = (long long)heads * DV;
+    x.k_save = k_save; x.v_save = v_save; x.g_save = g_save; x.b_save = b_save;
+    return launch_typed<kCore>(x, state_bf16 != 0, (cudaStream_t)stream);
+}
+
+}  // namespace
+
+int layer_chain_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t rows, const glm53f_bf16* p,
+                       int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g,
+                       int64_t g_stride, const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w,
+                       const void* state_in, void* state_out, const int64_t* state_off, bool bf16_state,
+                       const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower,
+                       glm53f_bf16* out, int64_t out_stride, cudaStream_t stream) {
+    Params q{};
+    q.H = heads;
+    q.layers = 1;
+    q.units = (long long)heads * batch;
+    q.cu_rows = cu_rows;
+    q.rows1 = rows;
+    q.P = p; q.p_stride = p_stride; q.b_off = b_off;
+    q.A = a; q.a_stride = a_stride;
+    q.G = g; q.g_stride = g_stride;
+    q.conv = conv; q.conv_off = reinterpret_cast<const long long*>(conv_off); q.cw = conv_w;
+    q.a_log = a_log; q.dt_bias = dt_bias; q.norm_w = norm_w; q.eps = eps; q.lower = lower;
+    q.state_in = state_in; q.state_out = state_out;
+    q.state_off = reinterpret_cast<const long long*>(state_off);
+    q.out = out; q.out_stride = out_stride;
+    return launch_typed<kLayer>(q, bf16_state, stream);
+}
+
+int core_chain_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+                      const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
+                      const int64_t* state_off, bool bf16_state, int32_t flags, const glm53f_bf16* gate,
+                      const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, cudaStream_t stream) {
+    return core_entry(heads, batch, cu_rows, q, k, v, g, beta, state_in, state_out, state_off, bf16_state ? 1 : 0, flags, gate,
+                      norm_w, eps, out, nullptr, nullptr, nullptr, nullptr, (glm53f_stream_t)stream);
+}
+
+}  // namespace kda
+
+using namespace kda;
+
+extern "C" int glm53f_kda_chain(int32_t heads, int32_t rows, const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                                const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g, int64_t g_stride,
+                                const glm53f_bf16* conv, const glm53f_bf16* conv_w, const float* state_in,
+                                float* state_out, const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                                float eps, float lower, glm53f_bf16* out, int64_t out_stride, float* k_save,
+                                glm53f_bf16* v_save, float* g_save, float* b_save, glm53f_stream_t stream) {
+    return chain_entry(heads, 1, false, nullptr, rows, p, p_stride, b_off, a, a_stride, g, g_stride, conv, nullptr, conv_w,
+                       state_in, state_out, nullptr, false, a_log, dt_bias, norm_w, eps, lower, out, out_stride, k_save,
+                       v_save, g_save, b_save, stream);
+}
+
+extern "C" int glm53f_kda_chain_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* p,
+                                      int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride,
+                                      const glm53f_bf16* g, int64_t g_stride, const glm53f_bf16* conv,
+                                      const int64_t* conv_off, const glm53f_bf16* conv_w, const float* state_in,
+                                      float* state_out, const int64_t* state_off, const float* a_log,
+                                      const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower,
+                                      glm53f_bf16* out, int64_t out_stride, float* k_save, glm53f_bf16* v_save,
+                                      float* g_save, float* b_save, glm53f_stream_t stream) {
+    return chain_entry(heads, batch, true, cu_rows, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
+                       conv_w, state_in, state_out, state_off, false, a_log, dt_bias, norm_w, eps, lower, out,
+                       out_stride, k_save, v_save, g_save, b_save, stream);
+}
+
+extern "C" int glm53f_kda_chain_batch_bf16state(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                                                const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                                                const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g,
+                                                int64_t g_stride, const glm53f_bf16* conv, const int64_t* conv_off,
+                                                const glm53f_bf16* conv_w, const glm53f_bf16* state_in,
+                                                glm53f_bf16* state_out, const int64_t* state_off, const float* a_log,
+                                                const float* dt_bias, const glm53f_bf16* norm_w, float eps,
+                                                float lower, glm53f_bf16* out, int64_t out_stride, float* k_save,
+                                                glm53f_bf16* v_save, float* g_save, float* b_save,
+                                                glm53f_stream_t stream) {
+    return chain_entry(heads, batch, true, cu_rows, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
+                       conv_w, state_in, state_out, state_off, true, a_log, dt_bias, norm_w, eps, lower, out, out_stride,
+                       k_save, v_save, g_save, b_save, stream);
+}
+
+extern "C" int glm53f_kda_replay(int32_t heads, int32_t rows, const float* state_in, float* state_out,
+                                 const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                                 const float* b_save, glm53f_stream_t stream) {
+    return replay_entry(heads, 1, 1, false, nullptr, nullptr, rows, state_in, state_out, 0, nullptr, false, k_save,
+                        v_save, g_save, b_save, 0, 0, stream);
+}
+
+extern "C" int glm53f_kda_replay_layers(int32_t heads, int32_t layers, int32_t rows, const float* state_in,
+                                        float* state_out, int64_t state_stride, const float* k_save,
+                                        const glm53f_bf16* v_save, const float* g_save, const float* b_save,
+                                        int64_t kv_stride, int64_t b_stride, glm53f_stream_t stream) {
+    return replay_entry(heads, layers, 1, false, nullptr, nullptr, rows, state_in, state_out, state_stride, nullptr,
+                        false, k_save, v_save, g_save, b_save, kv_stride, b_stride, stream);
+}
+
+extern "C" int glm53f_kda_replay_batch(int32_t heads, int32_t layers, int32_t batch, const int32_t* cu_rows,
+                                       const int32_t* keep, const float* state_in, float* state_out,
+                                       int64_t state_stride, const int64_t* state_off, const float* k_save,
+                                       const glm53f_bf16* v_save, const float* g_save, const float* b_save,
+                                       int64_t kv_stride, int64_t b_stride, glm53f_stream_t stream) {
+    return replay_entry(heads, layers, batch, true, cu_rows, keep, 0, state_in, state_out, state_stride, state_off, false,
+                        k_save, v_save, g_save, b_save, kv_stride, b_stride, stream);
+}
+
+extern "C" int glm53f_kda_replay_batch_bf16state(int32_t heads, int32_t layers, int32_t batch, const int32_t* cu_rows,
+                                                 const int32_t* keep, const glm53f_bf16* state_in,
+                                                 glm53f_bf16* state_out, int64_t state_stride,
+                                                 const int64_t* state_off, const float* k_save,
+                                                 const glm53f_bf16* v_save, const float* g_save, const float* b_save,
+                                                 int64_t kv_stride, int64_t b_stride, glm53f_stream_t stream) {
+    return replay_entry(heads, layers, batch, true, cu_rows, keep, 0, state_in, state_out, state_stride, state_off, true,
+                        k_save, v_save, g_save, b_save, kv_stride, b_stride, stream);
+}
+
+extern "C" int glm53f_kda_core_decode_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q,
+                                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g,
+                                            const float* beta, const void* state_in, void* state_out,
+                                            const int64_t* state_off, int32_t state_bf16, int32_t flags,
+                                            const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                            glm53f_bf16* out, glm53f_stream_t stream) {
+    return core_entry(heads, batch, cu_rows, q, k, v, g, beta, state_in, state_out, state_off, state_bf16, flags, gate,
+                      norm_w, eps, out, nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+extern "C" int glm53f_kda_core_verify_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q,
+                                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g,
+                                            const float* beta, const void* state_in, void* state_out,
+                                            const int64_t* state_off, int32_t state_bf16, int32_t flags,
+                                            const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                            glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save,
+                                            float* b_save, glm53f_stream_t stream) {
+    return core_entry(heads, batch, cu_rows, q, k, v, g, beta, state_in, state_out, state_off, state_bf16, flags, gate,
+                      norm_w, eps, out, k_save, v_save, g_save, b_save, stream);
+}
+
+extern "C" int glm53f_kda_core_commit_batch(int32_t heads, int32_t layers, int32_t batch, const int32_t* cu_rows,
+                                            const int32_t* keep, const void* state_in, void* state_out,
+                                            int64_t state_stride, const int64_t* state_off, int32_t state_bf16,
+                                            const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                                            const float* b_save, int64_t kv_stride, int64_t b_stride,
+                                            glm53f_stream_t stream) {
+    return replay_entry(heads, layers, batch, true, cu_rows, keep, 0, state_in, state_out, state_stride, state_off,
+                        state_bf16 != 0, k_save, v_save, g_save, b_save, kv_stride, b_stride, stream);
+}
+
+int* kda::status_word() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+
+extern "C" int glm53f_kda_device_status(void) {
+    int v = 0, zero = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemcpyFromSymbol(&v, g_status, sizeof v);
+    if (e != cudaSuccess) return (int)e;
+    if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof zero);
+    return v;
+}

@@ -1,0 +1,37 @@
+// Launchers shared between the translation units of the library (not part of the C ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "glm53f_kda.h"
+
+namespace kda {
+
+// The layer chain without the rows >= 1 restriction of glm53f_kda_chain: a request with no rows copies its state.
+// cu_rows == nullptr runs one request of `rows` rows (conv_off / state_off may then be nullptr too).
+int layer_chain_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t rows, const glm53f_bf16* p,
+                       int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g,
+                       int64_t g_stride, const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w,
+                       const void* state_in, void* state_out, const int64_t* state_off, bool bf16_state,
+                       const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower,
+                       glm53f_bf16* out, int64_t out_stride, cudaStream_t stream);
+
+// The core chain (row-by-row recurrence) on post-conv inputs; the slow-but-exact fallback of the chunked prefill.
+int core_chain_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+                      const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
+                      const int64_t* state_off, bool bf16_state, int32_t flags, const glm53f_bf16* gate,
+                      const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, cudaStream_t stream);
+
+// Window past `keep` rows for every (layer, request): keep from keep[b], else keep1 if >= 0, else the request's
+// whole row count (the prefill's advance).
+int conv_shift_launch(int32_t channels, int32_t layers, int32_t batch, const int32_t* cu_rows, const int32_t* keep,
+                      int32_t keep1, int32_t rows1, glm53f_bf16* conv, int64_t conv_stride, const int64_t* conv_off,
+                      const glm53f_bf16* p, int64_t p_layer_stride, int64_t p_stride, cudaStream_t stream);
+
+int sm_count();
+
+// Device address of the status word kernels record a timed-out wait in (current device).
+int* status_word();
+
+}  // namespace kda

@@ -1,0 +1,274 @@
+/* glm53f_kda.h: C ABI of the B200 (sm_100a) KDA (Kimi delta attention) recurrent core.
+ *
+ * Part 1 declares the thirteen entry points of the reference crate's kernel header
+ * (crates/glm53f-kda/kernels/glm53f_kda.h:73-270, bound by crates/glm53f-kda/src/ffi.rs:16-287) with the
+ * same names, argument order, types and meaning, so the reference's Rust `ffi` module links against this
+ * library unchanged.  Part 2 adds the "core" entry points the benchmark configurations use (inputs after
+ * the short convolution: q, k, v, log decay, beta) and one entry point for callers that cannot allocate.
+ *
+ * Conventions shared by every entry point (reference header lines 5-9, 43-47):
+ *   - raw device pointers, strides and offsets in ELEMENTS of the pointed-to type, a CUDA stream;
+ *   - the return value is a cudaError_t: 0 = enqueued, 1 (cudaErrorInvalidValue) = rejected on the host
+ *     before anything was enqueued, anything else = the launch error;
+ *   - launches are asynchronous on `stream`; nothing is allocated, nothing is synchronised;
+ *   - device-side metadata arrays (cu_rows, keep, conv_off, state_off) are read on the device only, so a
+ *     captured graph can be replayed with new metadata.
+ *
+ * Geometry: DK = DV = 128, TAPS = 4, any heads H in [1, 65535]; C = 3*H*128 conv channels (q | k | v).
+ *
+ * Layouts (row-major):
+ *   recurrent state   [H][128 (v)][128 (k)], f32 or (the *_bf16state entry points) bf16
+ *   conv window       bf16 [3][C], the 3 projection rows before the window's first row, oldest first
+ *   conv weight       bf16 [C][4], tap 3 multiplies the current row
+ *   replay saves      row r, head h: k (f32, L2-normalised) and exp(g) (f32) at (r*H + h)*128, v (bf16) at the
+ *                     same index, beta (f32) at r*H + h
+ *
+ * Numerics: FP32 arithmetic in the reference kernels' operation order with no multiply-add contraction for
+ * everything the chain, the replays and the conv shift compute, so those entry points return the reference
+ * kernels' bits.  The chunked prefill agrees with the chain to rounding, as the reference's does.
+ */
+#ifndef GLM53F_KDA_H
+#define GLM53F_KDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+struct CUstream_st;
+typedef struct CUstream_st* glm53f_stream_t; /* cudaStream_t; NULL = the legacy default stream */
+typedef uint16_t glm53f_bf16;                /* raw bfloat16 bits */
+
+#define GLM53F_KDA_DK 128
+#define GLM53F_KDA_DV 128
+#define GLM53F_KDA_TAPS 4
+
+/* ===================================================================================================
+ * Part 1: the reference's entry points
+ * =================================================================================================== */
+
+/* Replaces reference glm53f_kda.h:73-83 (kernels/kda.cu:303-318).
+ * One layer, one request, `rows` >= 1 consecutive rows from the committed state.
+ *   p        bf16 rows; row r has q|k|v at [0, C) of p + r*p_stride and H beta logits at [b_off, b_off+H)
+ *            (b_off may be negative)
+ *   a, g     bf16 forget-gate / output-gate rows, [H*128] each, strides a_stride / g_stride
+ *   conv     bf16 [3][C] window (read only);  conv_w bf16 [C][4]
+ *   state_in f32 [H][128][128];  state_out the state after the last row, may be NULL or == state_in
+ *   a_log f32 [H]; dt_bias f32 [H*128]; norm_w bf16 [128]; eps 1e-5; lower -5
+ *   out      bf16 rows [H*128] at out + r*out_stride: the gated RMSNorm output
+ *   k_save, v_save, g_save, b_save   replay inputs for every row; all NULL or all set */
+int glm53f_kda_chain(int32_t heads, int32_t rows,
+                     const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                     const glm53f_bf16* a, int64_t a_stride,
+                     const glm53f_bf16* g, int64_t g_stride,
+                     const glm53f_bf16* conv, const glm53f_bf16* conv_w,
+                     const float* state_in, float* state_out,
+                     const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                     float eps, float lower,
+                     glm53f_bf16* out, int64_t out_stride,
+                     float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save,
+                     glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:97-108 (kernels/kda.cu:343-354).
+ * A batch of requests: request b owns rows [cu_rows[b], cu_rows[b+1]) (device int32 [batch+1]; 0 rows
+ * allowed, the state is then copied), its window is conv + conv_off[b], its state state_in + state_off[b]
+ * written to state_out + state_off[b] (device int64 [batch] each; regions must not overlap). */
+int glm53f_kda_chain_batch(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                           const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                           const glm53f_bf16* a, int64_t a_stride,
+                           const glm53f_bf16* g, int64_t g_stride,
+                           const glm53f_bf16* conv, const int64_t* conv_off,
+                           const glm53f_bf16* conv_w,
+                           const float* state_in, float* state_out, const int64_t* state_off,
+                           const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                           float eps, float lower,
+                           glm53f_bf16* out, int64_t out_stride,
+                           float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save,
+                           glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:118-130 (kernels/kda.cu:356-371).
+ * As above with bf16 states (offsets in bf16 elements): FP32 arithmetic on the widened state, rounded to
+ * bf16 after every row's read-out, so R rows in one call equal R single-row calls bit for bit. */
+int glm53f_kda_chain_batch_bf16state(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                                     const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                                     const glm53f_bf16* a, int64_t a_stride,
+                                     const glm53f_bf16* g, int64_t g_stride,
+                                     const glm53f_bf16* conv, const int64_t* conv_off,
+                                     const glm53f_bf16* conv_w,
+                                     const glm53f_bf16* state_in, glm53f_bf16* state_out,
+                                     const int64_t* state_off,
+                                     const float* a_log, const float* dt_bias,
+                                     const glm53f_bf16* norm_w, float eps, float lower,
+                                     glm53f_bf16* out, int64_t out_stride,
+                                     float* k_save, glm53f_bf16* v_save, float* g_save,
+                                     float* b_save, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:136-138 (kernels/kda.cu:392-397).
+ * The state after the first `rows` >= 0 saved rows of a chain; state_out may equal state_in. */
+int glm53f_kda_replay(int32_t heads, int32_t rows, const float* state_in, float* state_out,
+                      const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                      const float* b_save, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:144-148 (kernels/kda.cu:399-405).
+ * Every layer of one request: layer l at state + l*state_stride, saves + l*kv_stride, b_save + l*b_stride. */
+int glm53f_kda_replay_layers(int32_t heads, int32_t layers, int32_t rows,
+                             const float* state_in, float* state_out, int64_t state_stride,
+                             const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                             const float* b_save, int64_t kv_stride, int64_t b_stride,
+                             glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:157-163 (kernels/kda.cu:407-415).
+ * The commit after a verify round: every layer of every request; request b replays keep[b] rows from its
+ * row cu_rows[b], 0 <= keep[b] <= its row count (device int32 [batch]). */
+int glm53f_kda_replay_batch(int32_t heads, int32_t layers, int32_t batch,
+                            const int32_t* cu_rows, const int32_t* keep,
+                            const float* state_in, float* state_out, int64_t state_stride,
+                            const int64_t* state_off,
+                            const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                            const float* b_save, int64_t kv_stride, int64_t b_stride,
+                            glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:170-176 (kernels/kda.cu:417-427).  bf16 states, rounded after every row. */
+int glm53f_kda_replay_batch_bf16state(int32_t heads, int32_t layers, int32_t batch,
+                                      const int32_t* cu_rows, const int32_t* keep,
+                                      const glm53f_bf16* state_in, glm53f_bf16* state_out,
+                                      int64_t state_stride, const int64_t* state_off,
+                                      const float* k_save, const glm53f_bf16* v_save,
+                                      const float* g_save, const float* b_save, int64_t kv_stride,
+                                      int64_t b_stride, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:183-184 (kernels/kda.cu:448-451).
+ * Window rows j = 0..2 become rows keep+j of [window; new rows], in place; new row r is [0, channels) of
+ * p + r*p_stride. */
+int glm53f_kda_conv_shift(int32_t channels, int32_t keep, glm53f_bf16* conv,
+                          const glm53f_bf16* p, int64_t p_stride, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:191-195 (kernels/kda.cu:453-460).
+ * Every layer of every request: window conv + l*conv_stride + conv_off[b], new rows from
+ * p + l*p_layer_stride + cu_rows[b]*p_stride, keep[b] rows kept. */
+int glm53f_kda_conv_shift_batch(int32_t channels, int32_t layers, int32_t batch,
+                                const int32_t* cu_rows, const int32_t* keep,
+                                glm53f_bf16* conv, int64_t conv_stride, const int64_t* conv_off,
+                                const glm53f_bf16* p, int64_t p_layer_stride, int64_t p_stride,
+                                glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:204 (kernels/kda_prefill.cu:695-698).
+ * Bytes of workspace for `rows_per_pass` rows of every request per pass; the reference's figure
+ * (34,816 B per 16 rows, head and request) is kept so callers' arenas fit.  0 for bad arguments. */
+int64_t glm53f_kda_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t rows_per_pass);
+
+/* Replaces reference glm53f_kda.h:223-232 (kernels/kda_prefill.cu:700-710).
+ * Prefill of `rows` >= 0 rows from the committed state and window; also advances the window past the rows,
+ * in place.  state_out must not be NULL (may equal state_in); lower in [-5.8, 0]; value_blocks in
+ * {0, 1, 2, 4}; workspace of at least glm53f_kda_prefill_workspace_bytes(heads, 1, 16) bytes. */
+int glm53f_kda_prefill(int32_t heads, int32_t rows,
+                       const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                       const glm53f_bf16* a, int64_t a_stride,
+                       const glm53f_bf16* g, int64_t g_stride,
+                       glm53f_bf16* conv, const glm53f_bf16* conv_w,
+                       const float* state_in, float* state_out,
+                       const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                       float eps, float lower,
+                       glm53f_bf16* out, int64_t out_stride, int32_t value_blocks,
+                       float* workspace, int64_t workspace_bytes, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:240-250 (kernels/kda_prefill.cu:712-725).  max_rows (host) >= the longest
+ * request's rows. */
+int glm53f_kda_prefill_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t max_rows,
+                             const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                             const glm53f_bf16* a, int64_t a_stride,
+                             const glm53f_bf16* g, int64_t g_stride,
+                             glm53f_bf16* conv, const int64_t* conv_off,
+                             const glm53f_bf16* conv_w,
+                             const float* state_in, float* state_out, const int64_t* state_off,
+                             const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                             float eps, float lower,
+                             glm53f_bf16* out, int64_t out_stride, int32_t value_blocks,
+                             float* workspace, int64_t workspace_bytes, glm53f_stream_t stream);
+
+/* Replaces reference glm53f_kda.h:260-270 (kernels/kda_prefill.cu:727-742).  bf16 states. */
+int glm53f_kda_prefill_batch_bf16state(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                                       int32_t max_rows, const glm53f_bf16* p, int64_t p_stride,
+                                       int64_t b_off, const glm53f_bf16* a, int64_t a_stride,
+                                       const glm53f_bf16* g, int64_t g_stride, glm53f_bf16* conv,
+                                       const int64_t* conv_off, const glm53f_bf16* conv_w,
+                                       const glm53f_bf16* state_in, glm53f_bf16* state_out,
+                                       const int64_t* state_off, const float* a_log,
+                                       const float* dt_bias, const glm53f_bf16* norm_w, float eps,
+                                       float lower, glm53f_bf16* out, int64_t out_stride,
+                                       int32_t value_blocks, float* workspace,
+                                       int64_t workspace_bytes, glm53f_stream_t stream);
+
+/* ===================================================================================================
+ * Part 2: the core entry points (inputs after the short convolution)
+ *
+ * These take what the reference's CPU definitions of the recurrence take (crates/glm53f-kda/src/cpu.rs:573-610,
+ * `literal::step`, and src/chunked.rs:67-75, `head`): per row and head q, k, v (bf16, dense [rows][H][128]),
+ * the per-channel LOG decay g (f32 [rows][H][128], <= 0) and beta (f32 [rows][H]).  The reference's kernels
+ * have no such entry points; its forward always enters through Part 1.
+ *
+ * Common arguments:
+ *   state_in / state_out, state_off   as in glm53f_kda_chain_batch; state_bf16 != 0 selects bf16 storage
+ *                                     (rounded after every row in decode/verify/commit, once per chunk in prefill)
+ *   flags    GLM53F_KDA_CORE_L2NORM   q and k are L2-normalised (eps 1e-6 inside the sum) and q is scaled by
+ *                                     128^-0.5 in the kernel; without it q, k are used as given
+ *   gate, norm_w, eps                 gate != NULL fuses the gated RMSNorm: out = bf16(norm_w * y/rms(y) *
+ *                                     sigmoid(gate)), gate bf16 [rows][H][128]; gate == NULL stores bf16(y)
+ *   out                               bf16 [rows][H][128]
+ * =================================================================================================== */
+
+#define GLM53F_KDA_CORE_L2NORM 1
+
+/* One recurrent step per row, rows of request b run in order from its state (decode: one row per request). */
+int glm53f_kda_core_decode_batch(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                                 const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                 const float* g, const float* beta,
+                                 const void* state_in, void* state_out, const int64_t* state_off,
+                                 int32_t state_bf16, int32_t flags,
+                                 const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                 glm53f_bf16* out, glm53f_stream_t stream);
+
+/* Draft verification: as decode over each request's window of rows, with the replay saves written
+ * (k f32, v bf16, exp(g) f32, beta f32; layout of Part 1) and the state optionally left untouched
+ * (state_out == NULL). */
+int glm53f_kda_core_verify_batch(int32_t heads, int32_t batch, const int32_t* cu_rows,
+                                 const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                 const float* g, const float* beta,
+                                 const void* state_in, void* state_out, const int64_t* state_off,
+                                 int32_t state_bf16, int32_t flags,
+                                 const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                 glm53f_bf16* out,
+                                 float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save,
+                                 glm53f_stream_t stream);
+
+/* The commit after a verify round, for every layer at once: glm53f_kda_replay_batch with the state type as
+ * an argument.  Keeping keep[b] rows gives the bits of keep[b] single-row decode calls. */
+int glm53f_kda_core_commit_batch(int32_t heads, int32_t layers, int32_t batch,
+                                 const int32_t* cu_rows, const int32_t* keep,
+                                 const void* state_in, void* state_out, int64_t state_stride,
+                                 const int64_t* state_off, int32_t state_bf16,
+                                 const float* k_save, const glm53f_bf16* v_save, const float* g_save,
+                                 const float* b_save, int64_t kv_stride, int64_t b_stride,
+                                 glm53f_stream_t stream);
+
+/* Chunked prefill (chunk 64) of variable-length sequences packed along the row axis: sequence b owns rows
+ * [cu_seqlens[b], cu_seqlens[b+1]) (device int32 [batch+1]); chunks count from each sequence's first row.
+ * max_len (host) >= the longest sequence.  state_out must not be NULL. */
+int glm53f_kda_core_prefill_varlen(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
+                                   const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                   const float* g, const float* beta,
+                                   const void* state_in, void* state_out, const int64_t* state_off,
+                                   int32_t state_bf16, int32_t flags,
+                                   const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                   glm53f_bf16* out, glm53f_stream_t stream);
+
+/* Status word of the most recent launches on the current device: 0, or a code recorded by a kernel whose
+ * bounded wait ran out (the kernel then returned early instead of spinning).  Reads and clears it;
+ * synchronises the device.  Not in the reference (its kernels have no device-side waits). */
+int glm53f_kda_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLM53F_KDA_H */

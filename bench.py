@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the KDA recurrent core on B200: batched single-token decode (state GB/s against the HBM roofline).
+
+One step = the decode of one token for every slot across all 34 KDA layers of the model: 34 launches of
+glm53f_kda_core_decode_batch, one per layer, each over 16 slots x 64 heads with its own bf16 state
+(16 x 2 MiB read + 16 x 2 MiB written per layer).  The 34 layers' states are distinct buffers (1.06 GiB in all),
+so every launch streams its states from HBM: the working set is ~8x the 126 MB L2.
+
+  value     state GB/s with the token inputs already resident in HBM (CUDA events around K steps)
+  e2e       the same metric through the host-facing API: each step copies its token inputs from pinned host memory,
+            runs the 34 launches and reads the 34 layers' outputs back
+  roofline  algorithmic state bytes per launch / mean launch time, against the measured HBM copy bandwidth
+  cpu_baseline   the CPU oracle (the reference's recurrence restated in C++) on all host cores, on a bounded sample
+
+`--impl reference` times the reference's CPU formulation instead (the oracle port: the reference is Rust and no
+Rust toolchain exists on this machine) and prints the same line with "impl": "reference".
+With torchrun (N > 1) every rank decodes its own 16 slots (slots are independent units: no collective on the data
+path); the time is the maximum over ranks and `value` the whole job's.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HEADS, LAYERS, SLOTS, DK = 64, 34, 16, 128
+STATE_ELEMS = HEADS * DK * DK                        # one slot, one layer
+STATE_BYTES_PER_LAUNCH = 2 * SLOTS * STATE_ELEMS * 2  # bf16 read + write = 64 MiB
+TOKEN_IN_BYTES = HEADS * DK * (2 + 2 + 2 + 4) + HEADS * 4  # q, k, v bf16 + g f32 + beta f32 per token
+TOKEN_OUT_BYTES = HEADS * DK * 2
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised
+# under profiles/ (None until a capture exists).
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def oracle_module():
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import kda_oracle
+
+    kda_oracle.build()
+    return kda_oracle
+
+
+def cpu_decode_gbs(seconds: float, layers_sample: int = 2):
+    """The CPU oracle's decode (kernel-order recurrence, bf16-rounded states) on every host core: state GB/s counted
+    as for the GPU (2 bytes read + 2 written per state element)."""
+    import numpy as np
+
+    o = oracle_module()
+    pkg = importlib.import_module("glm53f-afd_b200")
+    cores = os.cpu_count() or 1
+    toks = [pkg.synth.tokens(1, l, SLOTS, HEADS) for l in range(layers_sample)]
+    rng = np.random.default_rng(1)
+    states = [o.bf16_round_np((rng.standard_normal(SLOTS * STATE_ELEMS) * 0.05).astype(np.float32)) for _ in range(layers_sample)]
+    cu = np.arange(SLOTS + 1, dtype=np.int32)
+    offs = np.arange(SLOTS, dtype=np.int64) * STATE_ELEMS
+    lib = o.lib()
+    f32p, u16p = C.POINTER(C.c_float), C.POINTER(C.c_uint16)
+    args = []
+    for l in range(layers_sample):
+        q, k, v, g, b = toks[l]
+        y = np.zeros(SLOTS * HEADS * DK, np.float32)
+        args.append((q, k, v, g, b, states[l], y))
+    steps, t0 = 0, time.perf_counter()
+    while True:
+        for q, k, v, g, b, s, y in args:
+            lib.kdao_core_step_batch(C.c_int(HEADS), C.c_int(SLOTS), cu.ctypes.data_as(C.POINTER(C.c_int32)),
+                                     q.ctypes.data_as(u16p), k.ctypes.data_as(u16p), v.ctypes.data_as(u16p),
+                                     g.ctypes.data_as(f32p), b.ctypes.data_as(f32p), s.ctypes.data_as(f32p),
+                                     offs.ctypes.data_as(C.POINTER(C.c_int64)), C.c_int(1), C.c_int(0), C.c_int(cores),
+                                     y.ctypes.data_as(f32p), None, None, None, None)
+        steps += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    gbs = steps * layers_sample * STATE_BYTES_PER_LAUNCH / dt / 1e9
+    return gbs, cores, f"{steps} steps x {layers_sample} of 34 layers x {SLOTS} slots x {HEADS} heads in {dt:.1f} s"
+
+
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    per_step = max(1.0, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_decode_gbs(min(per_step, 1.0))
+    vals = []
+    for _ in range(args.steps):
+        v, cores, sample = cpu_decode_gbs(per_step)
+        vals.append(v)
+    value = sum(vals) / len(vals)
+    ms = STATE_BYTES_PER_LAUNCH * LAYERS / (value * 1e9) * 1e3
+    line = {
+        "impl": "reference", "metric": "KDA decode state GB/s (16 slots x 34 layers, bf16 states)", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config 1: batched single-token decode, 16 slots, H=64, d=128, 34 layers, bf16-stored states"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's CPU path is Rust (no toolchain here): this is the C++ port in oracle/, all host threads",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=8.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import numpy as np
+    import torch
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg = importlib.import_module("glm53f-afd_b200")
+    core = importlib.import_module("glm53f-afd_b200.core")
+    ffi = pkg.ffi
+    lib = ffi.load()  # raises when the CUDA library is missing: there is no fallback
+    layers = args.layers
+
+    # ---- inputs: host-generated tokens (seeded, exact distributions), device-generated carried states N(0, 0.05)
+    gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 1 + rank)
+    arena = (torch.randn(layers * SLOTS * STATE_ELEMS, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    host = []
+    for l in range(layers):
+        q, k, v, g, b = pkg.synth.tokens(1, l + 1000 * rank, SLOTS, HEADS)
+        host.append([torch.from_numpy(x.view(np.int16) if x.dtype == np.uint16 else x).pin_memory() for x in (q, k, v, g, b)])
+    dev = [[t.cuda() for t in ts] for ts in host]
+    outs = [torch.zeros(SLOTS * HEADS * DK, dtype=torch.int16, device="cuda") for _ in range(layers)]
+    host_outs = [torch.zeros(SLOTS * HEADS * DK, dtype=torch.int16).pin_memory() for _ in range(layers)]
+    cu = torch.arange(SLOTS + 1, dtype=torch.int32, device="cuda")
+    offs = torch.arange(SLOTS, dtype=torch.int64, device="cuda") * STATE_ELEMS
+    # one checked launch, then raw calls in the timed loops (as the reference's own bench does)
+    core.decode_batch(HEADS, SLOTS, cu, *dev[0], arena[:SLOTS * STATE_ELEMS], offs, out=outs[0])
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    launches = 0
+
+    def step(inputs):
+        nonlocal launches
+        for l in range(layers):
+            q, k, v, g, b = inputs[l]
+            st = C.c_void_p(arena.data_ptr() + 2 * l * SLOTS * STATE_ELEMS)
+            rc = lib.glm53f_kda_core_decode_batch(HEADS, SLOTS, P(cu), P(q), P(k), P(v), P(g), P(b), st, st, P(offs), 1, 0, None,
+                                                  None, 1e-5, P(outs[l]), stream)
+            if rc != 0:
+                raise RuntimeError(f"decode launch failed: {rc}")
+            launches += 1
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    # ---- device-resident timing
+    for _ in range(max(3, args.warmup)):
+        step(dev)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches = 0
+    ms = timed(lambda: step(dev), args.steps)
+    timed_launches = launches
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    per_rank_bytes = layers * STATE_BYTES_PER_LAUNCH
+    value = world * per_rank_bytes / (ms_per_step * 1e-3) / 1e9
+    launch_s = ms * 1e-3 / (args.steps * layers)
+    achieved = STATE_BYTES_PER_LAUNCH / launch_s / 1e9
+    peak, peak_kind = peaks()
+
+    # ---- end to end: pinned host inputs in, outputs back, every step
+    def e2e_step():
+        staged = []
+        for l in range(layers):
+            staged.append([t.cuda(non_blocking=True) for t in host[l]])
+        step(staged)
+        for l in range(layers):
+            host_outs[l].copy_(outs[l], non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_value = world * per_rank_bytes / (e2e_ms * 1e-3) / 1e9
+    assert core.device_status() == 0
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    line = {
+        "metric": "KDA decode state GB/s (16 slots x 34 layers, bf16 states)",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config 1: batched single-token decode, 16 slots per GPU, H=64, d=128, 34 layers, bf16-stored states",
+                   "layers": layers, "l2": "inputs larger than L2: 1.06 GiB of states stream per step", "sharding": "by slot, no collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_kind, "frac_of_nominal_8tbs": achieved / 8000.0,
+                     "algorithmic_bytes_per_launch": STATE_BYTES_PER_LAUNCH, "kernel": "recurrent_kernel<bf16, core>"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": layers * SLOTS * TOKEN_IN_BYTES,
+                "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES},
+        "gpu_launches": timed_launches,
+        "clocks": clocks,
+    }
+    if not args.no_cpu:
+        v, cores, sample = cpu_decode_gbs(args.cpu_seconds)
+        line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

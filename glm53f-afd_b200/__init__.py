@@ -5,7 +5,7 @@
 `synth`   seeded synthetic inputs of the benchmark configurations;
 `build()` compiles csrc/ into libglm53f_kda.so (nvcc, sm_100a).
 """
-from . import _build, ffi  # noqa: F401
+from . import _build, ffi, synth  # noqa: F401
 
 DK = DV = 128
 TAPS = 4

@@ -596,3 +596,55 @@ void kdao_core_forward(int heads, int h0, int h1, int64_t t, const uint16_t* q_b
         });
     for (auto& th : pool) th.join();
 }
+
+// ---------------------------------------------------------------- src/cpu.rs:436-453 on post-conv inputs
+void kdao_core_step_batch(int heads, int batch, const int32_t* cu_rows, const uint16_t* q_bits, const uint16_t* k_bits,
+                          const uint16_t* v_bits, const float* g, const float* beta, float* states,
+                          const int64_t* state_off, int bf16_state, int l2norm, int threads, float* y, float* k_save,
+                          float* v_save, float* g_save, float* b_save) {
+    const size_t per = (size_t)DV * DK;
+    const int units = heads * batch;
+    auto run_unit = [&](int u) {
+        const int b = u / heads, h = u % heads;
+        float* s = states + state_off[b] + (size_t)h * per;
+        for (int r = cu_rows[b]; r < cu_rows[b + 1]; ++r) {
+            const size_t at = ((size_t)r * heads + h) * DK;
+            float q[DK], k[DK], v[DV], gm[DK], yr[DV];
+            for (int i = 0; i < DK; ++i) {
+                q[i] = kdao_bf16_to_f32(q_bits[at + i]);
+                k[i] = kdao_bf16_to_f32(k_bits[at + i]);
+                v[i] = kdao_bf16_to_f32(v_bits[at + i]);
+                gm[i] = std::exp(g[at + i]);
+            }
+            if (l2norm) {
+                float qn[DK], kn[DK];
+                kdao_l2norm(q, 1, kdao_q_scale(), qn);
+                kdao_l2norm(k, 0, 0.0f, kn);
+                std::memcpy(q, qn, sizeof q);
+                std::memcpy(k, kn, sizeof k);
+            }
+            const float bt = beta[(size_t)r * heads + h];
+            kdao_update(s, k, gm, v, bt);
+            kdao_read_out(s, q, yr);
+            if (y)
+                for (int i = 0; i < DV; ++i) y[at + i] = kdao_bf16_round(yr[i]);
+            if (bf16_state)
+                for (size_t i = 0; i < per; ++i) s[i] = kdao_bf16_round(s[i]);
+            if (k_save) std::memcpy(k_save + at, k, sizeof k);
+            if (v_save) std::memcpy(v_save + at, v, sizeof v);
+            if (g_save) std::memcpy(g_save + at, gm, sizeof gm);
+            if (b_save) b_save[(size_t)r * heads + h] = bt;
+        }
+    };
+    const int nthreads = std::max(1, std::min(threads, units));
+    if (nthreads == 1) {
+        for (int u = 0; u < units; ++u) run_unit(u);
+        return;
+    }
+    std::vector<std::thread> pool;
+    for (int w = 0; w < nthreads; ++w)
+        pool.emplace_back([&, w]() {
+            for (int u = w; u < units; u += nthreads) run_unit(u);
+        });
+    for (auto& th : pool) th.join();
+}

@@ -110,6 +110,17 @@ void kdao_core_forward(int heads, int h0, int h1, int64_t t, const uint16_t* q_b
                        const uint16_t* v_bits, const float* g, const float* beta, float* state, int form,
                        int chunk, int bf16_state, int threads, float* y);
 
+/* The recurrent core in the KERNELS' operation order (src/cpu.rs:449-453 without the conv and the gates' own
+ * arithmetic): for request b and each of its rows [cu_rows[b], cu_rows[b+1]): decay multipliers exp(g), optional
+ * kernel-order L2 norms of q and k (src/cpu.rs:304-315), kdao_update, kdao_read_out rounded to bf16, then the
+ * state rounded to bf16 when bf16_state.  State b lives at states + state_off[b], kernel layout, f32 values
+ * (bf16-exact for bf16 states), updated in place.  y: bf16-rounded read-out [rows][H][128].  Optional saves as the
+ * kernels write them.  Units (request, head) are spread over `threads` host threads. */
+void kdao_core_step_batch(int heads, int batch, const int32_t* cu_rows, const uint16_t* q_bits, const uint16_t* k_bits,
+                          const uint16_t* v_bits, const float* g, const float* beta, float* states,
+                          const int64_t* state_off, int bf16_state, int l2norm, int threads, float* y, float* k_save,
+                          float* v_save, float* g_save, float* b_save);
+
 #ifdef __cplusplus
 }
 #endif

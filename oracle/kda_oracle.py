@@ -374,3 +374,32 @@ def core_forward(heads, q_bits, k_bits, v_bits, g, beta_, state_, form="recurren
                             _p(g), _p(beta_), _p(s), C.c_int(1 if form == "chunked" else 0), C.c_int(chunk),
                             C.c_int(int(bf16_state)), C.c_int(threads), _p(y) if want_y else None)
     return y, s
+
+
+def core_step_batch(heads, cu_rows, q_bits, k_bits, v_bits, g, beta_, states, state_off, bf16_state=False, l2norm=False,
+                    threads=1, want_saves=False):
+    """The recurrent core in the kernels' operation order; returns (y, states after[, saves])."""
+    cu = np.ascontiguousarray(cu_rows, dtype=np.int32)
+    so = np.ascontiguousarray(state_off, dtype=np.int64)
+    q_bits = np.ascontiguousarray(q_bits, dtype=np.uint16)
+    k_bits = np.ascontiguousarray(k_bits, dtype=np.uint16)
+    v_bits = np.ascontiguousarray(v_bits, dtype=np.uint16)
+    g, beta_ = _f(g), _f(beta_)
+    s = _f(states).copy()
+    rows = int(cu[-1])
+    y = np.zeros(rows * heads * DV, np.float32)
+    sv = ChainOut()
+    sv.heads, sv.rows = heads, rows
+    if want_saves:
+        sv.k = np.zeros(rows * heads * DK, np.float32)
+        sv.v = np.zeros(rows * heads * DV, np.float32)
+        sv.g = np.zeros(rows * heads * DK, np.float32)
+        sv.beta = np.zeros(rows * heads, np.float32)
+    i32p, i64p = C.POINTER(C.c_int32), C.POINTER(C.c_int64)
+    lib().kdao_core_step_batch(C.c_int(heads), C.c_int(cu.size - 1), cu.ctypes.data_as(i32p),
+                               q_bits.ctypes.data_as(_u16p), k_bits.ctypes.data_as(_u16p), v_bits.ctypes.data_as(_u16p),
+                               _p(g), _p(beta_), _p(s), so.ctypes.data_as(i64p), C.c_int(int(bf16_state)),
+                               C.c_int(int(l2norm)), C.c_int(threads), _p(y),
+                               _p(sv.k) if want_saves else None, _p(sv.v) if want_saves else None,
+                               _p(sv.g) if want_saves else None, _p(sv.beta) if want_saves else None)
+    return (y, s, sv) if want_saves else (y, s)

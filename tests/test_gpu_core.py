@@ -1,0 +1,245 @@
+"""GPU parity of the core entry points (post-conv inputs) on scaled-down copies of the benchmark configurations.
+
+Tolerances are the task's: bf16 outputs within max-abs 2e-2 and rel-L2 5e-3 of the FP32 oracle, FP32 final state
+within rel-L2 1e-3; the rollback identities (verify + commit(k) == k single-row decode steps) are bit for bit.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+DK = DV = 128
+OUT_MAX_ABS, OUT_REL_L2, STATE_REL_L2 = 2e-2, 5e-3, 1e-3
+
+
+@pytest.fixture(scope="module")
+def G():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import kda_gpu
+
+    kda_gpu.product()
+    return kda_gpu
+
+
+@pytest.fixture(scope="module")
+def core(G):
+    import importlib
+
+    return importlib.import_module("glm53f-afd_b200.core")
+
+
+def upload_tokens(G, tok):
+    q, k, v, g, beta = tok
+    return G.dev_bits(q), G.dev_bits(k), G.dev_bits(v), G.dev_f32(g), G.dev_f32(beta)
+
+
+def run_decode(G, core, heads, cu, tok, states, offs, bf16, saves=False, state_out="in_place", flags=0, gate=None, norm_w=None):
+    rows = int(cu[-1])
+    dq, dk, dv, dg, db = upload_tokens(G, tok)
+    d_state = G.dev_bf16(states) if bf16 else G.dev_f32(states)
+    d_out = torch.full((rows * heads * DV + 32,), -1, dtype=torch.int16, device="cuda")
+    d_cu, d_off = G.dev_i32(cu), G.dev_i64(offs)
+    sv = None
+    if saves:
+        sv = (torch.zeros(rows * heads * DK, device="cuda"), torch.zeros(rows * heads * DV, dtype=torch.int16, device="cuda"),
+              torch.zeros(rows * heads * DK, device="cuda"), torch.zeros(rows * heads, device="cuda"))
+    d_gate = G.dev_bf16(gate) if gate is not None else None
+    d_nw = G.dev_bf16(norm_w) if norm_w is not None else None
+    core.decode_batch(heads, rows, d_cu, dq, dk, dv, dg, db, d_state, d_off, state_out=state_out, flags=flags, gate=d_gate,
+                      norm_w=d_nw, out=d_out, saves=sv)
+    G.check_status()
+    out = G.host_bf16(d_out)
+    assert (d_out[rows * heads * DV:].cpu().numpy() == -1).all()
+    st = G.host_bf16(d_state) if bf16 else G.host_f32(d_state)
+    return out[:rows * heads * DV], st, sv
+
+
+# Configuration 1 scaled down: one token per slot, each slot with its own carried state.
+@pytest.mark.parametrize("bf16", [True, False])
+def test_decode_matches_the_oracle(G, core, oracle, pkg, bf16):
+    o, synth = oracle, pkg.synth
+    heads, slots = 64, 4
+    tok = synth.tokens(1, 0, slots, heads)
+    per = heads * DV * DK
+    states = np.concatenate([synth.state(1, 0, s, heads) for s in range(slots)])
+    if bf16:
+        states = o.bf16_round_np(states)
+    cu = np.arange(slots + 1)
+    order = [3, 1, 0, 2]  # slots scattered in the arena
+    offs = [s * per for s in order]
+    out, st, _ = run_decode(G, core, heads, cu, tok, states, offs, bf16)
+    # kernel-order oracle: everything but exp() has the kernel's bits, so the agreement is tight
+    y, s_ref = o.core_step_batch(heads, cu, *tok, states, offs, bf16_state=bf16, threads=8)
+    assert G.max_abs(out, y) / G.max_abs(y) <= 1.0 / 256.0
+    assert G.ulps(out, y)[1] * 200 <= y.size
+    assert G.rel_l2(st, s_ref) <= (4e-3 if bf16 else 1e-6)
+    # the task's bound against the FP32 recurrence of the reference's literal formulation
+    for slot in range(slots):
+        sl = slice(offs[slot], offs[slot] + per)
+        q, k, v, g, beta = tok
+        row = lambda a, w: a.reshape(slots, heads * w)[slot]
+        y_lit, s_lit = o.core_forward(heads, row(q, DK), row(k, DK), row(v, DV), row(g, DK), beta.reshape(slots, heads)[slot],
+                                      states[sl], form="recurrent", bf16_state=bf16, threads=8)
+        got = out.reshape(slots, heads * DV)[slot]
+        assert G.max_abs(got, y_lit) <= OUT_MAX_ABS
+        assert G.rel_l2(got, y_lit) <= OUT_REL_L2
+        assert G.rel_l2(st[sl], s_lit) <= (4e-3 if bf16 else STATE_REL_L2)
+
+
+def test_decode_with_fused_norms_and_output_gate(G, core, oracle, pkg):
+    o = oracle
+    heads, slots = 3, 2
+    rng = o.Rng(77)
+    n = slots * heads * DK
+    q = o.bf16_bits(rng.fill_bf16(n, -1, 1))
+    k = o.bf16_bits(rng.fill_bf16(n, -1, 1))
+    v = o.bf16_bits(rng.fill_bf16(n, -1, 1))
+    g = np.log(1.0 / (1.0 + np.exp(-rng.fill(n, 0, 5)))).astype(np.float32)
+    beta = rng.fill(slots * heads, 0, 1)
+    gate = rng.fill_bf16(n, -4, 4)
+    norm_w = rng.fill_bf16(DV, 0.25, 1.75)
+    per = heads * DV * DK
+    states = rng.fill(slots * per, -0.5, 0.5)
+    cu, offs = [0, 1, 2], [0, per]
+    out, st, _ = run_decode(G, core, heads, cu, (q, k, v, g, beta), states, offs, False, flags=core.L2NORM, gate=gate, norm_w=norm_w)
+    y, s_ref = o.core_step_batch(heads, cu, q, k, v, g, beta, states, offs, l2norm=True)
+    want = np.concatenate([o.gated_rmsnorm(y[i * DV:(i + 1) * DV], norm_w, gate[i * DV:(i + 1) * DV], 1e-5) for i in range(slots * heads)])
+    assert G.max_abs(out, want) / G.max_abs(want) <= 1.0 / 128.0
+    assert G.rel_l2(st, s_ref) <= 1e-6
+
+
+# Configuration 4 scaled down: verify a window per slot, roll back to a drawn prefix, for several layers at once.
+@pytest.mark.parametrize("bf16", [True, False])
+def test_verify_then_commit_equals_serial_decode_bitwise(G, core, oracle, pkg, bf16):
+    o, synth = oracle, pkg.synth
+    heads, slots, window, layers = 8, 5, 16, 3
+    keeps = [0, 16, 7, 1, 11]
+    per = heads * DV * DK
+    rows = slots * window
+    cu = np.arange(slots + 1) * window
+    offs = [s * per for s in range(slots)]
+    toks = [synth.tokens(4, l, rows, heads) for l in range(layers)]
+    states = [np.concatenate([synth.state(4, l, s, heads) for s in range(slots)]) for l in range(layers)]
+    if bf16:
+        states = [o.bf16_round_np(s) for s in states]
+    arena = np.concatenate(states)  # [layers][slots][H][128][128]
+    d_arena = G.dev_bf16(arena) if bf16 else G.dev_f32(arena)
+    d_cu, d_off, d_keep = G.dev_i32(cu), G.dev_i64(offs), G.dev_i32(keeps)
+    nkv = rows * heads * DK
+    ks = torch.zeros(layers * nkv, device="cuda")
+    vs = torch.zeros(layers * nkv, dtype=torch.int16, device="cuda")
+    gs = torch.zeros(layers * nkv, device="cuda")
+    bs = torch.zeros(layers * rows * heads, device="cuda")
+    outs = []
+    for l in range(layers):
+        dq, dk, dv, dg, db = upload_tokens(G, toks[l])
+        d_out = torch.zeros(rows * heads * DV, dtype=torch.int16, device="cuda")
+        sl = d_arena[l * slots * per:(l + 1) * slots * per]
+        core.decode_batch(heads, rows, d_cu, dq, dk, dv, dg, db, sl, d_off, state_out=None, out=d_out,
+                          saves=(ks[l * nkv:], vs[l * nkv:], gs[l * nkv:], bs[l * rows * heads:]))
+        outs.append(d_out)
+    G.check_status()
+    got = G.host_bf16(d_arena) if bf16 else G.host_f32(d_arena)
+    assert np.array_equal(G.bits(got), G.bits(arena)), "verify must not touch the states"
+    core.commit_batch(heads, layers, d_cu, d_keep, d_arena, slots * per, d_off, (ks, vs, gs, bs), nkv, rows * heads)
+    G.check_status()
+    committed = G.host_bf16(d_arena) if bf16 else G.host_f32(d_arena)
+    # k serial single-row decode steps per slot
+    for l in range(layers):
+        q, k, v, g, beta = toks[l]
+        cur = states[l].copy()
+        y_serial = np.zeros((slots, window, heads * DV), np.float32)
+        for step in range(window):
+            live = [s for s in range(slots) if keeps[s] > step]
+            if not live:
+                break
+            idx = [s * window + step for s in live]
+            pick = lambda a, w: np.ascontiguousarray(a.reshape(rows, heads * w)[idx]).reshape(-1)
+            tok = (pick(q, DK), pick(k, DK), pick(v, DV), pick(g, DK), np.ascontiguousarray(beta.reshape(rows, heads)[idx]).reshape(-1))
+            out, cur, _ = run_decode(G, core, heads, np.arange(len(live) + 1), tok, cur, [offs[s] for s in live], bf16)
+            for j, s in enumerate(live):
+                y_serial[s, step] = out.reshape(len(live), heads * DV)[j]
+        assert np.array_equal(G.bits(committed[l * slots * per:(l + 1) * slots * per]), G.bits(cur)), l
+        ver = G.host_bf16(outs[l]).reshape(slots, window, heads * DV)
+        for s in range(slots):
+            assert np.array_equal(G.bits(ver[s, :keeps[s]]), G.bits(y_serial[s, :keeps[s]])), (l, s)
+        # and the oracle's bit-level replay of the kernel's saves
+        sv = o.ChainOut()
+        sv.heads, sv.rows = heads, rows
+        sv.k, sv.g = G.host_f32(ks[l * nkv:(l + 1) * nkv]), G.host_f32(gs[l * nkv:(l + 1) * nkv])
+        sv.v, sv.beta = G.host_bf16(vs[l * nkv:(l + 1) * nkv]), G.host_f32(bs[l * rows * heads:(l + 1) * rows * heads])
+        for s in (1, 2):
+            one = o.ChainOut()
+            one.heads, one.rows = heads, window
+            pickr = lambda a, w: a.reshape(rows, heads * w)[s * window:(s + 1) * window].reshape(-1)
+            one.k, one.g, one.v, one.beta = pickr(sv.k, DK), pickr(sv.g, DK), pickr(sv.v, DV), pickr(sv.beta, 1)
+            want = o.replay(states[l][offs[s]:offs[s] + per], one, keeps[s], bf16_state=bf16)
+            assert np.array_equal(G.bits(committed[l * slots * per + offs[s]:l * slots * per + offs[s] + per]), G.bits(want)), (l, s)
+
+
+def prefill_case(G, core, oracle, synth, config, heads, lens, carried, bf16=False):
+    o = oracle
+    rows = sum(lens)
+    tok = synth.tokens(config, 0, rows, heads)
+    per = heads * DV * DK
+    states = np.concatenate([synth.state(config, 0, i, heads) if carried[i] else np.zeros(per, np.float32) for i in range(len(lens))])
+    if bf16:
+        states = o.bf16_round_np(states)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    offs = [i * per for i in range(len(lens))]
+    dq, dk, dv, dg, db = upload_tokens(G, tok)
+    d_state = G.dev_bf16(states) if bf16 else G.dev_f32(states)
+    d_out = torch.full((rows * heads * DV + 32,), -1, dtype=torch.int16, device="cuda")
+    d_cu, d_off = G.dev_i32(cu), G.dev_i64(offs)
+    core.prefill_varlen(heads, rows, d_cu, max(lens), dq, dk, dv, dg, db, d_state, d_off, out=d_out)
+    G.check_status()
+    out = G.host_bf16(d_out)[:rows * heads * DV].reshape(rows, heads * DV)
+    st = G.host_bf16(d_state) if bf16 else G.host_f32(d_state)
+    q, k, v, g, beta = tok
+    for i, n in enumerate(lens):
+        r0 = cu[i]
+        part = lambda a, w: a.reshape(rows, heads * w)[r0:r0 + n].reshape(-1)
+        args = (heads, part(q, DK), part(k, DK), part(v, DV), part(g, DK), beta.reshape(rows, heads)[r0:r0 + n].reshape(-1),
+                states[offs[i]:offs[i] + per])
+        y_rec, s_rec = o.core_forward(*args, form="recurrent", threads=8)
+        y_chk, s_chk = o.core_forward(*args, form="chunked", chunk=64, threads=8)
+        # the two formulations of the reference agree (its own bound), so either is the oracle
+        assert G.max_abs(y_chk, y_rec) / max(G.max_abs(y_rec), 1e-30) < 2e-5 and G.max_abs(s_chk, s_rec) / G.max_abs(s_rec) < 2e-5
+        got = out[r0:r0 + n].reshape(-1)
+        assert G.max_abs(got, y_rec) <= OUT_MAX_ABS, (i, n)
+        assert G.rel_l2(got, y_rec) <= OUT_REL_L2, (i, n)
+        assert G.rel_l2(st[offs[i]:offs[i] + per], s_rec) <= (8e-3 if bf16 else STATE_REL_L2), (i, n)
+    return out, st
+
+
+# Configuration 0 scaled down (one sequence from a zero state) and the ragged edge cases of the chunking.
+@pytest.mark.parametrize("t", [1, 7, 63, 64, 65, 150, 512])
+def test_prefill_single_sequence(G, core, oracle, pkg, t):
+    prefill_case(G, core, oracle, pkg.synth, 0, 4, [t], [False])
+
+
+# Configuration 2 scaled down: packed variable-length sequences, some from a carried-over state.
+def test_prefill_varlen_packed(G, core, oracle, pkg):
+    lens = [300, 64, 1, 129, 77]
+    prefill_case(G, core, oracle, pkg.synth, 2, 8, lens, [True, False, True, False, True])
+
+
+def test_core_rejections(G, core, pkg):
+    heads = 2
+    z16 = torch.zeros(heads * DK * 4, dtype=torch.int16, device="cuda")
+    zf = torch.zeros(heads * DK * 4, device="cuda")
+    st = torch.zeros(heads * DV * DK, device="cuda")
+    cu, off = G.dev_i32([0, 1]), G.dev_i64([0])
+    with pytest.raises(core.Invalid):
+        core.decode_batch(heads, 1, cu, z16, z16, z16, zf, zf, st, off, out=None)
+    with pytest.raises(core.Invalid):
+        core.decode_batch(heads, 1, cu, z16, z16, z16, zf, zf, st, off, out=z16, gate=z16, norm_w=None)
+    with pytest.raises(core.Invalid):
+        core.decode_batch(0, 1, cu, z16, z16, z16, zf, zf, st, off, out=z16)
+    with pytest.raises(core.Invalid):
+        core.decode_batch(heads, 1, cu, z16, z16, z16, zf, zf, st, off, out=z16, flags=8)
+    with pytest.raises(core.Invalid):
+        core.prefill_varlen(heads, 1, cu, 1, z16, z16, z16, zf, zf, st, off, out=z16, state_out=None)
+    assert core.device_status() == 0

@@ -49,6 +49,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware until the phase completes or the hint runs
+// out, instead of burning issue slots (and shared-memory bandwidth) in a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -76,8 +89,8 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
     uint64_t t0 = global_timer_ns();
     uint32_t seen = *ctx.progress;
     for (;;) {
-        for (int i = 0; i < 256; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
             if (*ctx.abort) return false;
         }
         const uint32_t now_p = *ctx.progress;

@@ -5,7 +5,7 @@
 //
 //   mover (1 warp)      bulk-copies (cp.async.bulk) each unit's 128x128 state and each row's raw inputs from global
 //                       memory into shared-memory rings, several units ahead of the arithmetic;
-//   prologue (4 warps)  turns a row's raw inputs into q, k, v, the decay multipliers, beta and sigmoid(gate)
+//   prologue (2 warps)  turns a row's raw inputs into q, k, v, the decay multipliers, beta and sigmoid(gate)
 //                       (short conv + SiLU, L2 norms, gates for the layer entry points; exp(g) for the core ones);
 //   recurrence (16 warps) keeps the unit's state in registers across its rows: warp w owns value rows 8w..8w+7,
 //                       lane l key columns 4l..4l+3; per row the delta rule and the read-out; afterwards each warp
@@ -53,7 +53,7 @@ namespace {
 
 enum Mode : int { kLayer = 0, kCore = 1, kReplay = 2 };
 
-constexpr int kRecWarps = 16, kProWarps = 4;
+constexpr int kRecWarps = 16, kProWarps = 2;
 constexpr int kRecThreads = kRecWarps * 32, kProThreads = kProWarps * 32;
 constexpr int kThreads = kRecThreads + kProThreads + 64;  // + epilogue warp + mover warp
 constexpr int kRowsPerLane = DV / kRecWarps;              // 8
@@ -97,6 +97,7 @@ struct Params {
     float* g_save;
     float* b_save;
     long long kv_stride, b_stride;
+    unsigned long long neg_zero2;  // two -0.0f: see mul2
 };
 
 // Raw-row slot layouts, byte offsets.
@@ -161,37 +162,77 @@ struct Smem {
 struct Unit {
     int b, h, layer, rows;
     long long row0;
-    long long s_elem;  // element offset of this head's state inside state_in / state_out
+    long long s_elem;    // element offset of this head's state inside state_in / state_out
+    long long conv_off;  // layer entry points: element offset of the request's conv window
+    float a_log;         // layer entry points: A_log of the head
 };
 
+// The units of this block, u = blockIdx.x, blockIdx.x + gridDim.x, ...: (request, head) with the head fastest, or
+// (request, layer, head) for the replay.  Indices advance by 32-bit arithmetic; the metadata of the next unit
+// (row range, state and window offsets: loads from global memory) is fetched while the current one is processed.
 template <int MODE>
-__device__ __forceinline__ Unit unit_of(const Params& p, long long u) {
-    Unit x;
-    if (MODE == kReplay) {
-        const long long per = (long long)p.layers * p.H;
-        x.b = (int)(u / per);
-        const int rem = (int)(u % per);
-        x.layer = rem / p.H;
-        x.h = rem % p.H;
-        x.row0 = p.cu_rows ? p.cu_rows[x.b] : 0;
-        x.rows = p.keep ? p.keep[x.b] : p.rows1;
-    } else {
-        x.b = (int)(u / p.H);
-        x.h = (int)(u % p.H);
-        x.layer = 0;
-        if (p.cu_rows) {
-            const int r0 = p.cu_rows[x.b];
+struct UnitIter {
+    unsigned long long u;
+    unsigned b, h, layer;
+    bool ok;
+    Unit nxt;
+
+    __device__ __forceinline__ explicit UnitIter(const Params& p) {
+        u = blockIdx.x;
+        ok = u < (unsigned long long)p.units;
+        const unsigned H = (unsigned)p.H, L = (unsigned)p.layers;
+        h = blockIdx.x % H;
+        const unsigned q = blockIdx.x / H;
+        layer = MODE == kReplay ? q % L : 0u;
+        b = MODE == kReplay ? q / L : q;
+        if (ok) nxt = fetch(p);
+    }
+    __device__ __forceinline__ Unit fetch(const Params& p) const {
+        Unit x;
+        x.b = (int)b;
+        x.h = (int)h;
+        x.layer = (int)layer;
+        if (MODE == kReplay) {
+            x.row0 = p.cu_rows ? p.cu_rows[b] : 0;
+            x.rows = p.keep ? p.keep[b] : p.rows1;
+        } else if (p.cu_rows) {
+            const int r0 = p.cu_rows[b];
             x.row0 = r0;
-            x.rows = p.cu_rows[x.b + 1] - r0;
+            x.rows = p.cu_rows[b + 1] - r0;
         } else {
             x.row0 = 0;
             x.rows = p.rows1;
         }
+        if (x.rows < 0) x.rows = 0;
+        x.s_elem = (long long)layer * p.state_stride + (p.state_off ? p.state_off[b] : 0) + (long long)h * DV * DK;
+        x.conv_off = 0;
+        x.a_log = 0.0f;
+        if (MODE == kLayer) {
+            x.conv_off = p.conv_off ? p.conv_off[b] : 0;
+            x.a_log = p.a_log[h];
+        }
+        return x;
     }
-    if (x.rows < 0) x.rows = 0;
-    x.s_elem = (long long)x.layer * p.state_stride + (p.state_off ? p.state_off[x.b] : 0) + (long long)x.h * DV * DK;
-    return x;
-}
+    __device__ __forceinline__ bool valid() const { return ok; }
+    // The current unit; advances to the next one and starts fetching its metadata.
+    __device__ __forceinline__ Unit take(const Params& p) {
+        const Unit cur = nxt;
+        u += gridDim.x;
+        ok = u < (unsigned long long)p.units;
+        const unsigned H = (unsigned)p.H;
+        const unsigned nh = h + gridDim.x, dq = nh / H;
+        h = nh - dq * H;
+        if (MODE == kReplay) {
+            const unsigned L = (unsigned)p.layers, nl = layer + dq, lq = nl / L;
+            layer = nl - lq * L;
+            b += lq;
+        } else {
+            b += dq;
+        }
+        if (ok) nxt = fetch(p);
+        return cur;
+    }
+};
 
 // Whether a unit without rows still has to move its state (out of place copy).
 __device__ __forceinline__ bool copies_state(const Params& p) { return p.state_out != nullptr && p.state_out != p.state_in; }
@@ -207,41 +248,101 @@ struct Ring {
     }
 };
 
+// ---- packed FP32 pairs -----------------------------------------------------------------------------------------
+// sm_100 has two-wide FP32 instructions (mul.f32x2, add.f32x2): each half is an IEEE round-to-nearest operation,
+// so a pair gives the bits of two scalar instructions for half the issue slots.  The recurrence is bound by
+// instruction issue, not by the FP32 pipe, so the state is held as pairs: pair jp of a lane holds value rows
+// 2jp and 2jp+1 of its warp at one key column.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+// The product of two pairs, each half rounded once.  It is written as fma(a, b, -0) with the -0 pair read from the
+// kernel's parameters: ptxas contracts a dependent mul.rn.f32x2 / add.rn.f32x2 pair into one FFMA2 even when
+// contraction is off (measured: 1-ulp differences against the scalar sequence), which would break the bitwise
+// contract; a product that comes out of an FMA with an addend the compiler cannot see through is left alone, and
+// x*y + (-0) is x*y for every x*y, signed zeros included.
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b, f32x2 nz) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(nz));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+constexpr int kPairs = kRowsPerLane / 2;  // 4 row pairs per lane
+
 // ---- state registers <-> shared memory -----------------------------------------------------------------------
 template <typename S>
-__device__ __forceinline__ void load_rows(const unsigned char* slot, int warp, int lane, float (&s)[kRowsPerLane][4]) {
-#pragma unroll
-    for (int j = 0; j < kRowsPerLane; ++j) {
-        const int row = warp * kRowsPerLane + j;
-        if constexpr (sizeof(S) == 4) {
-            const float4 x = *reinterpret_cast<const float4*>(slot + ((size_t)row * DK + lane * 4) * 4);
-            s[j][0] = x.x; s[j][1] = x.y; s[j][2] = x.z; s[j][3] = x.w;
-        } else {
-            const uint2 x = *reinterpret_cast<const uint2*>(slot + ((size_t)row * DK + lane * 4) * 2);
-            s[j][0] = __uint_as_float(x.x << 16);
-            s[j][1] = __uint_as_float(x.x & 0xffff0000u);
-            s[j][2] = __uint_as_float(x.y << 16);
-            s[j][3] = __uint_as_float(x.y & 0xffff0000u);
-        }
+__device__ __forceinline__ void load_row(const unsigned char* slot, int row, int lane, float (&x)[4]) {
+    if constexpr (sizeof(S) == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(slot + ((size_t)row * DK + lane * 4) * 4);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(slot + ((size_t)row * DK + lane * 4) * 2);
+        x[0] = __uint_as_float(v.x << 16);
+        x[1] = __uint_as_float(v.x & 0xffff0000u);
+        x[2] = __uint_as_float(v.y << 16);
+        x[3] = __uint_as_float(v.y & 0xffff0000u);
     }
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
 }
 
 template <typename S>
-__device__ __forceinline__ void store_rows(unsigned char* slot, int warp, int lane, const float (&s)[kRowsPerLane][4]) {
+__device__ __forceinline__ void load_rows(const unsigned char* slot, int warp, int lane, f32x2 (&s)[kPairs][4]) {
 #pragma unroll
-    for (int j = 0; j < kRowsPerLane; ++j) {
-        const int row = warp * kRowsPerLane + j;
-        if constexpr (sizeof(S) == 4) {
-            *reinterpret_cast<float4*>(slot + ((size_t)row * DK + lane * 4) * 4) = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
-        } else {
-            *reinterpret_cast<uint2*>(slot + ((size_t)row * DK + lane * 4) * 2) =
-                make_uint2(pack_bf16x2(s[j][0], s[j][1]), pack_bf16x2(s[j][2], s[j][3]));
-        }
+    for (int jp = 0; jp < kPairs; ++jp) {
+        float a[4], b[4];
+        load_row<S>(slot, warp * kRowsPerLane + 2 * jp, lane, a);
+        load_row<S>(slot, warp * kRowsPerLane + 2 * jp + 1, lane, b);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[jp][i] = pack2(a[i], b[i]);
     }
+}
+
+// Two floats rounded to bf16 (nearest even) in one instruction: lo in the low half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <typename S>
+__device__ __forceinline__ void store_row(unsigned char* slot, int row, int lane, const float (&x)[4]) {
+    if constexpr (sizeof(S) == 4) {
+        *reinterpret_cast<float4*>(slot + ((size_t)row * DK + lane * 4) * 4) = make_float4(x[0], x[1], x[2], x[3]);
+    } else {
+        *reinterpret_cast<uint2*>(slot + ((size_t)row * DK + lane * 4) * 2) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+    }
+}
+
+template <typename S>
+__device__ __forceinline__ void store_rows(unsigned char* slot, int warp, int lane, const f32x2 (&s)[kPairs][4]) {
+#pragma unroll
+    for (int jp = 0; jp < kPairs; ++jp) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) unpack2(s[jp][i], a[i], b[i]);
+        store_row<S>(slot, warp * kRowsPerLane + 2 * jp, lane, a);
+        store_row<S>(slot, warp * kRowsPerLane + 2 * jp + 1, lane, b);
+    }
+}
+
+// A bf16 state's rounding between two rows of a window: every element to bf16 and back.
+__device__ __forceinline__ void round_rows(f32x2 (&s)[kPairs][4]) {
+#pragma unroll
+    for (int jp = 0; jp < kPairs; ++jp)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float a, b;
+            unpack2(s[jp][i], a, b);
+            const uint32_t r = pack_bf16x2(a, b);
+            s[jp][i] = pack2(__uint_as_float(r << 16), __uint_as_float(r & 0xffff0000u));
+        }
 }
 
 // The 32-lane xor butterfly (offsets 16, 8, 4, 2, 1) of eight independent values per lane, evaluated as a
@@ -274,6 +375,20 @@ __device__ __forceinline__ float butterfly8(const float (&p)[kRowsPerLane], int 
     return x;
 }
 
+// Dot products of the lane's eight rows with a key-channel vector x (both halves of x2[i] hold x[i]): per row the
+// lane's four channels added in order from zero, then the butterfly.  Lane l gets row (l >> 2).
+__device__ __forceinline__ float rows_dot(const f32x2 (&s)[kPairs][4], const f32x2 (&x2)[4], int lane, f32x2 nz) {
+    float part[kRowsPerLane];
+#pragma unroll
+    for (int jp = 0; jp < kPairs; ++jp) {
+        f32x2 acc = pack2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc = add2(acc, mul2(s[jp][i], x2[i], nz));
+        unpack2(acc, part[2 * jp], part[2 * jp + 1]);
+    }
+    return butterfly8(part, lane);
+}
+
 // The plain butterfly for one value per lane (norms).
 __device__ __forceinline__ float butterfly1(float x) {
 #pragma unroll
@@ -282,26 +397,19 @@ __device__ __forceinline__ float butterfly1(float x) {
 }
 
 // One delta-rule step on a lane's 8 x 4 tile (reference kda.cu:38-53): decay, read with k, correct toward v.
-__device__ __forceinline__ void delta_rule(float (&s)[kRowsPerLane][4], const float (&kk)[4], const float (&gg)[4],
-                                           const float* vrow, int warp, int lane, float beta) {
-    float part[kRowsPerLane];
+__device__ __forceinline__ void delta_rule(f32x2 (&s)[kPairs][4], const f32x2 (&kk)[4], const f32x2 (&gg)[4],
+                                           const float* vrow, int warp, int lane, float beta, f32x2 nz) {
 #pragma unroll
-    for (int j = 0; j < kRowsPerLane; ++j) {
-        float kv = 0.0f;
+    for (int jp = 0; jp < kPairs; ++jp)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            s[j][i] = s[j][i] * gg[i];
-            kv = kv + s[j][i] * kk[i];
-        }
-        part[j] = kv;
-    }
-    const float kv = butterfly8(part, lane);
+        for (int i = 0; i < 4; ++i) s[jp][i] = mul2(s[jp][i], gg[i], nz);
+    const float kv = rows_dot(s, kk, lane, nz);
     const float mine = (vrow[warp * kRowsPerLane + (lane >> 2)] - kv) * beta;
 #pragma unroll
-    for (int j = 0; j < kRowsPerLane; ++j) {
-        const float delta = __shfl_sync(FULL, mine, 4 * j);
+    for (int jp = 0; jp < kPairs; ++jp) {
+        const f32x2 delta = pack2(__shfl_sync(FULL, mine, 8 * jp), __shfl_sync(FULL, mine, 8 * jp + 4));
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[j][i] = s[j][i] + kk[i] * delta;
+        for (int i = 0; i < 4; ++i) s[jp][i] = add2(s[jp][i], mul2(kk[i], delta, nz));
     }
 }
 
@@ -316,7 +424,7 @@ __device__ __forceinline__ void for_each_piece(const Params& p, const Unit& u, i
     const long long gr = u.row0 + r;
     if constexpr (MODE == kLayer) {
         const long long C = 3LL * p.H * DK;
-        const uint16_t* cs = p.conv + (p.conv_off ? p.conv_off[u.b] : 0);
+        const uint16_t* cs = p.conv + u.conv_off;
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
             const int at = r + tap;
@@ -358,8 +466,9 @@ __device__ void mover_role(const Params& p, unsigned char* smem, uint64_t* bars,
     uint64_t* raw_empty = raw_full + L::kRawSlots;
     Ring st, raw;
     const bool copy0 = copies_state(p);
-    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
-        const Unit un = unit_of<MODE>(p, u);
+    UnitIter<MODE> units(p);
+    while (units.valid()) {
+        const Unit un = units.take(p);
         if (un.rows == 0 && !copy0) continue;
         // The unit's state.
         if (!mbar_wait(&st_empty[st.idx], st.phase ^ 1u, ctx, kStatusWaitStateEmpty)) return;
@@ -447,11 +556,12 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
     const int warp = t >> 5, lane = t & 31;
     Ring raw, row;
     const bool copy0 = copies_state(p);
-    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
-        const Unit un = unit_of<MODE>(p, u);
+    UnitIter<MODE> units(p);
+    while (units.valid()) {
+        const Unit un = units.take(p);
         if (un.rows == 0 && !copy0) continue;
         float decay_rate = 0.0f;
-        if constexpr (MODE == kLayer) decay_rate = expf(p.a_log[un.h]);
+        if constexpr (MODE == kLayer) decay_rate = expf(un.a_log);
         for (int r = 0; r < un.rows; ++r) {
             if (!mbar_wait(&raw_full[raw.idx], raw.phase, ctx, kStatusWaitRawFull)) return;
             if (!mbar_wait(&row_empty[row.idx], row.phase ^ 1u, ctx, kStatusWaitRowEmpty)) return;
@@ -460,25 +570,27 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
             const long long gr = un.row0 + r;
             bool normalise = true;
             if constexpr (MODE == kLayer) {
-                // Short conv + SiLU, one bf16 rounding (kda.cu:129-142): thread t owns channel t of q, k and v.
+                // Short conv + SiLU, one bf16 rounding (kda.cu:129-142): channel c of q, k and v.
                 const uint16_t* x = reinterpret_cast<const uint16_t*>(in + RawLayer::X);
                 const uint16_t* w = reinterpret_cast<const uint16_t*>(in + RawLayer::W);
+                for (int c = t; c < DK; c += kProThreads) {
 #pragma unroll
-                for (int part = 0; part < 3; ++part) {
-                    float acc = 0.0f;
+                    for (int part = 0; part < 3; ++part) {
+                        float acc = 0.0f;
 #pragma unroll
-                    for (int tap = 0; tap < TAPS; ++tap)
-                        acc = acc + bf16_bits_to_f32(w[(part * DK + t) * TAPS + tap]) * bf16_bits_to_f32(x[(tap * 3 + part) * DK + t]);
-                    const float act = bf16_round(acc / (1.0f + expf(-acc)));
-                    if (part == 0) scratch[t] = act;
-                    else if (part == 1) scratch[DK + t] = act;
-                    else ck.v[t] = act;
+                        for (int tap = 0; tap < TAPS; ++tap)
+                            acc = acc + bf16_bits_to_f32(w[(part * DK + c) * TAPS + tap]) * bf16_bits_to_f32(x[(tap * 3 + part) * DK + c]);
+                        const float act = bf16_round(acc / (1.0f + expf(-acc)));
+                        if (part == 0) scratch[c] = act;
+                        else if (part == 1) scratch[DK + c] = act;
+                        else ck.v[c] = act;
+                    }
+                    // Decay multiplier (kda.cu:143-146) and sigmoid of the output gate (kda.cu:199-200).
+                    const float a = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::A)[c]) +
+                                    reinterpret_cast<const float*>(in + RawLayer::DTB)[c];
+                    ck.g[c] = expf(p.lower * sigmoidf_(decay_rate * a));
+                    ck.sg[c] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::GATE)[c]));
                 }
-                // Decay multiplier (kda.cu:143-146) and sigmoid of the output gate (kda.cu:199-200).
-                const float a = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::A)[t]) +
-                                reinterpret_cast<const float*>(in + RawLayer::DTB)[t];
-                ck.g[t] = expf(p.lower * sigmoidf_(decay_rate * a));
-                ck.sg[t] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawLayer::GATE)[t]));
                 if (t == 0) {
                     const uintptr_t addr = reinterpret_cast<uintptr_t>(p.P + gr * p.p_stride + p.b_off + un.h);
                     const uint16_t logit = *reinterpret_cast<const uint16_t*>(in + RawLayer::B + (addr & 15));
@@ -486,27 +598,31 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
                 }
             } else if constexpr (MODE == kCore) {
                 normalise = (p.flags & GLM53F_KDA_CORE_L2NORM) != 0;
-                const float qv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::Q)[t]);
-                const float kv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::K)[t]);
-                if (normalise) {
-                    scratch[t] = qv;
-                    scratch[DK + t] = kv;
-                } else {
-                    ck.q[t] = qv;
-                    ck.k[t] = kv;
+                for (int c = t; c < DK; c += kProThreads) {
+                    const float qv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::Q)[c]);
+                    const float kv = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::K)[c]);
+                    if (normalise) {
+                        scratch[c] = qv;
+                        scratch[DK + c] = kv;
+                    } else {
+                        ck.q[c] = qv;
+                        ck.k[c] = kv;
+                    }
+                    ck.v[c] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::V)[c]);
+                    ck.g[c] = expf(reinterpret_cast<const float*>(in + RawCore::GLOG)[c]);
+                    if (p.G) ck.sg[c] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::GATE)[c]));
                 }
-                ck.v[t] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::V)[t]);
-                ck.g[t] = expf(reinterpret_cast<const float*>(in + RawCore::GLOG)[t]);
-                if (p.G) ck.sg[t] = sigmoidf_(bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawCore::GATE)[t]));
                 if (t == 0) {
                     const uintptr_t addr = reinterpret_cast<uintptr_t>(p.beta + gr * p.H + un.h);
                     ck.beta = *reinterpret_cast<const float*>(in + RawCore::B + (addr & 15));
                 }
             } else {
                 normalise = false;
-                ck.k[t] = reinterpret_cast<const float*>(in + RawReplay::K)[t];
-                ck.g[t] = reinterpret_cast<const float*>(in + RawReplay::G)[t];
-                ck.v[t] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawReplay::V)[t]);
+                for (int c = t; c < DK; c += kProThreads) {
+                    ck.k[c] = reinterpret_cast<const float*>(in + RawReplay::K)[c];
+                    ck.g[c] = reinterpret_cast<const float*>(in + RawReplay::G)[c];
+                    ck.v[c] = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(in + RawReplay::V)[c]);
+                }
                 if (t == 0) {
                     const uintptr_t addr = reinterpret_cast<uintptr_t>(p.b_save + un.layer * p.b_stride + gr * p.H + un.h);
                     ck.beta = *reinterpret_cast<const float*>(in + RawReplay::B + (addr & 15));
@@ -518,8 +634,8 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
                 else if (warp == 1) l2norm_warp(scratch + DK, ck.k, lane, false);
                 named_bar_sync(2, kProThreads);  // scratch may be overwritten by the next row
             }
-            mbar_arrive(&row_full[row.idx]);   // 128 arrivals: every thread's writes are released
-            mbar_arrive(&raw_empty[raw.idx]);  // 128 arrivals
+            mbar_arrive(&row_full[row.idx]);   // one arrival per prologue thread: every thread's writes are released
+            mbar_arrive(&raw_empty[raw.idx]);
             raw.next(L::kRawSlots);
             row.next(L::kRowSlots);
         }
@@ -538,12 +654,13 @@ __device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* 
     Ring st, row;
     const bool copy0 = copies_state(p);
     int pending = -1;  // lane 0: a state slot whose bulk store may still be reading shared memory
-    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
-        const Unit un = unit_of<MODE>(p, u);
+    UnitIter<MODE> units(p);
+    while (units.valid()) {
+        const Unit un = units.take(p);
         if (un.rows == 0 && !copy0) continue;
         if (!mbar_wait(&st_full[st.idx], st.phase, ctx, kStatusWaitStateFull)) return;
         unsigned char* slot = smem + L::oState + st.idx * L::kStateBytes;
-        float s[kRowsPerLane][4];
+        f32x2 s[kPairs][4];
         if (un.rows > 0) load_rows<S>(slot, warp, lane, s);
         const bool writes = p.state_out != nullptr;
         if (!writes) {  // verify: the slot is free as soon as the registers hold the state
@@ -553,34 +670,24 @@ __device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* 
         for (int r = 0; r < un.rows; ++r) {
             if (!mbar_wait(&row_full[row.idx], row.phase, ctx, kStatusWaitRowFull)) return;
             Cooked& ck = *reinterpret_cast<Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
-            float kk[4], gg[4];
+            f32x2 kk[4], gg[4];
             {
                 const float4 k4 = *reinterpret_cast<const float4*>(&ck.k[lane * 4]);
                 const float4 g4 = *reinterpret_cast<const float4*>(&ck.g[lane * 4]);
-                kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
-                gg[0] = g4.x; gg[1] = g4.y; gg[2] = g4.z; gg[3] = g4.w;
+                kk[0] = pack2(k4.x, k4.x); kk[1] = pack2(k4.y, k4.y); kk[2] = pack2(k4.z, k4.z); kk[3] = pack2(k4.w, k4.w);
+                gg[0] = pack2(g4.x, g4.x); gg[1] = pack2(g4.y, g4.y); gg[2] = pack2(g4.z, g4.z); gg[3] = pack2(g4.w, g4.w);
             }
-            delta_rule(s, kk, gg, ck.v, warp, lane, ck.beta);
+            delta_rule(s, kk, gg, ck.v, warp, lane, ck.beta, p.neg_zero2);
             if constexpr (MODE != kReplay) {
                 // Read-out y = S q, rounded to bf16 (kda.cu:172-179).
                 const float4 q4 = *reinterpret_cast<const float4*>(&ck.q[lane * 4]);
-                const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
-                float part[kRowsPerLane];
-#pragma unroll
-                for (int j = 0; j < kRowsPerLane; ++j) {
-                    float o = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) o = o + s[j][i] * qq[i];
-                    part[j] = o;
-                }
-                const float o = butterfly8(part, lane);
+                const f32x2 qq[4] = {pack2(q4.x, q4.x), pack2(q4.y, q4.y), pack2(q4.z, q4.z), pack2(q4.w, q4.w)};
+                const float o = rows_dot(s, qq, lane, p.neg_zero2);
                 if ((lane & 3) == 0) ck.ys[warp * kRowsPerLane + (lane >> 2)] = bf16_round(o);
             }
-            if constexpr (sizeof(S) == 2) {  // a bf16 state is rounded after every row, after its read-out
-#pragma unroll
-                for (int j = 0; j < kRowsPerLane; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) s[j][i] = bf16_round(s[j][i]);
+            // A bf16 state is rounded after every row, after its read-out; after the last row the store rounds.
+            if constexpr (sizeof(S) == 2) {
+                if (r + 1 < un.rows || !writes) round_rows(s);
             }
             __syncwarp();
             if (lane == 0) {
@@ -640,8 +747,9 @@ __device__ void epilogue_role(const Params& p, unsigned char* smem, uint64_t* ba
     if (gated)
 #pragma unroll
         for (int i = 0; i < 4; ++i) nw[i] = bf16_bits_to_f32(p.norm_w[lane * 4 + i]);
-    for (long long u = blockIdx.x; u < p.units; u += gridDim.x) {
-        const Unit un = unit_of<MODE>(p, u);
+    UnitIter<MODE> units(p);
+    while (units.valid()) {
+        const Unit un = units.take(p);
         if (un.rows == 0 && !copy0) continue;
         for (int r = 0; r < un.rows; ++r) {
             if (!mbar_wait(&y_full[row.idx], row.phase, ctx, kStatusWaitYFull)) return;
@@ -751,7 +859,9 @@ int launch(const Params& p, cudaStream_t stream) {
     }
     const long long sms = sm_count();
     const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
-    recurrent_kernel<S, MODE><<<grid, kThreads, L::kBytes, stream>>>(p);
+    Params q = p;
+    q.neg_zero2 = 0x8000000080000000ull;
+    recurrent_kernel<S, MODE><<<grid, kThreads, L::kBytes, stream>>>(q);
     return (int)cudaGetLastError();
 }
 

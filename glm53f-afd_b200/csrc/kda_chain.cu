@@ -9,11 +9,11 @@
 //                       (short conv + SiLU, L2 norms, gates for the layer entry points; exp(g) for the core ones);
 //   recurrence (16 warps) keeps the unit's state in registers across its rows: warp w owns value rows 8w..8w+7,
 //                       lane l key columns 4l..4l+3; per row the delta rule and the read-out; afterwards each warp
-//                       bulk-stores its own 8 rows;
+//                       stores its own 8 rows, a whole contiguous row per instruction;
 //   epilogue (1 warp)   gated RMSNorm, bf16 outputs, replay saves.
 //
-// The state therefore crosses HBM once in each direction as 16-byte-aligned bulk transfers that are always
-// several units deep in flight, and no role ever waits on a global load.
+// The state therefore crosses HBM once in each direction -- in as bulk transfers that are always several units deep
+// in flight, out as coalesced vector stores from the registers -- and no role ever waits on a global load.
 //
 // Arithmetic contract (what makes this a drop-in for the reference's kernels/kda.cu): every sum over the 128 key
 // channels is formed as the reference forms it -- a lane's four consecutive channels added in order from zero,
@@ -329,6 +329,34 @@ __device__ __forceinline__ void store_rows(unsigned char* slot, int warp, int la
         for (int i = 0; i < 4; ++i) unpack2(s[jp][i], a[i], b[i]);
         store_row<S>(slot, warp * kRowsPerLane + 2 * jp, lane, a);
         store_row<S>(slot, warp * kRowsPerLane + 2 * jp + 1, lane, b);
+    }
+}
+
+template <typename S>
+__device__ __forceinline__ void store_rows_global(S* head, int warp, int lane, const f32x2 (&s)[kPairs][4]) {
+    const bool vec = (reinterpret_cast<uintptr_t>(head) & (4 * sizeof(S) - 1)) == 0;
+#pragma unroll
+    for (int jp = 0; jp < kPairs; ++jp) {
+        float x[2][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) unpack2(s[jp][i], x[0][i], x[1][i]);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            S* dst = head + (size_t)(warp * kRowsPerLane + 2 * jp + half) * DK + lane * 4;
+            if constexpr (sizeof(S) == 4) {
+                if (vec) *reinterpret_cast<float4*>(dst) = make_float4(x[half][0], x[half][1], x[half][2], x[half][3]);
+                else
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = x[half][i];
+            } else {
+                const uint32_t lo = pack_bf16x2(x[half][0], x[half][1]), hi = pack_bf16x2(x[half][2], x[half][3]);
+                if (vec) *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+                else {
+                    uint16_t* d = reinterpret_cast<uint16_t*>(dst);
+                    d[0] = (uint16_t)lo; d[1] = (uint16_t)(lo >> 16); d[2] = (uint16_t)hi; d[3] = (uint16_t)(hi >> 16);
+                }
+            }
+        }
     }
 }
 
@@ -653,7 +681,6 @@ __device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* 
     uint64_t* row_empty = y_full + L::kRowSlots;
     Ring st, row;
     const bool copy0 = copies_state(p);
-    int pending = -1;  // lane 0: a state slot whose bulk store may still be reading shared memory
     UnitIter<MODE> units(p);
     while (units.valid()) {
         const Unit un = units.take(p);
@@ -661,12 +688,10 @@ __device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* 
         if (!mbar_wait(&st_full[st.idx], st.phase, ctx, kStatusWaitStateFull)) return;
         unsigned char* slot = smem + L::oState + st.idx * L::kStateBytes;
         f32x2 s[kPairs][4];
-        if (un.rows > 0) load_rows<S>(slot, warp, lane, s);
+        load_rows<S>(slot, warp, lane, s);
         const bool writes = p.state_out != nullptr;
-        if (!writes) {  // verify: the slot is free as soon as the registers hold the state
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&st_empty[st.idx]);
-        }
+        __syncwarp();  // the slot is free as soon as every lane's registers hold the state
+        if (lane == 0) mbar_arrive(&st_empty[st.idx]);
         for (int r = 0; r < un.rows; ++r) {
             if (!mbar_wait(&row_full[row.idx], row.phase, ctx, kStatusWaitRowFull)) return;
             Cooked& ck = *reinterpret_cast<Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
@@ -698,40 +723,13 @@ __device__ void recurrence_role(const Params& p, unsigned char* smem, uint64_t* 
             row.next(L::kRowSlots);
         }
         if (writes) {
-            if (un.rows > 0) store_rows<S>(slot, warp, lane, s);
-            constexpr int kWarpBytes = kRowsPerLane * DK * (int)sizeof(S);
-            unsigned char* dst = reinterpret_cast<unsigned char*>(p.state_out) + un.s_elem * (long long)sizeof(S) + (size_t)warp * kWarpBytes;
-            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    bulk_store(dst, slot + (size_t)warp * kWarpBytes, kWarpBytes);
-                    bulk_commit();
-                    if (pending >= 0) {
-                        bulk_wait_read<1>();
-                        mbar_arrive(&st_empty[pending]);
-                    }
-                    pending = st.idx;
-                }
-            } else {  // an unaligned destination: element-wise stores
-                __syncwarp();
-                const S* src = reinterpret_cast<const S*>(slot + (size_t)warp * kWarpBytes);
-                S* d = reinterpret_cast<S*>(dst);
-                for (int e = lane; e < kRowsPerLane * DK; e += 32) d[e] = src[e];
-                __syncwarp();
-                if (lane == 0) {
-                    if (pending >= 0) {
-                        bulk_wait_read<0>();
-                        mbar_arrive(&st_empty[pending]);
-                        pending = -1;
-                    }
-                    mbar_arrive(&st_empty[st.idx]);
-                }
-            }
+            // Straight from the registers: per row a lane stores its 4 consecutive elements (8 or 16 bytes), a warp a
+            // whole contiguous row.  Each warp wrote nothing but the rows it read, so in place is safe.
+            S* dst = reinterpret_cast<S*>(p.state_out) + un.s_elem;
+            store_rows_global<S>(dst, warp, lane, s);
         }
         st.next(L::kStateSlots);
     }
-    if (lane == 0) bulk_wait_read<0>();
 }
 
 // ---- the epilogue --------------------------------------------------------------------------------------------

@@ -16,6 +16,7 @@ SOURCES = {
     "kda_chain.cu": IEEE,
     "kda_conv.cu": IEEE,
     "kda_prefill.cu": IEEE,
+    "kda_prefill_tc.cu": [],  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
 }
 
 

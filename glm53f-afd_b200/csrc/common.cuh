@@ -22,6 +22,7 @@ enum : int {
     kStatusWaitYFull = 107,
     kStatusWaitYEmpty = 108,
     kStatusWaitPrefill = 120,
+    kStatusPrefillRange = 121,  // a chunk's cumulative decay left the range the tensor-core prefill covers
 };
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }

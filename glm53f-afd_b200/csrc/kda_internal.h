@@ -29,6 +29,12 @@ int conv_shift_launch(int32_t channels, int32_t layers, int32_t batch, const int
                       int32_t keep1, int32_t rows1, glm53f_bf16* conv, int64_t conv_stride, const int64_t* conv_off,
                       const glm53f_bf16* p, int64_t p_layer_stride, int64_t p_stride, cudaStream_t stream);
 
+// The chunk-64 tensor-core prefill (kda_prefill_tc.cu).  q, k, v, g, out (and gate, norm_w) must be 16-byte aligned.
+int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, const glm53f_bf16* q, const glm53f_bf16* k,
+                           const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
+                           const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate, const glm53f_bf16* norm_w,
+                           float eps, glm53f_bf16* out, cudaStream_t stream);
+
 int sm_count();
 
 // Device address of the status word kernels record a timed-out wait in (current device).

@@ -4,8 +4,12 @@
 // length from a committed state and conv window; the window is advanced past the segment in place.
 // glm53f_kda_core_prefill_varlen: the same recurrence on post-conv inputs with packed variable-length sequences.
 //
-// Both currently run the exact row-by-row recurrence of kda_chain.cu (so their results are the chain's, bit for
-// bit for the layer entry points), with the chunk-64 tensor-core path taking over where it is enabled.
+// The layer entry points run the exact row-by-row recurrence of kda_chain.cu (their results are the chain's, bit
+// for bit: the model's gate bound of -5 per row is outside the range the chunk-64 tensor-core scheme covers).  The
+// core entry point runs the chunk-64 tcgen05 kernel of kda_prefill_tc.cu.
+
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "kda_internal.h"
@@ -95,6 +99,21 @@ extern "C" int glm53f_kda_core_prefill_varlen(int32_t heads, int32_t batch, cons
                                               const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
                                               glm53f_bf16* out, glm53f_stream_t stream) {
     if (max_len < 0 || !state_out) return kInvalid;
+    if (heads < 1 || heads > 65535 || batch < 1 || batch > 65535) return kInvalid;
+    if (!cu_seqlens || !q || !k || !v || !g || !beta || !state_in || !state_off || !out) return kInvalid;
+    if (gate && !norm_w) return kInvalid;
+    if (flags & ~GLM53F_KDA_CORE_L2NORM) return kInvalid;
+    // The tensor-core path takes 16-byte-aligned dense rows and inputs that are already normalised; anything else
+    // (and GLM53F_KDA_PREFILL=chain, for comparisons) runs the exact row-by-row recurrence.
+    auto aligned = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    static const bool force_chain = [] {
+        const char* e = getenv("GLM53F_KDA_PREFILL");
+        return e != nullptr && strcmp(e, "chain") == 0;
+    }();
+    if (!force_chain && flags == 0 && aligned(q) && aligned(k) && aligned(v) && aligned(g) && aligned(out) &&
+        (!gate || (aligned(gate) && aligned(norm_w))))
+        return core_prefill_tc_launch(heads, batch, cu_seqlens, q, k, v, g, beta, state_in, state_out, state_off, state_bf16 != 0,
+                                      gate, norm_w, eps, out, (cudaStream_t)stream);
     return core_chain_launch(heads, batch, cu_seqlens, q, k, v, g, beta, state_in, state_out, state_off, state_bf16 != 0, flags,
                              gate, norm_w, eps, out, (cudaStream_t)stream);
 }

@@ -1,15 +1,15 @@
 // Chunked KDA prefill on the 5th-generation tensor cores (tcgen05 + TMEM), chunk = 64 rows.
 //
-// One block of 128 threads per (sequence, head) walks the sequence's chunks in order; the head's 128x128 state
+// One block (16 compute warps + 1 loader warp) per (sequence, head) walks the sequence's chunks in order; the head's 128x128 state
 // stays in tensor memory (FP32 accumulator, 128 lanes = key channel, 128 columns = value channel) from the first
 // chunk to the last and touches HBM twice: once in, once out.  Per chunk (the algebra of the reference's CPU
 // definition crates/glm53f-kda/src/chunked.rs:67-198, which itself restates chunk_kimi_delta_attention):
 //
 //   G_i   = g_0 + ... + g_i per key channel (FP32 scan, thread = channel), E = exp(G), E_last = exp(G_63)
 //   Kg = k*E, Qg = q*E, Kinv = k/E, Kdec = k * E_last/E                       (operand tiles, written by hand)
-//   [L; M] = [Kg; Qg] Kinv^T          one 128x64x128 MMA; L strictly lower * beta_i, M lower incl. diagonal
-//   T  = (I + L)^-1                   FP32 on the CUDA cores: 16x16 diagonal blocks by substitution, the
-//                                     off-diagonal blocks by block back-substitution;  T' = T diag(beta)
+//   L = Kg Kinv^T, M = Qg Kinv^T      64x64x128 MMAs; L strictly lower * beta_i, M lower incl. diagonal
+//   T  = (I + L)^-1                   FP32 on the CUDA cores by recursive doubling: the lower-left block of every
+//                                     2sz x 2sz diagonal block is -T22 (L21 T11), sz = 1 .. 32;  T' = T diag(beta)
 //   W  = T' Kg,  U = T' V             64x128x64 MMAs; T' as bf16 hi + lo for U
 //   D  = U - W S,  QS = Qg S          64x128x128 MMAs on a bf16 copy of S; D accumulates in place (negated A)
 //   O  = QS + M D                     64x128x64 MMA
@@ -39,25 +39,31 @@ namespace kda {
 namespace {
 
 constexpr int CH = 64;            // rows per chunk
-constexpr int kThreadsTc = 128;   // thread t <-> TMEM lane t
+constexpr int kCompute = 512;     // 16 compute warps: warp w reaches TMEM lanes 32*(w%4).., and takes columns 32*(w/4)..
+constexpr int kThreadsTc = kCompute + 32;  // + one loader warp that streams the next chunk's rows in
 constexpr int RS16 = 272;         // staging row stride, bf16 tensors (256 + 16: rows 4 banks apart)
 constexpr int RS32 = 528;         // staging row stride, f32 tensor
-// Shared memory map (bytes).
+// Shared memory map (bytes).  Tiles are 64-row (R = 64) cell arrays unless noted; buffers whose lifetimes do not
+// overlap inside a chunk share space, so that the staging area is free again as soon as the operands are built and
+// the next chunk's rows can stream in behind the current chunk's arithmetic.
+constexpr int kTile = CH * 16 * 16;  // 16 KiB: 64 rows x 128 bf16
 constexpr int oRawQ = 0, oRawK = oRawQ + CH * RS16, oRawV = oRawK + CH * RS16, oRawG = oRawV + CH * RS16;
-constexpr int kRegionA = oRawG + CH * RS32;            // 86,016
-// Region A is reused once the operands are built: L, T, P (FP32) during the inversion, then S16 / D_hi / D_lo.
-constexpr int LS = 65;                                  // FP32 row stride of L and T
-constexpr int oL = 0, oT = oL + CH * LS * 4, oP = oT + CH * LS * 4;  // P: [16][49]
-constexpr int oS16 = 0, oDhi = oS16 + 128 * 16 * 16, oDlo = oDhi + CH * 16 * 16;
-static_assert(oP + 16 * 49 * 4 <= kRegionA && oDlo + CH * 16 * 16 <= kRegionA, "region A overflow");
-constexpr int XR = 192;                                 // X rows: Kg 0..63, Qg 64..127, W 128..191
-constexpr int oX = kRegionA, oKinv = oX + XR * 16 * 16, oKdHi = oKinv + CH * 16 * 16, oKdLo = oKdHi + CH * 16 * 16;
-constexpr int oTpHi = oKdLo + CH * 16 * 16, oTpLo = oTpHi + CH * 8 * 16, oMm = oTpLo + CH * 8 * 16, oV = oMm + CH * 8 * 16;
-constexpr int oBeta = oV + CH * 16 * 16, oEGL = oBeta + CH * 4, oBars = oEGL + 128 * 4, oCtl = oBars + 16;
+constexpr int oKg = oRawG + CH * RS32;   // Kg                       (steps 2-6)   } later S16 [128 rows] (steps 8-9)
+constexpr int oKinv = oKg + kTile;        // Kinv (2-3), then L FP32  (4-5)         }
+constexpr int oTp = oKinv + kTile;        // P FP32 (5), then T' hi | T' lo (5c-6)  } later D hi (steps 10-11)
+constexpr int oV = oTp + kTile;           // V                        (steps 2-6)   } later D lo
+constexpr int oQg = oV + kTile;           // Qg                       (steps 2-9)
+constexpr int oW = oQg + kTile;           // T FP32 (5), then W       (steps 7-9)
+constexpr int oKdHi = oW + kTile, oKdLo = oKdHi + kTile;  // Kdec hi, lo (steps 2-11)
+constexpr int oMm = oKdLo + kTile;        // M, 64 x 64 bf16          (steps 4-11)
+constexpr int oS16 = oKg, oDhi = oTp, oDlo = oV, oL = oKinv, oT = oW, oP = oTp, oTpHi = oTp, oTpLo = oTp + kTile / 2;
+constexpr int LS = 64;                    // FP32 row stride of L and T
+constexpr int oBeta = oMm + kTile / 2, oEGL = oBeta + 2 * CH * 4, oScan = oEGL + 128 * 4, oRed = oScan + 4 * 128 * 4;
+constexpr int oBars = oRed + 4 * CH * 4, oCtl = oBars + 32;
 constexpr int kSmemTc = oCtl + 32;
 static_assert(kSmemTc <= 232448, "shared memory budget");
 // Tensor memory columns.
-constexpr uint32_t cS = 0, cLM = 128, cW = 192, cQS = 192, cU = 320, kTmemCols = 512;
+constexpr uint32_t cS = 0, cL = 128, cMm = 192, cW = 256, cQS = 256, cU = 384, kTmemCols = 512;
 
 struct TcParams {
     int H;
@@ -76,17 +82,84 @@ struct TcParams {
     int* status;
 };
 
+__device__ __forceinline__ void compute_sync() { named_bar_sync(1, kCompute); }
+
 __device__ __forceinline__ unsigned char* cell(unsigned char* tile, int R, int c, int r) { return tile + ((size_t)c * R + r) * 16; }
+
+// Eight FP32 values (TMEM words) to one 16-byte cell of bf16.
+__device__ __forceinline__ uint4 pack8(const uint32_t* r) {
+    return make_uint4(tc::bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])), tc::bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                      tc::bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])), tc::bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+}
+
+// One level of the recursive-doubling inverse of I + L (L strictly lower, 64 x 64, row stride LS).  Given T correct on
+// every sz x sz diagonal block, fills the lower-left sz x sz block of every 2sz x 2sz diagonal block with
+// -T22 (L21 T11).  A thread computes VJ consecutive columns of one row; the loops run over the full block (the
+// triangular halves that are zero cost a few multiply-adds and keep the trip counts fixed and unrolled).
+template <int LG>
+__device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* Pm, int tid) {
+    constexpr int sz = 1 << LG, nblk = 32 >> LG, VJ = sz >= 4 ? 4 : sz, cols = sz / VJ, per = sz * cols, total = nblk * per;
+    for (int e = tid; e < total; e += kCompute) {
+        const int blk = e / per, rem = e % per, i = rem / cols, j0 = (rem % cols) * VJ;
+        const int c0 = blk * 2 * sz, r0 = c0 + sz;
+        const float* Lrow = Lm + (r0 + i) * LS + c0;
+        const float* Tc = Tm + c0 * LS + c0 + j0;
+        float acc[VJ];
+#pragma unroll
+        for (int v = 0; v < VJ; ++v) acc[v] = 0.0f;
+#pragma unroll
+        for (int m = 0; m < sz; ++m) {
+            const float l = Lrow[m];
+            if constexpr (VJ == 4) {
+                const float4 t = *reinterpret_cast<const float4*>(Tc + m * LS);
+                acc[0] = fmaf(l, t.x, acc[0]); acc[1] = fmaf(l, t.y, acc[1]); acc[2] = fmaf(l, t.z, acc[2]); acc[3] = fmaf(l, t.w, acc[3]);
+            } else {
+#pragma unroll
+                for (int v = 0; v < VJ; ++v) acc[v] = fmaf(l, Tc[m * LS + v], acc[v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VJ; ++v) Pm[blk * sz * sz + i * sz + j0 + v] = acc[v];
+    }
+    compute_sync();
+    for (int e = tid; e < total; e += kCompute) {
+        const int blk = e / per, rem = e % per, i = rem / cols, j0 = (rem % cols) * VJ;
+        const int c0 = blk * 2 * sz, r0 = c0 + sz;
+        const float* Trow = Tm + (r0 + i) * LS + r0;
+        const float* Pc = Pm + blk * sz * sz + j0;
+        float acc[VJ];
+#pragma unroll
+        for (int v = 0; v < VJ; ++v) acc[v] = 0.0f;
+#pragma unroll
+        for (int m = 0; m < sz; ++m) {
+            const float t = Trow[m];
+            if constexpr (VJ == 4) {
+                const float4 pv = *reinterpret_cast<const float4*>(Pc + m * sz);
+                acc[0] = fmaf(t, pv.x, acc[0]); acc[1] = fmaf(t, pv.y, acc[1]); acc[2] = fmaf(t, pv.z, acc[2]); acc[3] = fmaf(t, pv.w, acc[3]);
+            } else {
+#pragma unroll
+                for (int v = 0; v < VJ; ++v) acc[v] = fmaf(t, Pc[m * sz + v], acc[v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VJ; ++v) Tm[(r0 + i) * LS + c0 + j0 + v] = -acc[v];
+    }
+    compute_sync();
+}
 
 __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_constant__ TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
     uint64_t* bar_mma = bar_raw + 1;
+    uint64_t* bar_free = bar_raw + 2;  // the staging area may be overwritten
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
     uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
-    float* betas = reinterpret_cast<float*>(smem + oBeta);
+    float* betas2 = reinterpret_cast<float*>(smem + oBeta);  // [2][64]: the loader fills the next chunk's
     float* egl = reinterpret_cast<float*>(smem + oEGL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, cg = warp >> 2;   // TMEM lane quadrant, column group
+    const int lane_row128 = quad * 32 + lane;     // row of an M = 128 accumulator this thread reaches
+    const int lane_row64 = quad * 16 + lane;      // row of an M = 64 accumulator (lanes 0..15 only)
     const int h = blockIdx.x, b = blockIdx.y, H = p.H;
     const long long row0 = p.cu[b];
     const int T = p.cu[b + 1] - p.cu[b];
@@ -95,6 +168,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
     if (tid == 0) {
         mbar_init(bar_raw, 1);
         mbar_init(bar_mma, 1);
+        mbar_init(bar_free, 1);
         ctl[0] = 0u;
         ctl[1] = 0u;
         mbar_init_fence();
@@ -108,64 +182,120 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
     uint32_t raw_phase = 0, mma_phase = 0;
     bool alive = true;
 
-    // ---- the incoming state into tensor memory: thread = key channel, columns = value channel ----------------------
-    for (int c0 = 0; c0 < 4; ++c0) {
+    // ---- the loader warp: for every chunk, once the staging area is free, one bulk copy per row and tensor ----------
+    if (warp == kCompute / 32) {
+        uint32_t free_phase = 0;
+        for (int s = 0, it = 0; s < T; s += CH, ++it) {
+            if (it > 0) {
+                if (!mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
+                free_phase ^= 1u;
+            }
+            const int n = min(CH, T - s);
+            const long long gr0 = row0 + s;
+            float* bt = betas2 + (it & 1) * CH;
+            for (int r = lane; r < CH; r += 32) {
+                bt[r] = r < n ? p.beta[(gr0 + r) * H + h] : 0.0f;
+                if (r >= n) {  // rows past the end of the sequence are zero
+                    const uint4 z = make_uint4(0, 0, 0, 0);
+                    for (int e = 0; e < 16; ++e) {
+                        *reinterpret_cast<uint4*>(smem + oRawQ + r * RS16 + e * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + oRawK + r * RS16 + e * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + oRawV + r * RS16 + e * 16) = z;
+                    }
+                    for (int e = 0; e < 32; ++e) *reinterpret_cast<uint4*>(smem + oRawG + r * RS32 + e * 16) = z;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_expect_tx(bar_raw, (uint32_t)n * (3 * 256 + 512));  // releases beta and the zero rows
+            for (int r = lane; r < n; r += 32) {
+                const long long at = ((gr0 + r) * H + h) * DK;
+                bulk_load(smem + oRawQ + r * RS16, p.q + at, 256, bar_raw);
+                bulk_load(smem + oRawK + r * RS16, p.k + at, 256, bar_raw);
+                bulk_load(smem + oRawV + r * RS16, p.v + at, 256, bar_raw);
+                bulk_load(smem + oRawG + r * RS32, p.g + at, 512, bar_raw);
+            }
+        }
+        tc::fence_before_sync();
+        __syncthreads();  // the block's final barrier
+        return;
+    }
+
+    // One round of MMAs: thread 0 issues and commits, everybody waits for the tensor core.
+    auto mma_round = [&](auto&& issue) -> bool {
+        if (tid == 0) {
+            issue();
+            tc::mma_commit(bar_mma);
+            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+        }
+        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) return false;
+        mma_phase ^= 1u;
+        tc::fence_after_sync();
+        return true;
+    };
+    auto publish_operands = [&]() {  // generic-proxy writes -> tensor core, and TMEM accesses ordered across the block
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        compute_sync();
+        tc::fence_after_sync();
+    };
+
+    // ---- the incoming state into tensor memory: lane = key channel, columns = value channel -----------------------
+    {
         uint32_t r[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const long long at = s_elem + (long long)(c0 * 32 + j) * DK + tid;
+            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
             const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.state_in)[at])
                                          : reinterpret_cast<const float*>(p.state_in)[at];
             r[j] = __float_as_uint(x);
         }
-        tc::tmem_st32(tc::tmem_addr(tm, warp, cS + c0 * 32), r);
+        tc::tmem_st32(tc::tmem_addr(tm, quad, cS + cg * 32), r);
+        tc::tmem_st_wait();
     }
-    tc::tmem_st_wait();
 
-    for (int s = 0; s < T && alive; s += CH) {
+    for (int s = 0; s < T; s += CH) {
         const int n = min(CH, T - s);
         const long long gr0 = row0 + s;
-        // ---- 0. raw rows: bulk copies, one per row and tensor; rows past the end are zero ------------------------
-        if (tid == 0) mbar_arrive_expect_tx(bar_raw, (uint32_t)n * (3 * 256 + 512));
-        if (tid < n) {
-            const long long at = ((gr0 + tid) * H + h) * DK;
-            bulk_load(smem + oRawQ + tid * RS16, p.q + at, 256, bar_raw);
-            bulk_load(smem + oRawK + tid * RS16, p.k + at, 256, bar_raw);
-            bulk_load(smem + oRawV + tid * RS16, p.v + at, 256, bar_raw);
-            bulk_load(smem + oRawG + tid * RS32, p.g + at, 512, bar_raw);
-        } else if (tid < CH) {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            for (int e = 0; e < 16; ++e) {
-                *reinterpret_cast<uint4*>(smem + oRawQ + tid * RS16 + e * 16) = z;
-                *reinterpret_cast<uint4*>(smem + oRawK + tid * RS16 + e * 16) = z;
-                *reinterpret_cast<uint4*>(smem + oRawV + tid * RS16 + e * 16) = z;
-            }
-            for (int e = 0; e < 32; ++e) *reinterpret_cast<uint4*>(smem + oRawG + tid * RS32 + e * 16) = z;
-        }
-        if (tid < CH) betas[tid] = tid < n ? p.beta[(gr0 + tid) * H + h] : 0.0f;
+        const float* betas = betas2 + ((s / CH) & 1) * CH;
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
         raw_phase ^= 1u;
-        __syncthreads();
 
-        // ---- 1. cumulative log decay per key channel; the staging buffer keeps E = exp(G) ---------------------------
+        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging buffer --------------------------
+        // Thread (part, d): rows 16*part .. 16*part+15 of channel d; the parts' totals are combined through shared
+        // memory, so the scan is 16 steps deep instead of 64.
         {
-            float G = 0.0f, e = 1.0f;
-            for (int r = 0; r < CH; ++r) {
-                float* at = reinterpret_cast<float*>(smem + oRawG + r * RS32) + tid;
-                G += *at;
-                e = expf(G);
-                *at = e;
+            const int part = tid >> 7, d = tid & 127;
+            float* col = reinterpret_cast<float*>(smem + oRawG + (part * 16) * RS32) + d;
+            float* totals = reinterpret_cast<float*>(smem + oScan);
+            float loc[16], G = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                G += *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32);
+                loc[r] = G;
             }
-            egl[tid] = e;
-            if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            totals[part * 128 + d] = G;
+            compute_sync();
+            float base = 0.0f;
+            for (int q2 = 0; q2 < part; ++q2) base += totals[q2 * 128 + d];
+            float e = 1.0f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                e = __expf(base + loc[r]);
+                *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32) = e;
+            }
+            if (part == 3) {
+                egl[d] = e;
+                if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            }
         }
-        __syncthreads();
+        compute_sync();
 
-        // ---- 2. operand tiles: lane <-> row, 8 channels (one 16-byte cell) at a time -------------------------------
+        // ---- 2. operand tiles: lane <-> row, one 16-byte cell (8 channels) at a time -------------------------------------
         {
-            const int r = tid & 63, half = tid >> 6;
-            for (int cc = 0; cc < 8; ++cc) {
-                const int c = half * 8 + cc;
+            const int r = tid & 63, cgrp = tid >> 6;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cgrp * 2 + cc;
                 const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
                 const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
                 const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oRawV + r * RS16 + c * 16);
@@ -179,12 +309,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 uint32_t kg[4], qg[4], ki[4], dh[4], dl[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    float kf[2] = {__uint_as_float(kw[j] << 16), __uint_as_float(kw[j] & 0xffff0000u)};
-                    float qf[2] = {__uint_as_float(qw[j] << 16), __uint_as_float(qw[j] & 0xffff0000u)};
+                    const float kf[2] = {__uint_as_float(kw[j] << 16), __uint_as_float(kw[j] & 0xffff0000u)};
+                    const float qf[2] = {__uint_as_float(qw[j] << 16), __uint_as_float(qw[j] & 0xffff0000u)};
                     float a[2], bq[2], ci[2], hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const float e = E[2 * j + u], einv = __frcp_rn(e);
+                        const float e = E[2 * j + u], einv = __fdividef(1.0f, e);
                         a[u] = kf[u] * e;
                         bq[u] = qf[u] * e;
                         ci[u] = kf[u] * einv;
@@ -196,116 +326,69 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                     dh[j] = tc::bf16x2(hi[0], hi[1]);
                     dl[j] = tc::bf16x2(lo[0], lo[1]);
                 }
-                *reinterpret_cast<uint4*>(cell(smem + oX, XR, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oX, XR, c, 64 + r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
             }
         }
-        fence_proxy_async_smem();
-        tc::fence_before_sync();
-        __syncthreads();
-        tc::fence_after_sync();
+        publish_operands();
+        // The staging area is free: the loader streams the next chunk's rows in behind this chunk's arithmetic.
+        if (tid == 0 && s + CH < T) mbar_arrive(bar_free);
 
-        // ---- 3. [L; M] = [Kg; Qg] Kinv^T ---------------------------------------------------------------------------
-        if (tid == 0) {
-            constexpr uint32_t id = tc::idesc_bf16(128, 64, 0, 0, 0);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + cLM, tc::desc_kmajor_bf16(smem + oX, XR, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-            tc::mma_commit(bar_mma);
-            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
-        }
-        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
-        mma_phase ^= 1u;
-        tc::fence_after_sync();
+        // ---- 3. L = Kg Kinv^T, M = Qg Kinv^T ----------------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+            })) { alive = false; break; }
 
-        // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) ------------------
+        // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) --------------------------
+        // Column groups 0, 1 take the two halves of L, groups 2, 3 the two halves of M; lanes 0..15 hold rows.
         {
-            const int i = tid & 63;
-            float* Lr = reinterpret_cast<float*>(smem + oL) + i * LS;
-            float* Tr = reinterpret_cast<float*>(smem + oT) + i * LS;
-            const float bi = betas[i];
-            for (int c0 = 0; c0 < 2; ++c0) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, warp, cLM + c0 * 32), r);
-                tc::tmem_ld_wait();
-                if (tid < 64) {
+            uint32_t r[32];
+            const int half = cg & 1, i = lane_row64;
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg < 2 ? cL : cMm) + half * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
+                if (cg < 2) {
+                    float* Lr = reinterpret_cast<float*>(smem + oL) + i * LS + half * 32;
+                    const float bi = betas[i];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = c0 * 32 + j;
-                        Lr[col] = col < i ? bi * __uint_as_float(r[j]) : 0.0f;
-                        Tr[col] = 0.0f;
-                    }
+                    for (int j = 0; j < 32; ++j) Lr[j] = half * 32 + j < i ? bi * __uint_as_float(r[j]) : 0.0f;
                 } else {
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t w[4];
+                    for (int j = 0; j < 32; ++j)
+                        if (half * 32 + j > i) r[j] = 0u;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int col = c0 * 32 + cc * 8 + 2 * j;
-                            const float x0 = col <= i ? __uint_as_float(r[cc * 8 + 2 * j]) : 0.0f;
-                            const float x1 = col + 1 <= i ? __uint_as_float(r[cc * 8 + 2 * j + 1]) : 0.0f;
-                            w[j] = tc::bf16x2(x0, x1);
-                        }
-                        *reinterpret_cast<uint4*>(cell(smem + oMm, CH, c0 * 4 + cc, i)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
                 }
             }
         }
-        __syncthreads();
+        compute_sync();
 
-        // ---- 5. T = (I + L)^-1 in FP32 ------------------------------------------------------------------------------
+        // ---- 5. T = (I + L)^-1 in FP32 ------------------------------------------------------------------------------------------
         {
             const float* Lm = reinterpret_cast<const float*>(smem + oL);
             float* Tm = reinterpret_cast<float*>(smem + oT);
             float* Pm = reinterpret_cast<float*>(smem + oP);
-            // 5a. the four 16x16 diagonal blocks by forward substitution: thread j keeps column j of its block.
-            if (tid < 64) {
-                const int blk = tid >> 4, jj = tid & 15, base = blk * 16;
-                float tcol[16];
-#pragma unroll
-                for (int m = 0; m < 16; ++m) tcol[m] = m == jj ? 1.0f : 0.0f;
-#pragma unroll
-                for (int ii = 1; ii < 16; ++ii) {
-                    float acc = Lm[(base + ii) * LS + base + jj];
-#pragma unroll
-                    for (int m = 1; m < 15; ++m)
-                        if (m > jj && m < ii) acc = fmaf(Lm[(base + ii) * LS + base + m], tcol[m], acc);
-                    if (jj < ii) tcol[ii] = -acc;
-                }
-#pragma unroll
-                for (int m = 0; m < 16; ++m) Tm[(base + m) * LS + base + jj] = tcol[m];
-            }
-            __syncthreads();
-            // 5b. block rows 1..3: P = L[I, 0..I) T[0..I, 0..I), then T[I, 0..I) = -T[I,I] P.
-            for (int I = 1; I < 4; ++I) {
-                const int cols = 16 * I;
-                for (int e = tid; e < 16 * cols; e += kThreadsTc) {
-                    const int i = e / cols, j = e % cols;
-                    const float* Lrow = Lm + (16 * I + i) * LS;
-                    float a0 = 0.0f, a1 = 0.0f;
-                    for (int m = j & ~15; m < cols; m += 2) {  // T[m][j] is zero above its block's diagonal
-                        a0 = fmaf(Lrow[m], Tm[m * LS + j], a0);
-                        a1 = fmaf(Lrow[m + 1], Tm[(m + 1) * LS + j], a1);
-                    }
-                    Pm[i * 49 + j] = a0 + a1;
-                }
-                __syncthreads();
-                for (int e = tid; e < 16 * cols; e += kThreadsTc) {
-                    const int i = e / cols, j = e % cols;
-                    const float* Trow = Tm + (16 * I + i) * LS + 16 * I;
-                    float acc = 0.0f;
-                    for (int m = 0; m <= i; ++m) acc = fmaf(Trow[m], Pm[m * 49 + j], acc);
-                    Tm[(16 * I + i) * LS + j] = -acc;
-                }
-                __syncthreads();
-            }
-            // 5c. T' = T diag(beta) as bf16 hi + lo cells.
-            const int i = tid & 63, half = tid >> 6;
-            for (int cc = 0; cc < 4; ++cc) {
-                const int c = half * 4 + cc;
+            // Recursive doubling.  T starts as the identity; at block size sz the lower-left sz x sz block of every
+            // 2sz x 2sz diagonal block is -T22 (L21 T11), all blocks and elements in parallel.
+            for (int e = tid; e < CH * LS; e += kCompute) Tm[e] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
+            compute_sync();
+            invert_level<0>(Lm, Tm, Pm, tid);
+            invert_level<1>(Lm, Tm, Pm, tid);
+            invert_level<2>(Lm, Tm, Pm, tid);
+            invert_level<3>(Lm, Tm, Pm, tid);
+            invert_level<4>(Lm, Tm, Pm, tid);
+            invert_level<5>(Lm, Tm, Pm, tid);
+            // 5c. T' = T diag(beta) as bf16 hi + lo cells (P is dead: T' takes its place).
+            {
+                const int i = tid & 63, c = tid >> 6;
                 uint32_t wh[4], wl[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -313,8 +396,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         const int col = c * 8 + 2 * j + u;
-                        const float t = col <= i ? Tm[i * LS + col] * betas[col] : 0.0f;
-                        tc::split_bf16(t, hi[u], lo[u]);
+                        tc::split_bf16(Tm[i * LS + col] * betas[col], hi[u], lo[u]);
                     }
                     wh[j] = tc::bf16x2(hi[0], hi[1]);
                     wl[j] = tc::bf16x2(lo[0], lo[1]);
@@ -323,193 +405,140 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 *reinterpret_cast<uint4*>(cell(smem + oTpLo, CH, c, i)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
         }
-        fence_proxy_async_smem();
-        tc::fence_before_sync();
-        __syncthreads();
-        tc::fence_after_sync();
+        publish_operands();
 
-        // ---- 6. W = T' Kg (bf16 T'), U = T' V (T' hi + lo) -----------------------------------------------------------
-        if (tid == 0) {
-            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cW, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oX, XR, 0, k0), id, k0 > 0);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, k0 > 0);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, true);
-            tc::mma_commit(bar_mma);
-            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
-        }
-        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
-        mma_phase ^= 1u;
-        tc::fence_after_sync();
+        // ---- 6. W = T' Kg (bf16 T'), U = T' V (T' hi + lo) -------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cW, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oKg, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, true);
+            })) { alive = false; break; }
 
-        // ---- 7. W to bf16 cells (rows 128.. of X); 8. S to bf16 cells, and the decayed S back to tensor memory -------
+        // ---- 7. W to bf16 cells; 8. S to bf16 cells (over Kg | Kinv, both dead), the decayed S back to tensor memory ------------
         {
-            const int i = warp * 16 + lane;  // valid for lane < 16: row of an M = 64 accumulator
-            for (int c0 = 0; c0 < 4; ++c0) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, warp, cW + c0 * 32), r);
-                tc::tmem_ld_wait();
-                if (lane < 16) {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cW + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc)
-                        *reinterpret_cast<uint4*>(cell(smem + oX, XR, c0 * 4 + cc, 128 + i)) =
-                            make_uint4(tc::bf16x2(__uint_as_float(r[cc * 8 + 0]), __uint_as_float(r[cc * 8 + 1])),
-                                       tc::bf16x2(__uint_as_float(r[cc * 8 + 2]), __uint_as_float(r[cc * 8 + 3])),
-                                       tc::bf16x2(__uint_as_float(r[cc * 8 + 4]), __uint_as_float(r[cc * 8 + 5])),
-                                       tc::bf16x2(__uint_as_float(r[cc * 8 + 6]), __uint_as_float(r[cc * 8 + 7])));
-                }
+                for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oW, CH, cg * 4 + cc, lane_row64)) = pack8(r + cc * 8);
             }
-            const float el = egl[tid];
-            for (int c0 = 0; c0 < 4; ++c0) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, warp, cS + c0 * 32), r);
-                tc::tmem_ld_wait();
-                if (p.state_bf16) {  // a bf16 state is rounded once per chunk
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cS + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (p.state_bf16) {  // a bf16 state is rounded once per chunk
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bf16_round(__uint_as_float(r[j])));
-                }
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-                    *reinterpret_cast<uint4*>(cell(smem + oS16, 128, c0 * 4 + cc, tid)) =
-                        make_uint4(tc::bf16x2(__uint_as_float(r[cc * 8 + 0]), __uint_as_float(r[cc * 8 + 1])),
-                                   tc::bf16x2(__uint_as_float(r[cc * 8 + 2]), __uint_as_float(r[cc * 8 + 3])),
-                                   tc::bf16x2(__uint_as_float(r[cc * 8 + 4]), __uint_as_float(r[cc * 8 + 5])),
-                                   tc::bf16x2(__uint_as_float(r[cc * 8 + 6]), __uint_as_float(r[cc * 8 + 7])));
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * el);
-                tc::tmem_st32(tc::tmem_addr(tm, warp, cS + c0 * 32), r);
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bf16_round(__uint_as_float(r[j])));
             }
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oS16, 128, cg * 4 + cc, lane_row128)) = pack8(r + cc * 8);
+            const float el = egl[lane_row128];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * el);
+            tc::tmem_st32(tc::tmem_addr(tm, quad, cS + cg * 32), r);
             tc::tmem_st_wait();
         }
-        fence_proxy_async_smem();
-        tc::fence_before_sync();
-        __syncthreads();
-        tc::fence_after_sync();
+        publish_operands();
 
-        // ---- 9. QS = Qg S;  D = U - W S (negated A, accumulated onto U) -------------------------------------------------
-        if (tid == 0) {
-            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + cQS, tc::desc_kmajor_bf16(smem + oX, XR, 64, k0), tc::desc_mnmajor_bf16(smem + oS16, 128, 0, k0), id, k0 > 0);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oX, XR, 128, k0), tc::desc_mnmajor_bf16(smem + oS16, 128, 0, k0), idn, true);
-            tc::mma_commit(bar_mma);
-            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
-        }
-        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
-        mma_phase ^= 1u;
-        tc::fence_after_sync();
+        // ---- 9. QS = Qg S;  D = U - W S (negated A, accumulated onto U) ----------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cQS, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oS16, 128, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oW, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oS16, 128, 0, k0), idn, true);
+            })) { alive = false; break; }
 
-        // ---- 10. D as bf16 hi + lo cells --------------------------------------------------------------------------------
+        // ---- 10. D as bf16 hi + lo cells (over T' | V, both dead) -------------------------------------------------------------------
         {
-            const int i = warp * 16 + lane;
-            for (int c0 = 0; c0 < 4; ++c0) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, warp, cU + c0 * 32), r);
-                tc::tmem_ld_wait();
-                if (lane < 16) {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cU + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t wh[4], wl[4];
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t wh[4], wl[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            float h0, l0, h1, l1;
-                            tc::split_bf16(__uint_as_float(r[cc * 8 + 2 * j]), h0, l0);
-                            tc::split_bf16(__uint_as_float(r[cc * 8 + 2 * j + 1]), h1, l1);
-                            wh[j] = tc::bf16x2(h0, h1);
-                            wl[j] = tc::bf16x2(l0, l1);
-                        }
-                        *reinterpret_cast<uint4*>(cell(smem + oDhi, CH, c0 * 4 + cc, i)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                        *reinterpret_cast<uint4*>(cell(smem + oDlo, CH, c0 * 4 + cc, i)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                    for (int j = 0; j < 4; ++j) {
+                        float h0, l0, h1, l1;
+                        tc::split_bf16(__uint_as_float(r[cc * 8 + 2 * j]), h0, l0);
+                        tc::split_bf16(__uint_as_float(r[cc * 8 + 2 * j + 1]), h1, l1);
+                        wh[j] = tc::bf16x2(h0, h1);
+                        wl[j] = tc::bf16x2(l0, l1);
                     }
+                    *reinterpret_cast<uint4*>(cell(smem + oDhi, CH, cg * 4 + cc, lane_row64)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4*>(cell(smem + oDlo, CH, cg * 4 + cc, lane_row64)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
             }
         }
-        fence_proxy_async_smem();
-        tc::fence_before_sync();
-        __syncthreads();
-        tc::fence_after_sync();
+        publish_operands();
 
-        // ---- 11. O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) --------------------------------------------------
-        if (tid == 0) {
-            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cQS, tc::desc_kmajor_bf16(smem + oMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), id, true);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), ids, true);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDlo, CH, 0, k0), ids, true);
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), ids, true);
-            tc::mma_commit(bar_mma);
-            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
-        }
-        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
-        mma_phase ^= 1u;
-        tc::fence_after_sync();
+        // ---- 11. O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cQS, tc::desc_kmajor_bf16(smem + oMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), id, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), ids, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDlo, CH, 0, k0), ids, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), ids, true);
+            })) { alive = false; break; }
 
-        // ---- 12. outputs: bf16(y), or the gated RMSNorm of bf16(y) --------------------------------------------------------
+        // ---- 12. outputs: bf16(y), or the gated RMSNorm of bf16(y); a thread holds 32 columns of its row -------------------------------
         {
-            const int i = warp * 16 + lane;
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cQS + cg * 32), r);
+            tc::tmem_ld_wait();
+            const int i = lane_row64;
             const bool live = lane < 16 && i < n;
-            const long long at = ((gr0 + i) * H + h) * DV;
-            float y[128];
-            for (int c0 = 0; c0 < 4; ++c0) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, warp, cQS + c0 * 32), r);
-                tc::tmem_ld_wait();
+            const long long at = ((gr0 + i) * H + h) * DV + cg * 32;
+            float y[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) y[c0 * 32 + j] = bf16_round(__uint_as_float(r[j]));
+            for (int j = 0; j < 32; ++j) y[j] = bf16_round(__uint_as_float(r[j]));
+            if (p.gate != nullptr) {
+                float* red = reinterpret_cast<float*>(smem + oRed);
+                float ss = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ss = fmaf(y[j], y[j], ss);
+                if (lane < 16) red[cg * CH + i] = ss;
+                compute_sync();
+                if (live) {
+                    const float tot = (red[i] + red[CH + i]) + (red[2 * CH + i] + red[3 * CH + i]);
+                    const float rinv = 1.0f / sqrtf(tot / (float)DV + p.eps);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float gt = bf16_bits_to_f32(p.gate[at + j]), w = bf16_bits_to_f32(p.norm_w[cg * 32 + j]);
+                        y[j] = w * (y[j] * rinv) * (1.0f / (1.0f + __expf(-gt)));
+                    }
+                }
             }
             if (live) {
-                float rinv = 1.0f;
-                if (p.gate != nullptr) {
-                    float ss = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < 128; ++j) ss = fmaf(y[j], y[j], ss);
-                    rinv = 1.0f / sqrtf(ss / (float)DV + p.eps);
-                }
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    float o[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) o[j] = y[c * 8 + j];
-                    if (p.gate != nullptr) {
-                        const uint4 g8 = *reinterpret_cast<const uint4*>(p.gate + at + c * 8);
-                        const uint4 w8 = *reinterpret_cast<const uint4*>(p.norm_w + c * 8);
-                        const uint32_t gw[4] = {g8.x, g8.y, g8.z, g8.w}, ww[4] = {w8.x, w8.y, w8.z, w8.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
-                            const float w0 = __uint_as_float(ww[j] << 16), w1 = __uint_as_float(ww[j] & 0xffff0000u);
-                            o[2 * j] = w0 * (o[2 * j] * rinv) * (1.0f / (1.0f + expf(-g0)));
-                            o[2 * j + 1] = w1 * (o[2 * j + 1] * rinv) * (1.0f / (1.0f + expf(-g1)));
-                        }
-                    }
-                    *reinterpret_cast<uint4*>(p.out + at + c * 8) =
-                        make_uint4(tc::bf16x2(o[0], o[1]), tc::bf16x2(o[2], o[3]), tc::bf16x2(o[4], o[5]), tc::bf16x2(o[6], o[7]));
-                }
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(p.out + at + c * 8) = make_uint4(tc::bf16x2(y[c * 8], y[c * 8 + 1]), tc::bf16x2(y[c * 8 + 2], y[c * 8 + 3]),
+                                                                            tc::bf16x2(y[c * 8 + 4], y[c * 8 + 5]), tc::bf16x2(y[c * 8 + 6], y[c * 8 + 7]));
             }
         }
         tc::fence_before_sync();
-        __syncthreads();
+        compute_sync();
         tc::fence_after_sync();
     }
 
-    // ---- the outgoing state -------------------------------------------------------------------------------------------
+    // ---- the outgoing state -------------------------------------------------------------------------------------------------------
     if (alive) {
-        for (int c0 = 0; c0 < 4; ++c0) {
-            uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, warp, cS + c0 * 32), r);
-            tc::tmem_ld_wait();
+        uint32_t r[32];
+        tc::tmem_ld32(tc::tmem_addr(tm, quad, cS + cg * 32), r);
+        tc::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const long long at = s_elem + (long long)(c0 * 32 + j) * DK + tid;
-                if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
-                else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
-            }
+        for (int j = 0; j < 32; ++j) {
+            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+            if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
+            else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
         }
     }
     tc::fence_before_sync();

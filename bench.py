@@ -137,6 +137,123 @@ def cpu_decode_gbs(seconds: float, layers_sample: int = 2):
     return gbs, cores, f"{steps} steps x {layers_sample} of 34 layers x {SLOTS} slots x {HEADS} heads in {dt:.1f} s"
 
 
+PREFILL_T = 1_048_576           # config 3: one sequence, H = 64, d = 128, chunk 64
+PREFILL_BYTES_PER_TOKEN = 98_560  # q, k, v, out bf16 + g f32 + beta f32, all 64 heads
+PREFILL_FLOP_PER_TOKEN = 8.94e6   # causal-exact count of the chunk-64 form, all 64 heads
+BF16_SUSTAINED_TFLOPS_FALLBACK = 1400.0
+
+
+def tensor_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return BF16_SUSTAINED_TFLOPS_FALLBACK, "fallback"
+
+
+def cpu_prefill_toks(seconds: float):
+    """The CPU oracle's chunk-64 form on every host core, on a 2,048-token sample of the same distribution."""
+    import numpy as np
+
+    o = oracle_module()
+    pkg = importlib.import_module("glm53f-afd_b200")
+    cores = os.cpu_count() or 1
+    t = 2048
+    q, k, v, g, b = pkg.synth.tokens(3, 0, t, HEADS)
+    s0 = np.zeros(STATE_ELEMS, np.float32)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        o.core_forward(HEADS, q, k, v, g, b, s0, form="chunked", chunk=64, threads=cores, want_y=False)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    return n * t / dt, cores, f"{n} x {t} tokens x {HEADS} heads, chunk-64 form, in {dt:.1f} s"
+
+
+def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes):
+    """Config 3: chunked prefill of one long sequence, heads sharded over the ranks, outputs all-gathered."""
+    import ctypes as C
+
+    par = importlib.import_module("glm53f-afd_b200.parallel")
+    lo, hi = par.head_range(HEADS, rank, world)
+    hl = hi - lo
+    gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 3 + 97 * rank)
+    n = tokens * hl
+    piece = 1 << 22  # rows of 128 per generation slice: bounds the FP32 temporaries
+
+    def unit(scale):
+        out = torch.empty(n * DK, dtype=torch.bfloat16, device="cuda")
+        for a in range(0, n, piece):
+            m = min(piece, n - a)
+            x = torch.randn(m, DK, device="cuda", generator=gen)
+            x = x * (scale / torch.sqrt((x * x).sum(1, keepdim=True) + 1e-6))
+            out[a * DK:(a + m) * DK] = x.reshape(-1).to(torch.bfloat16)
+        return out
+
+    q, k = unit(DK ** -0.5), unit(1.0)
+    v = torch.empty(n * DK, dtype=torch.bfloat16, device="cuda")
+    g = torch.empty(n * DK, dtype=torch.float32, device="cuda")
+    for a in range(0, n, piece):
+        m = min(piece, n - a)
+        v[a * DK:(a + m) * DK] = torch.randn(m * DK, device="cuda", generator=gen).to(torch.bfloat16)
+        g[a * DK:(a + m) * DK] = torch.nn.functional.logsigmoid(torch.randn(m * DK, device="cuda", generator=gen) + 3.0)
+    beta = torch.sigmoid(torch.randn(n, device="cuda", generator=gen))
+    out = torch.empty(n * DK, dtype=torch.bfloat16, device="cuda")
+    state = torch.zeros(hl * DK * DK, device="cuda")
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    off = torch.zeros(1, dtype=torch.int64, device="cuda")
+    full = torch.empty((tokens, HEADS, DK), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+
+    def one_pass(gather):
+        state.zero_()
+        core.prefill_varlen(hl, tokens, cu, tokens, q, k, v, g, beta, state, off, out=out)
+        if gather and world > 1:
+            par.gather_heads(out.view(tokens, hl, DK), HEADS, out=full)
+
+    def timed(gather):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(passes):
+            one_pass(gather)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / passes
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    one_pass(True)
+    ms_compute = timed(False)
+    ms_total = timed(True) if world > 1 else ms_compute
+    assert core.device_status() == 0
+    hbm, hbm_kind = peaks()
+    tf, tf_kind = tensor_peak()
+    gbs = tokens * PREFILL_BYTES_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e9      # per GPU
+    tflops = tokens * PREFILL_FLOP_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e12  # per GPU
+    res = {
+        "workload": f"config 3: one sequence of {tokens} tokens, H=64 ({hl} heads per GPU), d=128, chunk 64, FP32 state",
+        "value": tokens / (ms_total * 1e-3), "unit": "tokens/s per layer", "ms_per_layer": ms_total,
+        "compute_only": {"value": tokens / (ms_compute * 1e-3), "ms_per_layer": ms_compute},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": hbm_kind,
+                     "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
+                                "flop_per_token": PREFILL_FLOP_PER_TOKEN},
+                     "algorithmic_bytes_per_token": PREFILL_BYTES_PER_TOKEN, "kernel": "prefill_tc_kernel"},
+        "gpu_launches": passes,
+        "collective": None if world == 1 else {"op": "all_gather of per-head outputs", "bytes_received_per_gpu": tokens * (HEADS - hl) * DK * 2,
+                                              "ms": ms_total - ms_compute},
+    }
+    del q, k, v, g, out, full
+    torch.cuda.empty_cache()
+    return res
+
+
 def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
@@ -175,6 +292,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
+    ap.add_argument("--prefill-passes", type=int, default=3)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -182,6 +301,7 @@ def main():
     import numpy as np
     import torch
 
+    dist = None
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -289,6 +409,12 @@ def main():
     e2e_value = world * per_rank_bytes / (e2e_ms * 1e-3) / 1e9
     assert core.device_status() == 0
 
+    prefill = None
+    if args.prefill_tokens > 0:
+        del arena, dev, outs
+        torch.cuda.empty_cache()
+        prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -308,10 +434,14 @@ def main():
                 "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES},
         "gpu_launches": timed_launches,
         "clocks": clocks,
+        "prefill": prefill,
     }
     if not args.no_cpu:
         v, cores, sample = cpu_decode_gbs(args.cpu_seconds)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        if prefill is not None:
+            v, cores, sample = cpu_prefill_toks(args.cpu_seconds)
+            prefill["cpu_baseline"] = {"value": v, "unit": "tokens/s per layer", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

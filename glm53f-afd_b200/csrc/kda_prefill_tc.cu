@@ -49,15 +49,19 @@ constexpr int RS32 = 528;         // staging row stride, f32 tensor
 constexpr int kTile = CH * 16 * 16;  // 16 KiB: 64 rows x 128 bf16
 constexpr int oRawQ = 0, oRawK = oRawQ + CH * RS16, oRawV = oRawK + CH * RS16, oRawG = oRawV + CH * RS16;
 constexpr int oKg = oRawG + CH * RS32;   // Kg                       (steps 2-6)   } later S16 [128 rows] (steps 8-9)
-constexpr int oKinv = oKg + kTile;        // Kinv (2-3), then L FP32  (4-5)         }
-constexpr int oTp = oKinv + kTile;        // P FP32 (5), then T' hi | T' lo (5c-6)  } later D hi (steps 10-11)
-constexpr int oV = oTp + kTile;           // V                        (steps 2-6)   } later D lo
+constexpr int oKinv = oKg + kTile;        // Kinv (2-3)                             }
+constexpr int oTp = oKinv + kTile;        // T' hi | T' lo (5c-6), later D hi (steps 10-11)
+constexpr int oW = oTp + kTile;           // W                        (steps 7-9)
+constexpr int oV = oW + kTile;            // V                        (steps 2-6), later D lo
 constexpr int oQg = oV + kTile;           // Qg                       (steps 2-9)
-constexpr int oW = oQg + kTile;           // T FP32 (5), then W       (steps 7-9)
-constexpr int oKdHi = oW + kTile, oKdLo = oKdHi + kTile;  // Kdec hi, lo (steps 2-11)
+constexpr int oKdHi = oQg + kTile, oKdLo = oKdHi + kTile;  // Kdec hi, lo (steps 2-11)
 constexpr int oMm = oKdLo + kTile;        // M, 64 x 64 bf16          (steps 4-11)
-constexpr int oS16 = oKg, oDhi = oTp, oDlo = oV, oL = oKinv, oT = oW, oP = oTp, oTpHi = oTp, oTpLo = oTp + kTile / 2;
-constexpr int LS = 64;                    // FP32 row stride of L and T
+constexpr int oS16 = oKg, oDhi = oTp, oDlo = oV, oTpHi = oTp, oTpLo = oTp + kTile / 2;
+// FP32 scratch of the inversion (steps 4-5) over Kinv | T' | W, all dead then: T, P, L.  Rows are padded to 68
+// floats so that one lane per row spreads over the banks while float4 loads stay aligned.
+constexpr int LS = 68;
+constexpr int oT = oKinv, oP = oT + CH * LS * 4, oL = oKinv + 24576;
+static_assert(oP + 32 * 32 * 4 <= oL && oL + CH * LS * 4 <= oKinv + 3 * kTile, "inversion scratch");
 constexpr int oBeta = oMm + kTile / 2, oEGL = oBeta + 2 * CH * 4, oScan = oEGL + 128 * 4, oRed = oScan + 4 * 128 * 4;
 constexpr int oBars = oRed + 4 * CH * 4, oCtl = oBars + 32;
 constexpr int kSmemTc = oCtl + 32;
@@ -378,7 +382,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
             float* Pm = reinterpret_cast<float*>(smem + oP);
             // Recursive doubling.  T starts as the identity; at block size sz the lower-left sz x sz block of every
             // 2sz x 2sz diagonal block is -T22 (L21 T11), all blocks and elements in parallel.
-            for (int e = tid; e < CH * LS; e += kCompute) Tm[e] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
+            for (int e = tid; e < CH * CH; e += kCompute) Tm[(e >> 6) * LS + (e & 63)] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
             compute_sync();
             invert_level<0>(Lm, Tm, Pm, tid);
             invert_level<1>(Lm, Tm, Pm, tid);
@@ -386,20 +390,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
             invert_level<3>(Lm, Tm, Pm, tid);
             invert_level<4>(Lm, Tm, Pm, tid);
             invert_level<5>(Lm, Tm, Pm, tid);
-            // 5c. T' = T diag(beta) as bf16 hi + lo cells (P is dead: T' takes its place).
+            // 5c. T' = T diag(beta) as bf16 hi + lo cells.  T' lands on the scratch itself, so every thread first reads
+            // its eight values of T, then the block synchronises, then the cells are written.
             {
                 const int i = tid & 63, c = tid >> 6;
+                float t8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t8[j] = Tm[i * LS + c * 8 + j] * betas[c * 8 + j];
+                compute_sync();
                 uint32_t wh[4], wl[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    float hi[2], lo[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int col = c * 8 + 2 * j + u;
-                        tc::split_bf16(Tm[i * LS + col] * betas[col], hi[u], lo[u]);
-                    }
-                    wh[j] = tc::bf16x2(hi[0], hi[1]);
-                    wl[j] = tc::bf16x2(lo[0], lo[1]);
+                    float h0, l0, h1, l1;
+                    tc::split_bf16(t8[2 * j], h0, l0);
+                    tc::split_bf16(t8[2 * j + 1], h1, l1);
+                    wh[j] = tc::bf16x2(h0, h1);
+                    wl[j] = tc::bf16x2(l0, l1);
                 }
                 *reinterpret_cast<uint4*>(cell(smem + oTpHi, CH, c, i)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oTpLo, CH, c, i)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);

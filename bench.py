@@ -171,7 +171,7 @@ def cpu_prefill_toks(seconds: float):
     return n * t / dt, cores, f"{n} x {t} tokens x {HEADS} heads, chunk-64 form, in {dt:.1f} s"
 
 
-def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes):
+def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
     """Config 3: chunked prefill of one long sequence, heads sharded over the ranks, outputs all-gathered."""
     import ctypes as C
 
@@ -204,10 +204,12 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes):
     cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
     off = torch.zeros(1, dtype=torch.int64, device="cuda")
     full = torch.empty((tokens, HEADS, DK), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    # Few chains (one sequence x this rank's heads): the two-pass form over a workspace keeps every SM busy.
+    ws = torch.empty(core.prefill_workspace_bytes(hl, 1, ws_chunks), dtype=torch.uint8, device="cuda") if ws_chunks > 0 else None
 
     def one_pass(gather):
         state.zero_()
-        core.prefill_varlen(hl, tokens, cu, tokens, q, k, v, g, beta, state, off, out=out)
+        core.prefill_varlen(hl, tokens, cu, tokens, q, k, v, g, beta, state, off, out=out, workspace=ws)
         if gather and world > 1:
             par.gather_heads(out.view(tokens, hl, DK), HEADS, out=full)
 
@@ -244,7 +246,9 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes):
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": hbm_kind,
                      "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
                                 "flop_per_token": PREFILL_FLOP_PER_TOKEN},
-                     "algorithmic_bytes_per_token": PREFILL_BYTES_PER_TOKEN, "kernel": "prefill_tc_kernel"},
+                     "algorithmic_bytes_per_token": PREFILL_BYTES_PER_TOKEN,
+                     "kernel": "intra_kernel + state_kernel" if ws_chunks > 0 else "prefill_tc_kernel",
+                     "workspace_bytes": 0 if ws is None else ws.numel()},
         "gpu_launches": passes,
         "collective": None if world == 1 else {"op": "all_gather of per-head outputs", "bytes_received_per_gpu": tokens * (HEADS - hl) * DK * 2,
                                               "ms": ms_total - ms_compute},
@@ -294,6 +298,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
+    ap.add_argument("--prefill-ws-chunks", type=int, default=32, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -413,7 +418,7 @@ def main():
     if args.prefill_tokens > 0:
         del arena, dev, outs
         torch.cuda.empty_cache()
-        prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes)
+        prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks)
 
     if rank != 0:
         if world > 1:

@@ -16,7 +16,8 @@ SOURCES = {
     "kda_chain.cu": IEEE,
     "kda_conv.cu": IEEE,
     "kda_prefill.cu": IEEE,
-    "kda_prefill_tc.cu": [],  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
+    "kda_prefill_tc.cu": [],
+    "kda_prefill_sp.cu": [],  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
 }
 
 

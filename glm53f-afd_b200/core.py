@@ -126,9 +126,14 @@ def commit_batch(heads, layers, cu_rows, keep, state, state_stride, state_off, s
     _launched(code, "glm53f_kda_core_commit_batch")
 
 
+def prefill_workspace_bytes(heads, batch, chunks_per_pass):
+    return int(ffi.glm53f_kda_core_prefill_workspace_bytes(heads, batch, chunks_per_pass))
+
+
 def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, state_off, *, state_out="in_place",
-                   flags=0, gate=None, norm_w=None, eps=1e-5, out=None):
-    """glm53f_kda_core_prefill_varlen: chunked prefill of packed variable-length sequences."""
+                   flags=0, gate=None, norm_w=None, eps=1e-5, out=None, workspace=None):
+    """glm53f_kda_core_prefill_varlen: chunked prefill of packed variable-length sequences.  With `workspace` (a
+    CUDA uint8 tensor) the two-pass glm53f_kda_core_prefill_varlen_ws runs instead."""
     batch = cu_seqlens.numel() - 1
     _need(cu_seqlens, "cu_seqlens", (torch.int32,), 2)
     _need(state_off, "state_off", (torch.int64,), batch)
@@ -137,6 +142,14 @@ def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, st
     so = state if isinstance(state_out, str) else state_out
     if so is None:
         raise Invalid("a prefill writes the state")
+    if workspace is not None:
+        if not workspace.is_cuda or not workspace.is_contiguous():
+            raise Invalid("workspace must be a contiguous CUDA tensor")
+        nbytes = workspace.numel() * workspace.element_size()
+        code = ffi.glm53f_kda_core_prefill_varlen_ws(heads, batch, _ptr(cu_seqlens), max_len, _ptr(q), _ptr(k), _ptr(v), _ptr(g),
+                                                     _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind, flags,
+                                                     _ptr(gate), _ptr(norm_w), eps, _ptr(out), _ptr(workspace), nbytes, _stream())
+        return _launched(code, "glm53f_kda_core_prefill_varlen_ws")
     code = ffi.glm53f_kda_core_prefill_varlen(heads, batch, _ptr(cu_seqlens), max_len, _ptr(q), _ptr(k), _ptr(v), _ptr(g),
                                               _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind, flags, _ptr(gate),
                                               _ptr(norm_w), eps, _ptr(out), _stream())

@@ -1,0 +1,663 @@
+// Chunk-64 tensor-core prefill in two passes over a caller-provided workspace, for launches with few (sequence,
+// head) chains: a single long sequence, or a GPU's shard of heads.
+//
+// The arithmetic is that of kda_prefill_tc.cu (same operand tiles, same products, same precision mix).  What
+// changes is where it runs.  Everything of a chunk that does not need the recurrent state -- the decay scan, the
+// operand tiles, L, M, the triangular inverse, W = T'Kg and U = T'V, about two thirds of a chunk's time -- is
+// independent from chunk to chunk, so `intra_kernel` spreads those (chain, chunk) items over every SM and leaves
+// per item, in the workspace, exactly what the state recurrence consumes: Qg, W, M, Kdec hi/lo (bf16 cell tiles),
+// U (FP32) and exp(G_last).  `state_kernel`, one block per chain, then walks the chunks in order with the state in
+// tensor memory and only the short dependent part per chunk: S as bf16 operand, QS = Qg S and -W S, D = U - W S,
+// O = QS + M D, S <- E_last S + Kdec^T D.  The two kernels alternate over segments of the sequence sized by the
+// workspace (stream order is the only synchronisation: no block ever waits on another block).
+//
+// Workspace slot of one (chain, chunk) item, bytes: Qg 0 | W 16,384 | M 32,768 | Kdec hi 40,960 | Kdec lo 57,344 |
+// U 73,728 (64 rows x 132 floats) | E_last 107,520 (128 floats); 108,544 per slot = 1,696 per row and head, inside
+// the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).
+
+#include "common.cuh"
+#include "glm53f_kda.h"
+#include "kda_internal.h"
+#include "prefill_common.cuh"
+#include "tc.cuh"
+
+namespace kda {
+namespace {
+
+using namespace pf;
+
+constexpr int US = 132;  // FP32 row stride of U (rows 4 banks apart, float4 aligned)
+constexpr int wQg = 0, wW = kTile, wMm = 2 * kTile, wKdHi = wMm + kTile / 2, wKdLo = wKdHi + kTile, wU = wKdLo + kTile;
+constexpr int wEgl = wU + CH * US * 4, kSlotBytes = 108544;
+static_assert(wEgl + 512 <= kSlotBytes && wU == 73728, "workspace slot layout");
+
+struct SpParams {
+    int H, batch;
+    const int32_t* cu;
+    const uint16_t *q, *k, *v;
+    const float* g;
+    const float* beta;
+    const void* state_in;   // segment 0 reads the caller's state, later segments the state written so far
+    void* state_out;
+    const long long* state_off;
+    int state_bf16;
+    const uint16_t* gate;
+    const uint16_t* norm_w;
+    float eps;
+    uint16_t* out;
+    unsigned char* ws;
+    int chunk0, seg_chunks;  // this segment: chunks [chunk0, chunk0 + seg_chunks) of every sequence
+    int* status;
+};
+
+__device__ __forceinline__ unsigned char* slot_of(const SpParams& p, int chain, int j) {
+    return p.ws + ((size_t)chain * p.seg_chunks + (j - p.chunk0)) * kSlotBytes;
+}
+
+// =====================================================================================================================
+// Pass 1: the state-independent part of every (chain, chunk) item of the segment, items spread over the grid.
+// =====================================================================================================================
+__global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_constant__ SpParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
+    uint64_t* bar_mma = bar_raw + 1;
+    uint64_t* bar_free = bar_raw + 2;
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    float* betas2 = reinterpret_cast<float*>(smem + oBeta);
+    float* egl = reinterpret_cast<float*>(smem + oEGL);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, cg = warp >> 2;
+    const int lane_row64 = quad * 16 + lane;
+    const int H = p.H, chains = p.batch * H;
+    const long long items = (long long)chains * p.seg_chunks;  // item = jj * chains + chain: chunk-major
+
+    if (tid == 0) {
+        mbar_init(bar_raw, 1);
+        mbar_init(bar_mma, 1);
+        mbar_init(bar_free, 1);
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+
+    // Decodes an item; returns false when the sequence has no such chunk.
+    auto decode = [&](long long item, int& chain, int& j, long long& gr0, int& n, int& h) -> bool {
+        chain = (int)(item % chains);
+        j = p.chunk0 + (int)(item / chains);
+        const int b = chain / H;
+        h = chain % H;
+        const int r0 = p.cu[b], T = p.cu[b + 1] - r0;
+        if ((long long)j * CH >= T) return false;
+        gr0 = (long long)r0 + (long long)j * CH;
+        n = min(CH, T - j * CH);
+        return true;
+    };
+
+    // ---- the loader warp ---------------------------------------------------------------------------------------------
+    if (warp == kCompute / 32) {
+        uint32_t free_phase = 0;
+        int it = 0;
+        for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+            int chain, j, n, h;
+            long long gr0;
+            if (!decode(item, chain, j, gr0, n, h)) continue;
+            if (it > 0) {
+                if (!mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
+                free_phase ^= 1u;
+            }
+            float* bt = betas2 + (it & 1) * CH;
+            for (int r = lane; r < CH; r += 32) {
+                bt[r] = r < n ? p.beta[(gr0 + r) * H + h] : 0.0f;
+                if (r >= n) {
+                    const uint4 z = make_uint4(0, 0, 0, 0);
+                    for (int e = 0; e < 16; ++e) {
+                        *reinterpret_cast<uint4*>(smem + oRawQ + r * RS16 + e * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + oRawK + r * RS16 + e * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + oRawV + r * RS16 + e * 16) = z;
+                    }
+                    for (int e = 0; e < 32; ++e) *reinterpret_cast<uint4*>(smem + oRawG + r * RS32 + e * 16) = z;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_expect_tx(bar_raw, (uint32_t)n * (3 * 256 + 512));
+            for (int r = lane; r < n; r += 32) {
+                const long long at = ((gr0 + r) * H + h) * DK;
+                bulk_load(smem + oRawQ + r * RS16, p.q + at, 256, bar_raw);
+                bulk_load(smem + oRawK + r * RS16, p.k + at, 256, bar_raw);
+                bulk_load(smem + oRawV + r * RS16, p.v + at, 256, bar_raw);
+                bulk_load(smem + oRawG + r * RS32, p.g + at, 512, bar_raw);
+            }
+            ++it;
+        }
+        tc::fence_before_sync();
+        __syncthreads();
+        return;
+    }
+
+    uint32_t raw_phase = 0, mma_phase = 0;
+    auto mma_round = [&](auto&& issue) -> bool {
+        if (tid == 0) {
+            issue();
+            tc::mma_commit(bar_mma);
+            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+        }
+        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) return false;
+        mma_phase ^= 1u;
+        tc::fence_after_sync();
+        return true;
+    };
+    auto publish_operands = [&]() {
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        compute_sync();
+        tc::fence_after_sync();
+    };
+
+    int it = 0;
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        int chain, j, n, h;
+        long long gr0;
+        if (!decode(item, chain, j, gr0, n, h)) continue;
+        unsigned char* slot = slot_of(p, chain, j);
+        const float* betas = betas2 + (it & 1) * CH;
+        ++it;
+        if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) break;
+        raw_phase ^= 1u;
+        // The previous item's bulk stores must have read their tiles before this item overwrites them.
+        if (tid == 0) bulk_wait_read<0>();
+        compute_sync();
+
+        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging buffer --------------------------
+        {
+            const int part = tid >> 7, d = tid & 127;
+            float* col = reinterpret_cast<float*>(smem + oRawG + (part * 16) * RS32) + d;
+            float* totals = reinterpret_cast<float*>(smem + oScan);
+            float loc[16], G = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                G += *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32);
+                loc[r] = G;
+            }
+            totals[part * 128 + d] = G;
+            compute_sync();
+            float base = 0.0f;
+            for (int q2 = 0; q2 < part; ++q2) base += totals[q2 * 128 + d];
+            float e = 1.0f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                e = __expf(base + loc[r]);
+                *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32) = e;
+            }
+            if (part == 3) {
+                egl[d] = e;
+                if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            }
+        }
+        compute_sync();
+
+        // ---- 2. operand tiles ------------------------------------------------------------------------------------------
+        {
+            const int r = tid & 63, cgrp = tid >> 6;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cgrp * 2 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
+                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
+                const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oRawV + r * RS16 + c * 16);
+                const float4 e0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
+                const float4 e1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
+                const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
+                const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
+                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
+                uint32_t kg[4], qg[4], ki[4], dh[4], dl[4];
+#pragma unroll
+                for (int u2 = 0; u2 < 4; ++u2) {
+                    const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
+                    const float qf[2] = {__uint_as_float(qw[u2] << 16), __uint_as_float(qw[u2] & 0xffff0000u)};
+                    float a[2], bq[2], ci[2], hi[2], lo[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float e = E[2 * u2 + u], einv = __fdividef(1.0f, e);
+                        a[u] = kf[u] * e;
+                        bq[u] = qf[u] * e;
+                        ci[u] = kf[u] * einv;
+                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * einv), hi[u], lo[u]);
+                    }
+                    kg[u2] = tc::bf16x2(a[0], a[1]);
+                    qg[u2] = tc::bf16x2(bq[0], bq[1]);
+                    ki[u2] = tc::bf16x2(ci[0], ci[1]);
+                    dh[u2] = tc::bf16x2(hi[0], hi[1]);
+                    dl[u2] = tc::bf16x2(lo[0], lo[1]);
+                }
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
+            }
+        }
+        publish_operands();
+        if (tid == 0) {
+            mbar_arrive(bar_free);  // the loader may stream the next item's rows in (it returns if there is none)
+            // Qg, Kdec hi/lo and exp(G_last) are final: out to the workspace while the rest of the item is computed.
+            bulk_store(slot + wQg, smem + oQg, kTile);
+            bulk_store(slot + wKdHi, smem + oKdHi, kTile);
+            bulk_store(slot + wKdLo, smem + oKdLo, kTile);
+            bulk_store(slot + wEgl, smem + oEGL, 512);
+            bulk_commit();
+        }
+
+        // ---- 3. L = Kg Kinv^T, M = Qg Kinv^T ----------------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+            })) break;
+
+        // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) --------------------------
+        {
+            uint32_t r[32];
+            const int half = cg & 1, i = lane_row64;
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg < 2 ? cL : cMm) + half * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
+                if (cg < 2) {
+                    float* Lr = reinterpret_cast<float*>(smem + oL) + i * LS + half * 32;
+                    const float bi = betas[i];
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) Lr[jj] = half * 32 + jj < i ? bi * __uint_as_float(r[jj]) : 0.0f;
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj)
+                        if (half * 32 + jj > i) r[jj] = 0u;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
+                }
+            }
+        }
+        compute_sync();
+
+        // ---- 5. T = (I + L)^-1 in FP32, T' = T diag(beta) as bf16 hi + lo cells ----------------------------------------------
+        {
+            const float* Lm = reinterpret_cast<const float*>(smem + oL);
+            float* Tm = reinterpret_cast<float*>(smem + oT);
+            float* Pm = reinterpret_cast<float*>(smem + oP);
+            for (int e = tid; e < CH * CH; e += kCompute) Tm[(e >> 6) * LS + (e & 63)] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
+            compute_sync();
+            invert_level<0>(Lm, Tm, Pm, tid);
+            invert_level<1>(Lm, Tm, Pm, tid);
+            invert_level<2>(Lm, Tm, Pm, tid);
+            invert_level<3>(Lm, Tm, Pm, tid);
+            invert_level<4>(Lm, Tm, Pm, tid);
+            invert_level<5>(Lm, Tm, Pm, tid);
+            const int i = tid & 63, c = tid >> 6;
+            float t8[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) t8[jj] = Tm[i * LS + c * 8 + jj] * betas[c * 8 + jj];
+            compute_sync();
+            uint32_t wh[4], wl[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                float h0, l0, h1, l1;
+                tc::split_bf16(t8[2 * jj], h0, l0);
+                tc::split_bf16(t8[2 * jj + 1], h1, l1);
+                wh[jj] = tc::bf16x2(h0, h1);
+                wl[jj] = tc::bf16x2(l0, l1);
+            }
+            *reinterpret_cast<uint4*>(cell(smem + oTpHi, CH, c, i)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+            *reinterpret_cast<uint4*>(cell(smem + oTpLo, CH, c, i)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+        }
+        publish_operands();
+
+        // ---- 6. W = T' Kg (bf16 T'), U = T' V (T' hi + lo) -------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cW, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oKg, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, true);
+            })) break;
+
+        // ---- 7. W as bf16 cells and U as FP32 rows (over Kg | Kinv | T', all dead), then M, W, U out to the workspace ----------
+        {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cW + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oW, CH, cg * 4 + cc, lane_row64)) = pack8(r + cc * 8);
+            }
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, cU + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
+                float* Ur = reinterpret_cast<float*>(smem + oKg) + lane_row64 * US + cg * 32;
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj)
+                    *reinterpret_cast<uint4*>(Ur + jj * 4) = make_uint4(r[jj * 4], r[jj * 4 + 1], r[jj * 4 + 2], r[jj * 4 + 3]);
+            }
+        }
+        publish_operands();
+        if (tid == 0) {
+            bulk_store(slot + wMm, smem + oMm, kTile / 2);
+            bulk_store(slot + wW, smem + oW, kTile);
+            bulk_store(slot + wU, smem + oKg, CH * US * 4);
+            bulk_commit();
+        }
+    }
+    if (tid == 0) bulk_wait_all<0>();
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
+}
+
+// =====================================================================================================================
+// Pass 2: the state recurrence of one chain over the segment's chunks, from the workspace.
+// =====================================================================================================================
+// Shared memory mirrors a workspace slot (three groups, each with its own full/empty barrier pair, refilled by the
+// loader warp as soon as the tensor core has consumed them), then S as bf16 cells and D hi/lo.
+constexpr int sSlot = 0, sS16 = kSlotBytes, sDhi = sS16 + 2 * kTile, sDlo = sDhi + kTile, sRed = sDlo + kTile;
+constexpr int sBars = sRed + 4 * CH * 4, sCtl = sBars + 64, kSmemState = sCtl + 32;
+constexpr uint32_t tS = 0, tQS = 128, tD = 256;
+
+__global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_constant__ SpParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + sBars);  // [3]
+    uint64_t* empty = full + 3;                                  // [3]
+    uint64_t* bar_mma = full + 6;
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + sCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, cg = warp >> 2;
+    const int lane_row128 = quad * 32 + lane, lane_row64 = quad * 16 + lane;
+    const int H = p.H, chain = blockIdx.x, b = chain / H, h = chain % H;
+    const long long row0 = p.cu[b];
+    const int T = p.cu[b + 1] - p.cu[b];
+    const int nch = (T + CH - 1) / CH;
+    const int j0 = p.chunk0, j1 = min(nch, p.chunk0 + p.seg_chunks);
+    const long long s_elem = p.state_off[b] + (long long)h * DV * DK;
+    // A chain with no chunk in this segment: only the first segment has anything to do (an empty sequence copies its state).
+    if (j0 >= j1 && !(j0 == 0 && p.state_out != p.state_in)) return;
+
+    if (tid == 0) {
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        mbar_init(bar_mma, 1);
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+
+    if (warp == kCompute / 32) {  // the loader warp
+        if (lane == 0) {
+            uint32_t ph = 1;  // the empty barriers start released
+            for (int j = j0; j < j1; ++j) {
+                const unsigned char* slot = slot_of(p, chain, j);
+                if (!mbar_wait(&empty[0], ph, ctx, kStatusWaitPrefill)) break;
+                mbar_arrive_expect_tx(&full[0], 2 * kTile + 512);
+                bulk_load(smem + sSlot + wQg, slot + wQg, 2 * kTile, &full[0]);
+                bulk_load(smem + sSlot + wEgl, slot + wEgl, 512, &full[0]);
+                if (!mbar_wait(&empty[1], ph, ctx, kStatusWaitPrefill)) break;
+                mbar_arrive_expect_tx(&full[1], CH * US * 4);
+                bulk_load(smem + sSlot + wU, slot + wU, CH * US * 4, &full[1]);
+                if (!mbar_wait(&empty[2], ph, ctx, kStatusWaitPrefill)) break;
+                mbar_arrive_expect_tx(&full[2], kTile / 2 + 2 * kTile);
+                bulk_load(smem + sSlot + wMm, slot + wMm, kTile / 2 + 2 * kTile, &full[2]);
+                ph ^= 1u;
+            }
+        }
+        tc::fence_before_sync();
+        __syncthreads();
+        return;
+    }
+
+    uint32_t mma_phase = 0, full_phase = 0;
+    bool alive = true;
+    auto mma_round = [&](auto&& issue) -> bool {
+        if (tid == 0) {
+            issue();
+            tc::mma_commit(bar_mma);
+            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+        }
+        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) return false;
+        mma_phase ^= 1u;
+        tc::fence_after_sync();
+        return true;
+    };
+    auto publish_operands = [&]() {
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        compute_sync();
+        tc::fence_after_sync();
+    };
+
+    // ---- the incoming state into tensor memory: lane = key channel, columns = value channel -----------------------
+    {
+        const void* src = j0 == 0 ? p.state_in : p.state_out;
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+            const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
+            r[j] = __float_as_uint(x);
+        }
+        tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+        tc::tmem_st_wait();
+    }
+
+    for (int j = j0; j < j1; ++j) {
+        const int n = min(CH, T - j * CH);
+        const long long gr0 = row0 + (long long)j * CH;
+        const float* egl = reinterpret_cast<const float*>(smem + sSlot + wEgl);
+
+        // ---- S as bf16 cells; the decayed S back to tensor memory ----------------------------------------------------
+        if (!mbar_wait(&full[0], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
+        {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (p.state_bf16) {
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(bf16_round(__uint_as_float(r[jj])));
+            }
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + sS16, 128, cg * 4 + cc, lane_row128)) = pack8(r + cc * 8);
+            const float el = egl[lane_row128];
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(__uint_as_float(r[jj]) * el);
+            tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+            tc::tmem_st_wait();
+        }
+        publish_operands();
+
+        // ---- QS = Qg S;  -W S ----------------------------------------------------------------------------------------
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + tQS, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + tD, tc::desc_kmajor_bf16(smem + sSlot + wW, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), idn, k0 > 0);
+            })) { alive = false; break; }
+        if (tid == 0) mbar_arrive(&empty[0]);  // Qg, W and exp(G_last) are consumed (the scale above read E_last before the round)
+
+        // ---- D = U - W S as bf16 hi + lo cells ---------------------------------------------------------------------------
+        if (!mbar_wait(&full[1], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
+        {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, tD + cg * 32), r);
+            tc::tmem_ld_wait();
+            if (lane < 16) {
+                const float* Ur = reinterpret_cast<const float*>(smem + sSlot + wU) + lane_row64 * US + cg * 32;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const float4 u0 = *reinterpret_cast<const float4*>(Ur + cc * 8), u1 = *reinterpret_cast<const float4*>(Ur + cc * 8 + 4);
+                    const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                    uint32_t wh[4], wl[4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        float h0, l0, h1, l1;
+                        tc::split_bf16(uu[2 * jj] + __uint_as_float(r[cc * 8 + 2 * jj]), h0, l0);
+                        tc::split_bf16(uu[2 * jj + 1] + __uint_as_float(r[cc * 8 + 2 * jj + 1]), h1, l1);
+                        wh[jj] = tc::bf16x2(h0, h1);
+                        wl[jj] = tc::bf16x2(l0, l1);
+                    }
+                    *reinterpret_cast<uint4*>(cell(smem + sDhi, CH, cg * 4 + cc, lane_row64)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4*>(cell(smem + sDlo, CH, cg * 4 + cc, lane_row64)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                }
+            }
+        }
+        publish_operands();
+        if (tid == 0) mbar_arrive(&empty[1]);
+
+        // ---- O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------
+        if (!mbar_wait(&full[2], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
+                const unsigned char* kdhi = smem + sSlot + wKdHi;
+                const unsigned char* kdlo = smem + sSlot + wKdLo;
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + tQS, tc::desc_kmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), id, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDlo, CH, 0, k0), ids, true);
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdlo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
+            })) { alive = false; break; }
+        if (tid == 0) mbar_arrive(&empty[2]);
+        full_phase ^= 1u;
+
+        // ---- outputs: bf16(y), or the gated RMSNorm of bf16(y) ------------------------------------------------------------------
+        {
+            uint32_t r[32];
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, tQS + cg * 32), r);
+            tc::tmem_ld_wait();
+            const int i = lane_row64;
+            const bool live = lane < 16 && i < n;
+            const long long at = ((gr0 + i) * H + h) * DV + cg * 32;
+            float y[32];
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) y[jj] = bf16_round(__uint_as_float(r[jj]));
+            if (p.gate != nullptr) {
+                float* red = reinterpret_cast<float*>(smem + sRed);
+                float ss = 0.0f;
+#pragma unroll
+                for (int jj = 0; jj < 32; ++jj) ss = fmaf(y[jj], y[jj], ss);
+                if (lane < 16) red[cg * CH + i] = ss;
+                compute_sync();
+                if (live) {
+                    const float tot = (red[i] + red[CH + i]) + (red[2 * CH + i] + red[3 * CH + i]);
+                    const float rinv = 1.0f / sqrtf(tot / (float)DV + p.eps);
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const float gt = bf16_bits_to_f32(p.gate[at + jj]), w = bf16_bits_to_f32(p.norm_w[cg * 32 + jj]);
+                        y[jj] = w * (y[jj] * rinv) * (1.0f / (1.0f + __expf(-gt)));
+                    }
+                }
+            }
+            if (live) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(p.out + at + c * 8) = make_uint4(tc::bf16x2(y[c * 8], y[c * 8 + 1]), tc::bf16x2(y[c * 8 + 2], y[c * 8 + 3]),
+                                                                            tc::bf16x2(y[c * 8 + 4], y[c * 8 + 5]), tc::bf16x2(y[c * 8 + 6], y[c * 8 + 7]));
+            }
+        }
+        tc::fence_before_sync();
+        compute_sync();
+        tc::fence_after_sync();
+    }
+
+    // ---- the outgoing state ---------------------------------------------------------------------------------------------
+    if (alive) {
+        uint32_t r[32];
+        tc::tmem_ld32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+            if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
+            else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
+}
+
+}  // namespace
+
+int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass) {
+    if (heads < 1 || batch < 1 || chunks_per_pass < 1) return 0;
+    return (int64_t)heads * batch * chunks_per_pass * kSlotBytes;
+}
+
+// The two passes over every segment of the longest sequence, in stream order.
+int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
+                           const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
+                           void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
+                           const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
+                           cudaStream_t stream) {
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemState);
+        if (e != cudaSuccess) return (int)e;
+        configured_dev = dev;
+    }
+    const long long chains = (long long)heads * batch;
+    long long seg = workspace_bytes / (chains * kSlotBytes);
+    if (seg < 1 || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return kInvalid;
+    const long long need = ((long long)max_len + CH - 1) / CH;
+    if (seg > need) seg = need > 0 ? need : 1;
+    SpParams p{};
+    p.H = heads; p.batch = batch; p.cu = cu_seqlens;
+    p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta;
+    p.state_in = state_in; p.state_out = state_out;
+    p.state_off = reinterpret_cast<const long long*>(state_off);
+    p.state_bf16 = bf16_state ? 1 : 0;
+    p.gate = gate; p.norm_w = norm_w; p.eps = eps; p.out = out;
+    p.ws = reinterpret_cast<unsigned char*>(workspace);
+    p.seg_chunks = (int)seg;
+    p.status = status_word();
+    if (p.status == nullptr) return (int)cudaErrorUnknown;
+    const int sms = sm_count();
+    for (long long c0 = 0; c0 == 0 || c0 < need; c0 += seg) {
+        p.chunk0 = (int)c0;
+        if (need > 0) {
+            const long long items = chains * seg;
+            intra_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsTc, kSmemTc, stream>>>(p);
+            const int rc = (int)cudaGetLastError();
+            if (rc != 0) return rc;
+        }
+        state_kernel<<<(unsigned)chains, kThreadsTc, kSmemState, stream>>>(p);
+        const int rc = (int)cudaGetLastError();
+        if (rc != 0) return rc;
+        if (need == 0) break;
+    }
+    return 0;
+}
+
+}  // namespace kda

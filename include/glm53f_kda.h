@@ -4,7 +4,7 @@
  * (crates/glm53f-kda/kernels/glm53f_kda.h:73-270, bound by crates/glm53f-kda/src/ffi.rs:16-287) with the
  * same names, argument order, types and meaning, so the reference's Rust `ffi` module links against this
  * library unchanged.  Part 2 adds the "core" entry points the benchmark configurations use (inputs after
- * the short convolution: q, k, v, log decay, beta) and one entry point for callers that cannot allocate.
+ * the short convolution: q, k, v, log decay, beta).
  *
  * Conventions shared by every entry point (reference header lines 5-9, 43-47):
  *   - raw device pointers, strides and offsets in ELEMENTS of the pointed-to type, a CUDA stream;
@@ -262,6 +262,25 @@ int glm53f_kda_core_prefill_varlen(int32_t heads, int32_t batch, const int32_t* 
                                    int32_t state_bf16, int32_t flags,
                                    const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
                                    glm53f_bf16* out, glm53f_stream_t stream);
+
+/* The same prefill in two passes over a caller-provided workspace, for launches with few (sequence, head) chains --
+ * one long sequence, or one GPU's shard of heads -- where one block per chain would leave most SMs idle: the part
+ * of every chunk that does not depend on the recurrent state is computed for many chunks at once on all SMs, then
+ * one block per chain runs the short state-dependent part chunk by chunk.  `workspace` (device memory, 16-byte
+ * aligned) holds 108,544 bytes per (sequence, head, chunk of 64 rows) in flight; its size sets how many chunks of
+ * every sequence one pass covers (at least one: glm53f_kda_core_prefill_workspace_bytes(heads, batch, 1)).
+ * Results do not depend on the workspace size and agree with glm53f_kda_core_prefill_varlen to rounding.  Inputs must be
+ * 16-byte aligned and flags must be 0 (status 1 otherwise).  Not in the reference; its own prefill takes a
+ * workspace the same way (reference glm53f_kda.h:198-204, 223-232). */
+int64_t glm53f_kda_core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass);
+int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
+                                      const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                      const float* g, const float* beta,
+                                      const void* state_in, void* state_out, const int64_t* state_off,
+                                      int32_t state_bf16, int32_t flags,
+                                      const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                      glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
+                                      glm53f_stream_t stream);
 
 /* Status word of the most recent launches on the current device: 0, or a code recorded by a kernel whose
  * bounded wait ran out (the kernel then returned early instead of spinning).  Reads and clears it;

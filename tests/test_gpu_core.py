@@ -179,7 +179,7 @@ def test_verify_then_commit_equals_serial_decode_bitwise(G, core, oracle, pkg, b
             assert np.array_equal(G.bits(committed[l * slots * per + offs[s]:l * slots * per + offs[s] + per]), G.bits(want)), (l, s)
 
 
-def prefill_case(G, core, oracle, synth, config, heads, lens, carried, bf16=False):
+def prefill_case(G, core, oracle, synth, config, heads, lens, carried, bf16=False, ws_chunks=None):
     o = oracle
     rows = sum(lens)
     tok = synth.tokens(config, 0, rows, heads)
@@ -193,13 +193,19 @@ def prefill_case(G, core, oracle, synth, config, heads, lens, carried, bf16=Fals
     d_state = G.dev_bf16(states) if bf16 else G.dev_f32(states)
     d_out = torch.full((rows * heads * DV + 32,), -1, dtype=torch.int16, device="cuda")
     d_cu, d_off = G.dev_i32(cu), G.dev_i64(offs)
-    core.prefill_varlen(heads, rows, d_cu, max(lens), dq, dk, dv, dg, db, d_state, d_off, out=d_out)
+    ws = None
+    if ws_chunks is not None:
+        ws = torch.empty(core.prefill_workspace_bytes(heads, len(lens), ws_chunks), dtype=torch.uint8, device="cuda")
+    core.prefill_varlen(heads, rows, d_cu, max(lens), dq, dk, dv, dg, db, d_state, d_off, out=d_out, workspace=ws)
     G.check_status()
     out = G.host_bf16(d_out)[:rows * heads * DV].reshape(rows, heads * DV)
     st = G.host_bf16(d_state) if bf16 else G.host_f32(d_state)
     q, k, v, g, beta = tok
     for i, n in enumerate(lens):
         r0 = cu[i]
+        if n == 0:  # an empty sequence keeps its state
+            assert np.array_equal(G.bits(st[offs[i]:offs[i] + per]), G.bits(states[offs[i]:offs[i] + per])), i
+            continue
         part = lambda a, w: a.reshape(rows, heads * w)[r0:r0 + n].reshape(-1)
         args = (heads, part(q, DK), part(k, DK), part(v, DV), part(g, DK), beta.reshape(rows, heads)[r0:r0 + n].reshape(-1),
                 states[offs[i]:offs[i] + per])
@@ -224,6 +230,24 @@ def test_prefill_single_sequence(G, core, oracle, pkg, t):
 def test_prefill_varlen_packed(G, core, oracle, pkg):
     lens = [300, 64, 1, 129, 77]
     prefill_case(G, core, oracle, pkg.synth, 2, 8, lens, [True, False, True, False, True])
+
+
+# The two-pass form over a workspace: the same results bit for bit whatever the workspace size (1 chunk per pass ..
+# everything at once), and the single-pass kernel's results to rounding (U - W S is summed in a different order).
+def test_prefill_two_pass_over_a_workspace(G, core, oracle, pkg):
+    lens = [300, 64, 1, 129, 0, 77]
+    carried = [True, False, True, False, True, True]
+    ref_out, ref_st = prefill_case(G, core, oracle, pkg.synth, 2, 4, lens, carried)
+    runs = [prefill_case(G, core, oracle, pkg.synth, 2, 4, lens, carried, ws_chunks=c) for c in (1, 2, 16)]
+    for out, st in runs[1:]:
+        assert np.array_equal(G.bits(out), G.bits(runs[0][0]))
+        assert np.array_equal(G.bits(st), G.bits(runs[0][1]))
+    assert G.max_abs(runs[0][0], ref_out) / G.max_abs(ref_out) <= 1.0 / 128.0
+    assert G.rel_l2(runs[0][1], ref_st) <= 1e-4
+
+
+def test_prefill_two_pass_bf16_state_and_long_sequence(G, core, oracle, pkg):
+    prefill_case(G, core, oracle, pkg.synth, 0, 2, [1100], [True], bf16=True, ws_chunks=4)
 
 
 def test_core_rejections(G, core, pkg):

@@ -14,6 +14,7 @@ from . import ffi
 
 DK = DV = 128
 L2NORM = 1
+STATIC_SCRATCH_SLOTS = 64  # chains the library's own scratch array can serve (one chunk per pass each)
 
 
 class Invalid(ValueError):
@@ -133,7 +134,9 @@ def prefill_workspace_bytes(heads, batch, chunks_per_pass):
 def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, state_off, *, state_out="in_place",
                    flags=0, gate=None, norm_w=None, eps=1e-5, out=None, workspace=None):
     """glm53f_kda_core_prefill_varlen: chunked prefill of packed variable-length sequences.  With `workspace` (a
-    CUDA uint8 tensor) the two-pass glm53f_kda_core_prefill_varlen_ws runs instead."""
+    CUDA uint8 tensor) the two-pass glm53f_kda_core_prefill_varlen_ws runs instead; with workspace="static" the
+    two passes run on the library's own fixed scratch array (glm53f_kda_core_prefill_varlen_static: for callers
+    that must not allocate; at most 64 (sequence, head) chains)."""
     batch = cu_seqlens.numel() - 1
     _need(cu_seqlens, "cu_seqlens", (torch.int32,), 2)
     _need(state_off, "state_off", (torch.int64,), batch)
@@ -142,6 +145,15 @@ def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, st
     so = state if isinstance(state_out, str) else state_out
     if so is None:
         raise Invalid("a prefill writes the state")
+    if isinstance(workspace, str):
+        if workspace != "static":
+            raise Invalid("workspace must be a tensor, None or \"static\"")
+        if heads * batch > STATIC_SCRATCH_SLOTS:
+            raise Invalid(f"the static scratch holds {STATIC_SCRATCH_SLOTS} (sequence, head) chains, got {heads * batch}")
+        code = ffi.glm53f_kda_core_prefill_varlen_static(heads, batch, _ptr(cu_seqlens), max_len, _ptr(q), _ptr(k), _ptr(v),
+                                                         _ptr(g), _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind,
+                                                         flags, _ptr(gate), _ptr(norm_w), eps, _ptr(out), _stream())
+        return _launched(code, "glm53f_kda_core_prefill_varlen_static")
     if workspace is not None:
         if not workspace.is_cuda or not workspace.is_contiguous():
             raise Invalid("workspace must be a contiguous CUDA tensor")

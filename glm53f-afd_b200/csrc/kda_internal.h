@@ -43,6 +43,12 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
                            const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
                            cudaStream_t stream);
 
+// The two-pass prefill on the library's own fixed scratch array (no workspace argument, nothing allocated).
+int core_prefill_static_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
+                               const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
+                               void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
+                               const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, cudaStream_t stream);
+
 int sm_count();
 
 // Device address of the status word kernels record a timed-out wait in (current device).

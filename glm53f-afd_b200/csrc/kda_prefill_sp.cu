@@ -660,4 +660,40 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same two-pass prefill for callers that may not allocate device memory at all.
+//
+// Some hosts of this library run inside a memory plan that is fixed before the first request: an inference engine
+// whose planner has handed every byte of HBM to weights, KV pages and state arenas, or a component running inside
+// somebody else's CUDA graph capture or allocator-locked region, where cudaMalloc would fail, fragment the plan or
+// break the capture.  Such a caller cannot produce the workspace glm53f_kda_core_prefill_varlen_ws asks for.  For
+// them the library carries its own scratch: a fixed array in device memory that exists as soon as the library is
+// loaded on a GPU (and is held by every GPU that loads it until the process exits), big enough for 64 workspace slots.
+constexpr int kStaticSlots = 64;
+constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes;  // 6,946,816 bytes
+static __device__ __align__(256) unsigned char g_prefill_scratch[kStaticScratchBytes];
+
+// The array's name is a host-side handle here, not a device address: the address a kernel can use is asked for once
+// per device (with that device current) and remembered.
+int core_prefill_static_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
+                               const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
+                               void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
+                               const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, cudaStream_t stream) {
+    constexpr int kMaxDevices = 64;
+    static void* scratch_of[kMaxDevices] = {};
+    if ((long long)heads * batch > kStaticSlots) return kInvalid;  // not even one chunk per pass would fit
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return kInvalid;
+    if (scratch_of[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_prefill_scratch);
+        if (e != cudaSuccess) return (int)e;
+        scratch_of[dev] = ptr;
+    }
+    return core_prefill_sp_launch(heads, batch, cu_seqlens, max_len, q, k, v, g, beta, state_in, state_out, state_off, bf16_state,
+                                  gate, norm_w, eps, out, scratch_of[dev], kStaticScratchBytes, stream);
+}
+
 }  // namespace kda

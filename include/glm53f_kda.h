@@ -282,6 +282,29 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
                                       glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
                                       glm53f_stream_t stream);
 
+/* No counterpart in the reference.  glm53f_kda_core_prefill_varlen_ws for callers that cannot call cudaMalloc: an
+ * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs
+ * where an allocation would fail or disturb its host (inside a stream capture, under an allocator lock).  It takes no
+ * workspace: the two passes run on a fixed array of 6,946,816 bytes (64 workspace slots) that lives in the library's
+ * device image, so every GPU on which the library is loaded holds that much until the process exits.
+ *   - Limit: heads * batch <= 64 (at least one chunk per pass must fit); more is rejected with status 1
+ *     (cudaErrorInvalidValue) before anything is enqueued.  A pass covers 64 / (heads * batch) chunks of every
+ *     sequence, so the entry point suits few chains: one sequence on one GPU's shard of heads.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
+ *     current) and remembers it; make that first call outside any stream capture.
+ *   - The call allocates and frees nothing.
+ *   - All calls on a device share the one array.  Its contents are scratch (every slot is written before it is read,
+ *     nothing needs clearing, nothing survives a call), so calls that overlap on the GPU -- different streams,
+ *     or different processes' threads on one context -- race; keep calls on one device in stream order.
+ * Arguments and results otherwise as glm53f_kda_core_prefill_varlen_ws (bit for bit). */
+int glm53f_kda_core_prefill_varlen_static(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
+                                          const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                          const float* g, const float* beta,
+                                          const void* state_in, void* state_out, const int64_t* state_off,
+                                          int32_t state_bf16, int32_t flags,
+                                          const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                          glm53f_bf16* out, glm53f_stream_t stream);
+
 /* Status word of the most recent launches on the current device: 0, or a code recorded by a kernel whose
  * bounded wait ran out (the kernel then returned early instead of spinning).  Reads and clears it;
  * synchronises the device.  Not in the reference (its kernels have no device-side waits). */

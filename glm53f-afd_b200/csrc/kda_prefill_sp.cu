@@ -664,11 +664,14 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
 // The same two-pass prefill for callers that may not allocate device memory at all.
 //
 // Some hosts of this library run inside a memory plan that is fixed before the first request: an inference engine
-// whose planner has handed every byte of HBM to weights, KV pages and state arenas, or a component running inside
-// somebody else's CUDA graph capture or allocator-locked region, where cudaMalloc would fail, fragment the plan or
-// break the capture.  Such a caller cannot produce the workspace glm53f_kda_core_prefill_varlen_ws asks for.  For
-// them the library carries its own scratch: a fixed array in device memory that exists as soon as the library is
-// loaded on a GPU (and is held by every GPU that loads it until the process exits), big enough for 64 workspace slots.
+// whose planner has handed every byte of HBM to weights, KV pages and state arenas, or a component called from a
+// region of its host where allocation is forbidden (an allocator lock held, a latency-critical loop), where cudaMalloc
+// would fail, fragment the plan or stall.  Such a caller cannot produce the workspace
+// glm53f_kda_core_prefill_varlen_ws asks for.  For them the library carries its own scratch: a fixed array in device
+// memory that exists as soon as the library is loaded on a GPU (and is held by every GPU that loads it until the
+// process exits), big enough for 64 workspace slots.  Nothing in it has to start at zero: the first pass writes every
+// byte of a slot that the second pass reads.  All calls share the one array, so two calls in flight at once (two
+// streams, two threads) overwrite each other's slots; the caller serialises them.
 constexpr int kStaticSlots = 64;
 constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes;  // 6,946,816 bytes
 static __device__ __align__(256) unsigned char g_prefill_scratch[kStaticScratchBytes];

@@ -124,6 +124,14 @@ __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src,
                  "r"(bytes)
                  : "memory");
 }
+// Tiled tensor copy (rank 3) of one box into this block's shared memory; `tmap` points at a CUtensorMap in the kernel's
+// parameters.  x (the innermost coordinate) times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tensor_load_3d(void* smem_dst, const void* tmap, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {

@@ -27,6 +27,7 @@
 // Reference lines restated here: kernels/kda.cu:38-53 (update), 98-210 (chain_kernel), 214-253 (replay_kernel),
 // 290-460 (argument checks and entry points).
 
+#include <cstdlib>
 #include "common.cuh"
 #include "glm53f_kda.h"
 #include "kda_internal.h"
@@ -821,6 +822,11 @@ __global__ void __launch_bounds__(kThreads, 1) recurrent_kernel(const __grid_con
         mbar_init_fence();
     }
     __syncthreads();
+    // Programmatic dependent launch: let the next kernel of the stream be scheduled onto SMs as this grid's blocks
+    // retire (its block set-up then overlaps this grid's tail), and do not touch global memory before every earlier
+    // grid of the stream has completed and flushed.  Both are no-ops for a launch without the attribute.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const WaitCtx ctx{ctl, ctl + 1, &g_status};
     if (warp < kRecWarps) {
         recurrence_role<S, MODE>(p, smem, bars, ctx, warp, lane);
@@ -859,8 +865,23 @@ int launch(const Params& p, cudaStream_t stream) {
     const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
     Params q = p;
     q.neg_zero2 = 0x8000000080000000ull;
-    recurrent_kernel<S, MODE><<<grid, kThreads, L::kBytes, stream>>>(q);
-    return (int)cudaGetLastError();
+    // Launched with programmatic stream serialization: the kernel itself waits for its predecessors before its first
+    // global access, so ordering is what a plain launch gives.  GLM53F_KDA_PDL=0 selects a plain launch.
+    static const bool pdl = [] {
+        const char* v = getenv("GLM53F_KDA_PDL");
+        return !(v && v[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, recurrent_kernel<S, MODE>, q);
 }
 
 template <int MODE>

@@ -15,6 +15,8 @@
 // U 73,728 (64 rows x 132 floats) | E_last 107,520 (128 floats); 108,544 per slot = 1,696 per row and head, inside
 // the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "glm53f_kda.h"
 #include "kda_internal.h"
@@ -31,7 +33,17 @@ constexpr int wQg = 0, wW = kTile, wMm = 2 * kTile, wKdHi = wMm + kTile / 2, wKd
 constexpr int wEgl = wU + CH * US * 4, kSlotBytes = 108544;
 static_assert(wEgl + 512 <= kSlotBytes && wU == 73728, "workspace slot layout");
 
+// Staging of a chunk's raw rows in the intra kernel: dense boxes of 64 rows x 128 bytes written by tiled tensor copies
+// with the 128-byte swizzle (16-byte piece p of row r sits at piece p ^ (r & 7)), so that threads walking down the
+// rows of one column spread over all banks.  q, k, v: two boxes each (channels 0-63, 64-127); the log decays: four.
+constexpr int kBox = CH * 128;  // 8 KiB
+constexpr int oBoxQ = 0, oBoxK = 2 * kBox, oBoxV = 4 * kBox, oBoxG = 6 * kBox;
+static_assert(oBoxG + 4 * kBox <= oKg, "raw staging must end below the operand tiles");
+// Byte offset inside a tensor's staging of the 16-byte piece `piece` (0..15 for bf16 rows, 0..31 for f32 rows) of row r.
+__device__ __forceinline__ int box_piece(int r, int piece) { return (piece >> 3) * kBox + r * 128 + (((piece & 7) ^ (r & 7)) << 4); }
+
 struct SpParams {
+    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_g;  // [rows][H][128] as (128, H, rows); boxes of 64 rows x 128 bytes
     int H, batch;
     const int32_t* cu;
     const uint16_t *q, *k, *v;
@@ -101,6 +113,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
     };
 
     // ---- the loader warp ---------------------------------------------------------------------------------------------
+    // A full chunk arrives by ten tiled tensor copies issued by one lane.  A sequence's last, partial chunk is copied
+    // by the warp's own loads and stores instead (rows past the sequence's end are not read, they become zero), so no
+    // copy ever reaches past the rows the caller's metadata names.
     if (warp == kCompute / 32) {
         uint32_t free_phase = 0;
         int it = 0;
@@ -108,31 +123,45 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
             int chain, j, n, h;
             long long gr0;
             if (!decode(item, chain, j, gr0, n, h)) continue;
+            float b0 = 0.0f, b1 = 0.0f;
+            if (lane < n) b0 = p.beta[(gr0 + lane) * H + h];
+            if (lane + 32 < n) b1 = p.beta[(gr0 + lane + 32) * H + h];
             if (it > 0) {
                 if (!mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
                 free_phase ^= 1u;
             }
             float* bt = betas2 + (it & 1) * CH;
-            for (int r = lane; r < CH; r += 32) {
-                bt[r] = r < n ? p.beta[(gr0 + r) * H + h] : 0.0f;
-                if (r >= n) {
-                    const uint4 z = make_uint4(0, 0, 0, 0);
-                    for (int e = 0; e < 16; ++e) {
-                        *reinterpret_cast<uint4*>(smem + oRawQ + r * RS16 + e * 16) = z;
-                        *reinterpret_cast<uint4*>(smem + oRawK + r * RS16 + e * 16) = z;
-                        *reinterpret_cast<uint4*>(smem + oRawV + r * RS16 + e * 16) = z;
+            bt[lane] = b0;
+            bt[lane + 32] = b1;
+            if (n == CH) {
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar_raw, 10u * kBox);
+                    const int row = (int)gr0;
+                    for (int x = 0; x < 2; ++x) {
+                        tensor_load_3d(smem + oBoxQ + x * kBox, &p.tm_q, x * 64, h, row, bar_raw);
+                        tensor_load_3d(smem + oBoxK + x * kBox, &p.tm_k, x * 64, h, row, bar_raw);
+                        tensor_load_3d(smem + oBoxV + x * kBox, &p.tm_v, x * 64, h, row, bar_raw);
                     }
-                    for (int e = 0; e < 32; ++e) *reinterpret_cast<uint4*>(smem + oRawG + r * RS32 + e * 16) = z;
+                    for (int x = 0; x < 4; ++x) tensor_load_3d(smem + oBoxG + x * kBox, &p.tm_g, x * 32, h, row, bar_raw);
                 }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(bar_raw, (uint32_t)n * (3 * 256 + 512));
-            for (int r = lane; r < n; r += 32) {
-                const long long at = ((gr0 + r) * H + h) * DK;
-                bulk_load(smem + oRawQ + r * RS16, p.q + at, 256, bar_raw);
-                bulk_load(smem + oRawK + r * RS16, p.k + at, 256, bar_raw);
-                bulk_load(smem + oRawV + r * RS16, p.v + at, 256, bar_raw);
-                bulk_load(smem + oRawG + r * RS32, p.g + at, 512, bar_raw);
+            } else {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+                for (int e = lane; e < CH * 16; e += 32) {
+                    const int r = e >> 4, piece = e & 15;
+                    const long long at = ((gr0 + r) * H + h) * DK + piece * 8;
+                    const bool in = r < n;
+                    *reinterpret_cast<uint4*>(smem + oBoxQ + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.q + at) : z;
+                    *reinterpret_cast<uint4*>(smem + oBoxK + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.k + at) : z;
+                    *reinterpret_cast<uint4*>(smem + oBoxV + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.v + at) : z;
+                }
+                for (int e = lane; e < CH * 32; e += 32) {
+                    const int r = e >> 5, piece = e & 31;
+                    const long long at = ((gr0 + r) * H + h) * DK + piece * 4;
+                    *reinterpret_cast<uint4*>(smem + oBoxG + box_piece(r, piece)) = r < n ? *reinterpret_cast<const uint4*>(p.g + at) : z;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_raw);
             }
             ++it;
         }
@@ -177,12 +206,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
         // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging buffer --------------------------
         {
             const int part = tid >> 7, d = tid & 127;
-            float* col = reinterpret_cast<float*>(smem + oRawG + (part * 16) * RS32) + d;
+            unsigned char* gbox = smem + oBoxG + (d & 3) * 4;
             float* totals = reinterpret_cast<float*>(smem + oScan);
             float loc[16], G = 0.0f;
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
-                G += *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32);
+                G += *reinterpret_cast<float*>(gbox + box_piece(part * 16 + r, d >> 2));
                 loc[r] = G;
             }
             totals[part * 128 + d] = G;
@@ -193,7 +222,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
                 e = __expf(base + loc[r]);
-                *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32) = e;
+                *reinterpret_cast<float*>(gbox + box_piece(part * 16 + r, d >> 2)) = e;
             }
             if (part == 3) {
                 egl[d] = e;
@@ -208,11 +237,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 const int c = cgrp * 2 + cc;
-                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
-                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
-                const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oRawV + r * RS16 + c * 16);
-                const float4 e0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
-                const float4 e1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
+                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oBoxK + box_piece(r, c));
+                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oBoxQ + box_piece(r, c));
+                const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oBoxV + box_piece(r, c));
+                const float4 e0 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c));
+                const float4 e1 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c + 1));
                 const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
                 const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
                 const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
@@ -607,6 +636,32 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
 
 }  // namespace
 
+// The driver's tensor-map encoder, looked up once through the runtime (the library does not link libcuda).
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiled>(f);
+    }();
+    return fn;
+}
+
+// A [rows][H][128] tensor of `elem`-byte elements as (128, H, rows) with boxes of 64 rows of one head, 128 bytes wide.
+static bool row_tensor_map(CUtensorMap* tm, const void* base, int elem, int H, long long rows) {
+    EncodeTiled enc = encode_tiled();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)DK, (cuuint64_t)H, (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)DK * elem, (cuuint64_t)H * DK * elem};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / elem), 1u, (cuuint32_t)CH};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(tm, elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass) {
     if (heads < 1 || batch < 1 || chunks_per_pass < 1) return 0;
     return (int64_t)heads * batch * chunks_per_pass * kSlotBytes;
@@ -643,6 +698,13 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     p.seg_chunks = (int)seg;
     p.status = status_word();
     if (p.status == nullptr) return (int)cudaErrorUnknown;
+    // Tensor copies fetch full chunks only, whose rows the caller's metadata vouches for; the extent written into the
+    // maps is the most rows the batch can hold.
+    long long rows_cap = (long long)batch * max_len;
+    rows_cap = rows_cap < CH ? CH : (rows_cap > 0x7fffffffll ? 0x7fffffffll : rows_cap);
+    if (!row_tensor_map(&p.tm_q, q, 2, heads, rows_cap) || !row_tensor_map(&p.tm_k, k, 2, heads, rows_cap) ||
+        !row_tensor_map(&p.tm_v, v, 2, heads, rows_cap) || !row_tensor_map(&p.tm_g, g, 4, heads, rows_cap))
+        return (int)cudaErrorNotSupported;
     const int sms = sm_count();
     for (long long c0 = 0; c0 == 0 || c0 < need; c0 += seg) {
         p.chunk0 = (int)c0;

@@ -247,7 +247,7 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
                      "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
                                 "flop_per_token": PREFILL_FLOP_PER_TOKEN},
                      "algorithmic_bytes_per_token": PREFILL_BYTES_PER_TOKEN,
-                     "kernel": "intra_kernel + state_kernel" if ws_chunks > 0 else "prefill_tc_kernel",
+                     "kernel": "prefill_sp_kernel (state role + intra role)" if ws_chunks > 0 else "prefill_tc_kernel",
                      "workspace_bytes": 0 if ws is None else ws.numel()},
         "gpu_launches": passes,
         "collective": None if world == 1 else {"op": "all_gather of per-head outputs", "bytes_received_per_gpu": tokens * (HEADS - hl) * DK * 2,
@@ -298,7 +298,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
-    ap.add_argument("--prefill-ws-chunks", type=int, default=32, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
+    ap.add_argument("--prefill-ws-chunks", type=int, default=128, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -4,16 +4,21 @@
 // The arithmetic is that of kda_prefill_tc.cu (same operand tiles, same products, same precision mix).  What
 // changes is where it runs.  Everything of a chunk that does not need the recurrent state -- the decay scan, the
 // operand tiles, L, M, the triangular inverse, W = T'Kg and U = T'V, about two thirds of a chunk's time -- is
-// independent from chunk to chunk, so `intra_kernel` spreads those (chain, chunk) items over every SM and leaves
+// independent from chunk to chunk, so the *intra role* spreads those (chain, chunk) items over every SM and leaves
 // per item, in the workspace, exactly what the state recurrence consumes: Qg, W, M, Kdec hi/lo (bf16 cell tiles),
-// U (FP32) and exp(G_last).  `state_kernel`, one block per chain, then walks the chunks in order with the state in
+// U (FP32) and exp(G_last).  The *state role*, one block per chain, walks the chunks in order with the state in
 // tensor memory and only the short dependent part per chunk: S as bf16 operand, QS = Qg S and -W S, D = U - W S,
-// O = QS + M D, S <- E_last S + Kdec^T D.  The two kernels alternate over segments of the sequence sized by the
-// workspace (stream order is the only synchronisation: no block ever waits on another block).
+// O = QS + M D, S <- E_last S + Kdec^T D.
+//
+// The sequence is cut into segments sized by the workspace.  One kernel launch runs the state role for segment s-1
+// (blocks 0..chains-1) and the intra role for segment s (every block, the chain blocks after their state work; items
+// are handed out through a counter in the workspace), on two halves of the workspace that swap from launch to
+// launch.  Stream order between launches is the only synchronisation: no block ever waits on another block.
 //
 // Workspace slot of one (chain, chunk) item, bytes: Qg 0 | W 16,384 | M 32,768 | Kdec hi 40,960 | Kdec lo 57,344 |
 // U 73,728 (64 rows x 132 floats) | E_last 107,520 (128 floats); 108,544 per slot = 1,696 per row and head, inside
-// the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).
+// the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).  The last
+// 256 bytes of the workspace hold the two item counters.
 
 #include <cuda.h>
 
@@ -57,25 +62,34 @@ struct SpParams {
     const uint16_t* norm_w;
     float eps;
     uint16_t* out;
-    unsigned char* ws;
-    int chunk0, seg_chunks;  // this segment: chunks [chunk0, chunk0 + seg_chunks) of every sequence
+    int seg_chunks;          // chunks of every sequence per segment = slots per chain in a workspace half
+    unsigned char* ws_intra; // intra role: chunks [intra_chunk0, intra_chunk0 + seg_chunks) of every sequence, or none
+    int intra_chunk0, has_intra;
+    unsigned char* ws_state; // state role: chunks [state_chunk0, state_chunk0 + seg_chunks) of every sequence, or none
+    int state_chunk0, has_state;
+    unsigned int* counters;  // [2] item counters: this launch hands items out of counters[ctr], and zeroes the other
+    int ctr;
     int* status;
 };
 
-__device__ __forceinline__ unsigned char* slot_of(const SpParams& p, int chain, int j) {
-    return p.ws + ((size_t)chain * p.seg_chunks + (j - p.chunk0)) * kSlotBytes;
+__device__ __forceinline__ unsigned char* slot_of(unsigned char* ws, int seg_chunks, int chain, int jj) {
+    return ws + ((size_t)chain * seg_chunks + jj) * kSlotBytes;
 }
+
+// Barriers of the two roles live apart (the state role's behind the intra role's shared-memory map), are set up once
+// per block and are never repurposed.
+constexpr int oBarsState = kSmemTc, kSmemSp = kSmemTc + 64;
+static_assert(kSmemSp <= 232448, "shared memory budget");
 
 // =====================================================================================================================
 // Pass 1: the state-independent part of every (chain, chunk) item of the segment, items spread over the grid.
 // =====================================================================================================================
-__global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_constant__ SpParams p) {
-    extern __shared__ __align__(1024) unsigned char smem[];
+__device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_t tm) {
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
     uint64_t* bar_mma = bar_raw + 1;
     uint64_t* bar_free = bar_raw + 2;
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
-    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    volatile int* item2 = reinterpret_cast<volatile int*>(smem + oCtl) + 4;  // the item of each staging generation
     float* betas2 = reinterpret_cast<float*>(smem + oBeta);
     float* egl = reinterpret_cast<float*>(smem + oEGL);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -83,26 +97,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
     const int lane_row64 = quad * 16 + lane;
     const int H = p.H, chains = p.batch * H;
     const long long items = (long long)chains * p.seg_chunks;  // item = jj * chains + chain: chunk-major
-
-    if (tid == 0) {
-        mbar_init(bar_raw, 1);
-        mbar_init(bar_mma, 1);
-        mbar_init(bar_free, 1);
-        ctl[0] = 0u;
-        ctl[1] = 0u;
-        mbar_init_fence();
-    }
-    if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
-    tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
-    const uint32_t tm = *tmem_slot;
     const WaitCtx ctx{ctl, ctl + 1, p.status};
 
     // Decodes an item; returns false when the sequence has no such chunk.
     auto decode = [&](long long item, int& chain, int& j, long long& gr0, int& n, int& h) -> bool {
         chain = (int)(item % chains);
-        j = p.chunk0 + (int)(item / chains);
+        j = p.intra_chunk0 + (int)(item / chains);
         const int b = chain / H;
         h = chain % H;
         const int r0 = p.cu[b], T = p.cu[b + 1] - r0;
@@ -119,10 +119,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
     if (warp == kCompute / 32) {
         uint32_t free_phase = 0;
         int it = 0;
-        for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-            int chain, j, n, h;
-            long long gr0;
-            if (!decode(item, chain, j, gr0, n, h)) continue;
+        for (;;) {
+            long long item = 0;
+            if (lane == 0) item = atomicAdd(&p.counters[p.ctr], 1u);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            int chain = 0, j = 0, n = 0, h = 0;
+            long long gr0 = 0;
+            const bool last = item >= items;
+            if (!last && !decode(item, chain, j, gr0, n, h)) continue;
+            if (last) {  // tell the compute warps that there is nothing more
+                if (it > 0 && !mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
+                if (lane == 0) {
+                    item2[it & 1] = -1;
+                    mbar_arrive(bar_raw);
+                }
+                break;
+            }
             float b0 = 0.0f, b1 = 0.0f;
             if (lane < n) b0 = p.beta[(gr0 + lane) * H + h];
             if (lane + 32 < n) b1 = p.beta[(gr0 + lane + 32) * H + h];
@@ -133,6 +145,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
             float* bt = betas2 + (it & 1) * CH;
             bt[lane] = b0;
             bt[lane + 32] = b1;
+            if (lane == 0) item2[it & 1] = (int)item;
             if (n == CH) {
                 __syncwarp();
                 if (lane == 0) {
@@ -189,16 +202,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
         tc::fence_after_sync();
     };
 
-    int it = 0;
-    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-        int chain, j, n, h;
-        long long gr0;
-        if (!decode(item, chain, j, gr0, n, h)) continue;
-        unsigned char* slot = slot_of(p, chain, j);
-        const float* betas = betas2 + (it & 1) * CH;
-        ++it;
+    for (int it = 0;; ++it) {
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) break;
         raw_phase ^= 1u;
+        const int item = item2[it & 1];
+        if (item < 0) break;
+        int chain, j, n, h;
+        long long gr0;
+        decode(item, chain, j, gr0, n, h);
+        unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, j - p.intra_chunk0);
+        const float* betas = betas2 + (it & 1) * CH;
         // The previous item's bulk stores must have read their tiles before this item overwrites them.
         if (tid == 0) bulk_wait_read<0>();
         compute_sync();
@@ -390,7 +403,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
     if (tid == 0) bulk_wait_all<0>();
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
 }
 
 // =====================================================================================================================
@@ -399,50 +411,32 @@ __global__ void __launch_bounds__(kThreadsTc, 1) intra_kernel(const __grid_const
 // Shared memory mirrors a workspace slot (three groups, each with its own full/empty barrier pair, refilled by the
 // loader warp as soon as the tensor core has consumed them), then S as bf16 cells and D hi/lo.
 constexpr int sSlot = 0, sS16 = kSlotBytes, sDhi = sS16 + 2 * kTile, sDlo = sDhi + kTile, sRed = sDlo + kTile;
-constexpr int sBars = sRed + 4 * CH * 4, sCtl = sBars + 64, kSmemState = sCtl + 32;
-constexpr uint32_t tS = 0, tQS = 128, tD = 256;
+static_assert(sRed + 4 * CH * 4 <= oBars, "state role shared memory");
+constexpr uint32_t tS = 0, tQS = 128, tD = 256, tQS1 = 384;  // QS/O accumulators alternate between chunks
 
-__global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_constant__ SpParams p) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + sBars);  // [3]
-    uint64_t* empty = full + 3;                                  // [3]
+__device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain) {
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + oBarsState);  // [3]
+    uint64_t* empty = full + 3;                                       // [3]
     uint64_t* bar_mma = full + 6;
-    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + sCtl);
-    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, cg = warp >> 2;
     const int lane_row128 = quad * 32 + lane, lane_row64 = quad * 16 + lane;
-    const int H = p.H, chain = blockIdx.x, b = chain / H, h = chain % H;
+    const int H = p.H, b = chain / H, h = chain % H;
     const long long row0 = p.cu[b];
     const int T = p.cu[b + 1] - p.cu[b];
     const int nch = (T + CH - 1) / CH;
-    const int j0 = p.chunk0, j1 = min(nch, p.chunk0 + p.seg_chunks);
+    const int j0 = p.state_chunk0, j1 = min(nch, p.state_chunk0 + p.seg_chunks);
     const long long s_elem = p.state_off[b] + (long long)h * DV * DK;
     // A chain with no chunk in this segment: only the first segment has anything to do (an empty sequence copies its state).
     if (j0 >= j1 && !(j0 == 0 && p.state_out != p.state_in)) return;
-
-    if (tid == 0) {
-        for (int i = 0; i < 3; ++i) {
-            mbar_init(&full[i], 1);
-            mbar_init(&empty[i], 1);
-        }
-        mbar_init(bar_mma, 1);
-        ctl[0] = 0u;
-        ctl[1] = 0u;
-        mbar_init_fence();
-    }
-    if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
-    tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
-    const uint32_t tm = *tmem_slot;
     const WaitCtx ctx{ctl, ctl + 1, p.status};
 
     if (warp == kCompute / 32) {  // the loader warp
         if (lane == 0) {
             uint32_t ph = 1;  // the empty barriers start released
             for (int j = j0; j < j1; ++j) {
-                const unsigned char* slot = slot_of(p, chain, j);
+                const unsigned char* slot = slot_of(p.ws_state, p.seg_chunks, chain, j - j0);
                 if (!mbar_wait(&empty[0], ph, ctx, kStatusWaitPrefill)) break;
                 mbar_arrive_expect_tx(&full[0], 2 * kTile + 512);
                 bulk_load(smem + sSlot + wQg, slot + wQg, 2 * kTile, &full[0]);
@@ -461,14 +455,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
         return;
     }
 
-    uint32_t mma_phase = 0, full_phase = 0;
+    uint32_t mma_phase = 0;
     bool alive = true;
-    auto mma_round = [&](auto&& issue) -> bool {
+    auto mma_issue = [&](auto&& issue) {
         if (tid == 0) {
             issue();
             tc::mma_commit(bar_mma);
             atomicAdd(const_cast<uint32_t*>(ctl), 1u);
         }
+    };
+    auto mma_wait = [&]() -> bool {
         if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) return false;
         mma_phase ^= 1u;
         tc::fence_after_sync();
@@ -480,28 +476,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
         compute_sync();
         tc::fence_after_sync();
     };
-
-    // ---- the incoming state into tensor memory: lane = key channel, columns = value channel -----------------------
-    {
-        const void* src = j0 == 0 ? p.state_in : p.state_out;
-        uint32_t r[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
-            const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
-            r[j] = __float_as_uint(x);
-        }
-        tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
-        tc::tmem_st_wait();
-    }
-
-    for (int j = j0; j < j1; ++j) {
-        const int n = min(CH, T - j * CH);
-        const long long gr0 = row0 + (long long)j * CH;
+    // S as bf16 cells for chunk c's products, the decayed S back to tensor memory, then QS = Qg S and -W S are started
+    // (not waited for) into the chunk's accumulators.
+    auto begin_chunk = [&](int c) -> bool {
+        if (!mbar_wait(&full[0], (uint32_t)(c & 1), ctx, kStatusWaitPrefill)) return false;
         const float* egl = reinterpret_cast<const float*>(smem + sSlot + wEgl);
-
-        // ---- S as bf16 cells; the decayed S back to tensor memory ----------------------------------------------------
-        if (!mbar_wait(&full[0], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
         {
             uint32_t r[32];
             tc::tmem_ld32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
@@ -519,19 +498,44 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
             tc::tmem_st_wait();
         }
         publish_operands();
+        const uint32_t tO = (c & 1) ? tQS1 : tQS;
+        mma_issue([&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + tD, tc::desc_kmajor_bf16(smem + sSlot + wW, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), idn, k0 > 0);
+        });
+        return true;
+    };
 
-        // ---- QS = Qg S;  -W S ----------------------------------------------------------------------------------------
-        if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + tQS, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + tD, tc::desc_kmajor_bf16(smem + sSlot + wW, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), idn, k0 > 0);
-            })) { alive = false; break; }
-        if (tid == 0) mbar_arrive(&empty[0]);  // Qg, W and exp(G_last) are consumed (the scale above read E_last before the round)
+    // ---- the incoming state into tensor memory: lane = key channel, columns = value channel -----------------------
+    {
+        const void* src = j0 == 0 ? p.state_in : p.state_out;
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+            const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
+            r[j] = __float_as_uint(x);
+        }
+        tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+        tc::tmem_st_wait();
+    }
+    tc::fence_before_sync();
+    compute_sync();
+    tc::fence_after_sync();
+    if (j0 < j1 && !begin_chunk(0)) alive = false;
+
+    for (int j = j0; alive && j < j1; ++j) {
+        const int c = j - j0, n = min(CH, T - j * CH);
+        const uint32_t par = (uint32_t)(c & 1), tO = (c & 1) ? tQS1 : tQS;
+        const long long gr0 = row0 + (long long)j * CH;
+        if (!mma_wait()) { alive = false; break; }
+        if (tid == 0) mbar_arrive(&empty[0]);  // Qg, W and exp(G_last) are consumed (begin_chunk read E_last before the products)
 
         // ---- D = U - W S as bf16 hi + lo cells ---------------------------------------------------------------------------
-        if (!mbar_wait(&full[1], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
+        if (!mbar_wait(&full[1], par, ctx, kStatusWaitPrefill)) { alive = false; break; }
         {
             uint32_t r[32];
             tc::tmem_ld32(tc::tmem_addr(tm, quad, tD + cg * 32), r);
@@ -560,27 +564,30 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
         if (tid == 0) mbar_arrive(&empty[1]);
 
         // ---- O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------
-        if (!mbar_wait(&full[2], full_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
-        if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
-                const unsigned char* kdhi = smem + sSlot + wKdHi;
-                const unsigned char* kdlo = smem + sSlot + wKdLo;
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + tQS, tc::desc_kmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), id, true);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDlo, CH, 0, k0), ids, true);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdlo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
-            })) { alive = false; break; }
+        if (!mbar_wait(&full[2], par, ctx, kStatusWaitPrefill)) { alive = false; break; }
+        mma_issue([&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
+            const unsigned char* kdhi = smem + sSlot + wKdHi;
+            const unsigned char* kdlo = smem + sSlot + wKdLo;
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), id, true);
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDlo, CH, 0, k0), ids, true);
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdlo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
+        });
+        if (!mma_wait()) { alive = false; break; }
         if (tid == 0) mbar_arrive(&empty[2]);
-        full_phase ^= 1u;
+
+        // The next chunk's first products run on the tensor core while this chunk's outputs leave.
+        if (j + 1 < j1 && !begin_chunk(c + 1)) { alive = false; break; }
 
         // ---- outputs: bf16(y), or the gated RMSNorm of bf16(y) ------------------------------------------------------------------
         {
             uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, tQS + cg * 32), r);
+            tc::tmem_ld32(tc::tmem_addr(tm, quad, tO + cg * 32), r);
             tc::tmem_ld_wait();
             const int i = lane_row64;
             const bool live = lane < 16 && i < n;
@@ -604,17 +611,15 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
                         y[jj] = w * (y[jj] * rinv) * (1.0f / (1.0f + __expf(-gt)));
                     }
                 }
+                compute_sync();  // the partial sums are read before the next chunk's are written
             }
             if (live) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(p.out + at + c * 8) = make_uint4(tc::bf16x2(y[c * 8], y[c * 8 + 1]), tc::bf16x2(y[c * 8 + 2], y[c * 8 + 3]),
-                                                                            tc::bf16x2(y[c * 8 + 4], y[c * 8 + 5]), tc::bf16x2(y[c * 8 + 6], y[c * 8 + 7]));
+                for (int c4 = 0; c4 < 4; ++c4)
+                    *reinterpret_cast<uint4*>(p.out + at + c4 * 8) = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
+                                                                             tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
             }
         }
-        tc::fence_before_sync();
-        compute_sync();
-        tc::fence_after_sync();
     }
 
     // ---- the outgoing state ---------------------------------------------------------------------------------------------
@@ -629,6 +634,36 @@ __global__ void __launch_bounds__(kThreadsTc, 1) state_kernel(const __grid_const
             else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
         }
     }
+    tc::fence_before_sync();
+    __syncthreads();
+}
+
+// One launch: the state role of one segment on the chain blocks, then the intra role of the next segment on all blocks.
+__global__ void __launch_bounds__(kThreadsTc, 1) prefill_sp_kernel(const __grid_constant__ SpParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        uint64_t* bi = reinterpret_cast<uint64_t*>(smem + oBars);
+        for (int i = 0; i < 3; ++i) mbar_init(bi + i, 1);  // intra role: raw, mma, free
+        uint64_t* bs = reinterpret_cast<uint64_t*>(smem + oBarsState);
+        for (int i = 0; i < 7; ++i) mbar_init(bs + i, 1);  // state role: full[3], empty[3], mma
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+        if (blockIdx.x == 0) p.counters[p.ctr ^ 1] = 0u;  // the next launch's counter; nobody reads it during this launch
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    if (p.has_state && blockIdx.x < (unsigned)(p.batch * p.H)) {
+        state_role(p, smem, tm, (int)blockIdx.x);
+        tc::fence_after_sync();
+    }
+    if (p.has_intra && ctl[1] == 0u) intra_role(p, smem, tm);
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
@@ -662,12 +697,16 @@ static bool row_tensor_map(CUtensorMap* tm, const void* base, int elem, int H, l
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr long long kCounterBytes = 256;  // tail of the workspace: the two item counters
+
 int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass) {
     if (heads < 1 || batch < 1 || chunks_per_pass < 1) return 0;
-    return (int64_t)heads * batch * chunks_per_pass * kSlotBytes;
+    return (int64_t)heads * batch * chunks_per_pass * kSlotBytes + kCounterBytes;
 }
 
-// The two passes over every segment of the longest sequence, in stream order.
+// The launches over every segment of the longest sequence, in stream order.  A workspace of two or more chunks per
+// chain is split into halves so that the state role of one segment runs beside the intra role of the next; a
+// workspace of one chunk per chain alternates intra-only and state-only launches.
 int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
                            void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
@@ -677,14 +716,17 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemState);
+        const cudaError_t e = cudaFuncSetAttribute(prefill_sp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemSp);
         if (e != cudaSuccess) return (int)e;
         configured_dev = dev;
     }
     const long long chains = (long long)heads * batch;
-    long long seg = workspace_bytes / (chains * kSlotBytes);
-    if (seg < 1 || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return kInvalid;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < kCounterBytes) return kInvalid;
+    const long long usable = (workspace_bytes - kCounterBytes) & ~15ll;
+    const long long whole = usable / (chains * kSlotBytes);
+    if (whole < 1) return kInvalid;
+    const bool overlap = whole >= 2;
+    long long seg = overlap ? whole / 2 : whole;
     const long long need = ((long long)max_len + CH - 1) / CH;
     if (seg > need) seg = need > 0 ? need : 1;
     SpParams p{};
@@ -694,8 +736,10 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     p.state_off = reinterpret_cast<const long long*>(state_off);
     p.state_bf16 = bf16_state ? 1 : 0;
     p.gate = gate; p.norm_w = norm_w; p.eps = eps; p.out = out;
-    p.ws = reinterpret_cast<unsigned char*>(workspace);
     p.seg_chunks = (int)seg;
+    unsigned char* base = reinterpret_cast<unsigned char*>(workspace);
+    unsigned char* half[2] = {base, overlap ? base + chains * seg * kSlotBytes : base};
+    p.counters = reinterpret_cast<unsigned int*>(base + usable);
     p.status = status_word();
     if (p.status == nullptr) return (int)cudaErrorUnknown;
     // Tensor copies fetch full chunks only, whose rows the caller's metadata vouches for; the extent written into the
@@ -705,19 +749,39 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     if (!row_tensor_map(&p.tm_q, q, 2, heads, rows_cap) || !row_tensor_map(&p.tm_k, k, 2, heads, rows_cap) ||
         !row_tensor_map(&p.tm_v, v, 2, heads, rows_cap) || !row_tensor_map(&p.tm_g, g, 4, heads, rows_cap))
         return (int)cudaErrorNotSupported;
-    const int sms = sm_count();
-    for (long long c0 = 0; c0 == 0 || c0 < need; c0 += seg) {
-        p.chunk0 = (int)c0;
-        if (need > 0) {
-            const long long items = chains * seg;
-            intra_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsTc, kSmemTc, stream>>>(p);
-            const int rc = (int)cudaGetLastError();
+    cudaError_t e = cudaMemsetAsync(p.counters, 0, 2 * sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return (int)e;
+    const long long sms = sm_count();
+    const long long segs = need > 0 ? (need + seg - 1) / seg : 0;
+    int launch_no = 0;
+    auto launch = [&](long long intra_seg, long long state_seg) -> int {
+        p.has_intra = intra_seg >= 0 ? 1 : 0;
+        p.has_state = state_seg >= 0 ? 1 : 0;
+        p.intra_chunk0 = (int)(intra_seg * seg);
+        p.state_chunk0 = (int)(state_seg * seg);
+        p.ws_intra = half[intra_seg & 1];
+        p.ws_state = half[state_seg & 1];
+        p.ctr = launch_no++ & 1;
+        long long grid = p.has_state ? chains : 0;
+        if (p.has_intra) {
+            const long long items = chains * seg, want = items < sms ? items : sms;
+            if (grid < want) grid = want;
+        }
+        prefill_sp_kernel<<<(unsigned)grid, kThreadsTc, kSmemSp, stream>>>(p);
+        return (int)cudaGetLastError();
+    };
+    if (segs == 0) return launch(-1, 0);  // nothing but empty sequences: their states are copied
+    if (overlap) {
+        for (long long s = 0; s <= segs; ++s) {
+            const int rc = launch(s < segs ? s : -1, s - 1);
             if (rc != 0) return rc;
         }
-        state_kernel<<<(unsigned)chains, kThreadsTc, kSmemState, stream>>>(p);
-        const int rc = (int)cudaGetLastError();
-        if (rc != 0) return rc;
-        if (need == 0) break;
+    } else {
+        for (long long s = 0; s < segs; ++s) {
+            int rc = launch(s, -1);
+            if (rc == 0) rc = launch(-1, s);
+            if (rc != 0) return rc;
+        }
     }
     return 0;
 }
@@ -731,11 +795,11 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
 // would fail, fragment the plan or stall.  Such a caller cannot produce the workspace
 // glm53f_kda_core_prefill_varlen_ws asks for.  For them the library carries its own scratch: a fixed array in device
 // memory that exists as soon as the library is loaded on a GPU (and is held by every GPU that loads it until the
-// process exits), big enough for 64 workspace slots.  Nothing in it has to start at zero: the first pass writes every
-// byte of a slot that the second pass reads.  All calls share the one array, so two calls in flight at once (two
+// process exits), big enough for 64 workspace slots and the item counters.  Nothing in it has to start at zero: the
+// intra role writes every byte of a slot that the state role reads, and each call clears the counters itself.  All calls share the one array, so two calls in flight at once (two
 // streams, two threads) overwrite each other's slots; the caller serialises them.
 constexpr int kStaticSlots = 64;
-constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes;  // 6,946,816 bytes
+constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes + kCounterBytes;  // 6,947,072 bytes
 static __device__ __align__(256) unsigned char g_prefill_scratch[kStaticScratchBytes];
 
 // The array's name is a host-side handle here, not a device address: the address a kernel can use is asked for once
@@ -746,7 +810,7 @@ int core_prefill_static_launch(int32_t heads, int32_t batch, const int32_t* cu_s
                                const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, cudaStream_t stream) {
     constexpr int kMaxDevices = 64;
     static void* scratch_of[kMaxDevices] = {};
-    if ((long long)heads * batch > kStaticSlots) return kInvalid;  // not even one chunk per pass would fit
+    if ((long long)heads * batch > kStaticSlots) return kInvalid;  // not even one chunk per chain would fit
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;

@@ -285,7 +285,7 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
 /* No counterpart in the reference.  glm53f_kda_core_prefill_varlen_ws for callers that cannot call cudaMalloc: an
  * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs
  * where an allocation would fail or disturb its host (inside a stream capture, under an allocator lock).  It takes no
- * workspace: the two passes run on a fixed array of 6,946,816 bytes (64 workspace slots) that lives in the library's
+ * workspace: the two passes run on a fixed array of 6,947,072 bytes (64 workspace slots and the item counters) that lives in the library's
  * device image, so every GPU on which the library is loaded holds that much until the process exits.
  *   - Limit: heads * batch <= 64 (at least one chunk per pass must fit); more is rejected with status 1
  *     (cudaErrorInvalidValue) before anything is enqueued.  A pass covers 64 / (heads * batch) chunks of every

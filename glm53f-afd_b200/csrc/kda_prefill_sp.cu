@@ -88,6 +88,7 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
     uint64_t* bar_mma = bar_raw + 1;
     uint64_t* bar_free = bar_raw + 2;
+    uint64_t* bar_mma2 = bar_raw + 3;
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
     volatile int* item2 = reinterpret_cast<volatile int*>(smem + oCtl) + 4;  // the item of each staging generation
     float* betas2 = reinterpret_cast<float*>(smem + oBeta);
@@ -183,17 +184,23 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
         return;
     }
 
-    uint32_t raw_phase = 0, mma_phase = 0;
-    auto mma_round = [&](auto&& issue) -> bool {
+    uint32_t raw_phase = 0, mma_phase = 0, mma2_phase = 0;
+    auto mma_issue = [&](uint64_t* bar, auto&& issue) {
         if (tid == 0) {
             issue();
-            tc::mma_commit(bar_mma);
+            tc::mma_commit(bar);
             atomicAdd(const_cast<uint32_t*>(ctl), 1u);
         }
-        if (!mbar_wait(bar_mma, mma_phase, ctx, kStatusWaitPrefill)) return false;
-        mma_phase ^= 1u;
+    };
+    auto mma_wait = [&](uint64_t* bar, uint32_t& phase) -> bool {
+        if (!mbar_wait(bar, phase, ctx, kStatusWaitPrefill)) return false;
+        phase ^= 1u;
         tc::fence_after_sync();
         return true;
+    };
+    auto mma_round = [&](auto&& issue) -> bool {
+        mma_issue(bar_mma, issue);
+        return mma_wait(bar_mma, mma_phase);
     };
     auto publish_operands = [&]() {
         fence_proxy_async_smem();
@@ -244,7 +251,37 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
         }
         compute_sync();
 
-        // ---- 2. operand tiles ------------------------------------------------------------------------------------------
+        // ---- 2a. the operands of L: Kg = K E and Kinv = K / E ---------------------------------------------------------------
+        {
+            const int r = tid & 63, cgrp = tid >> 6;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cgrp * 2 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oBoxK + box_piece(r, c));
+                const float4 e0 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c));
+                const float4 e1 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c + 1));
+                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
+                uint32_t kg[4], ki[4];
+#pragma unroll
+                for (int u2 = 0; u2 < 4; ++u2) {
+                    const float k0 = __uint_as_float(kw[u2] << 16), k1 = __uint_as_float(kw[u2] & 0xffff0000u);
+                    const float ea = E[2 * u2], eb = E[2 * u2 + 1];
+                    kg[u2] = tc::bf16x2(k0 * ea, k1 * eb);
+                    ki[u2] = tc::bf16x2(k0 * __fdividef(1.0f, ea), k1 * __fdividef(1.0f, eb));
+                }
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+            }
+        }
+        publish_operands();
+        // ---- 3a. L = Kg Kinv^T starts while the other operands are built ----------------------------------------------------
+        mma_issue(bar_mma, [&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+        });
+        // ---- 2b. Qg = Q E, Kdec = K E_last / E as bf16 hi + lo, V as cells --------------------------------------------------------
         {
             const int r = tid & 63, cgrp = tid >> 6;
 #pragma unroll
@@ -260,29 +297,23 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
                 const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
                 const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
                 const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
-                uint32_t kg[4], qg[4], ki[4], dh[4], dl[4];
+                uint32_t qg[4], dh[4], dl[4];
 #pragma unroll
                 for (int u2 = 0; u2 < 4; ++u2) {
                     const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
                     const float qf[2] = {__uint_as_float(qw[u2] << 16), __uint_as_float(qw[u2] & 0xffff0000u)};
-                    float a[2], bq[2], ci[2], hi[2], lo[2];
+                    float bq[2], hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const float e = E[2 * u2 + u], einv = __fdividef(1.0f, e);
-                        a[u] = kf[u] * e;
+                        const float e = E[2 * u2 + u];
                         bq[u] = qf[u] * e;
-                        ci[u] = kf[u] * einv;
-                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * einv), hi[u], lo[u]);
+                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * __fdividef(1.0f, e)), hi[u], lo[u]);
                     }
-                    kg[u2] = tc::bf16x2(a[0], a[1]);
                     qg[u2] = tc::bf16x2(bq[0], bq[1]);
-                    ki[u2] = tc::bf16x2(ci[0], ci[1]);
                     dh[u2] = tc::bf16x2(hi[0], hi[1]);
                     dl[u2] = tc::bf16x2(lo[0], lo[1]);
                 }
-                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
@@ -290,7 +321,7 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
         }
         publish_operands();
         if (tid == 0) {
-            mbar_arrive(bar_free);  // the loader may stream the next item's rows in (it returns if there is none)
+            mbar_arrive(bar_free);  // the loader may stream the next item's rows in
             // Qg, Kdec hi/lo and exp(G_last) are final: out to the workspace while the rest of the item is computed.
             bulk_store(slot + wQg, smem + oQg, kTile);
             bulk_store(slot + wKdHi, smem + oKdHi, kTile);
@@ -298,15 +329,14 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
             bulk_store(slot + wEgl, smem + oEGL, 512);
             bulk_commit();
         }
-
-        // ---- 3. L = Kg Kinv^T, M = Qg Kinv^T ----------------------------------------------------------------------------
-        if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-            })) break;
+        // ---- 3b. M = Qg Kinv^T ------------------------------------------------------------------------------------------------
+        mma_issue(bar_mma2, [&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+        });
+        if (!mma_wait(bar_mma, mma_phase)) break;
+        if (!mma_wait(bar_mma2, mma2_phase)) break;
 
         // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) --------------------------
         {
@@ -336,12 +366,7 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
             const float* Lm = reinterpret_cast<const float*>(smem + oL);
             float* Tm = reinterpret_cast<float*>(smem + oT);
             float* Pm = reinterpret_cast<float*>(smem + oP);
-            for (int e = tid; e < CH * CH; e += kCompute) Tm[(e >> 6) * LS + (e & 63)] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
-            compute_sync();
-            invert_level<0>(Lm, Tm, Pm, tid);
-            invert_level<1>(Lm, Tm, Pm, tid);
-            invert_level<2>(Lm, Tm, Pm, tid);
-            invert_level<3>(Lm, Tm, Pm, tid);
+            invert_diag16(Lm, Tm, tid);
             invert_level<4>(Lm, Tm, Pm, tid);
             invert_level<5>(Lm, Tm, Pm, tid);
             const int i = tid & 63, c = tid >> 6;
@@ -646,7 +671,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_sp_kernel(const __grid_
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) {
         uint64_t* bi = reinterpret_cast<uint64_t*>(smem + oBars);
-        for (int i = 0; i < 3; ++i) mbar_init(bi + i, 1);  // intra role: raw, mma, free
+        for (int i = 0; i < 4; ++i) mbar_init(bi + i, 1);  // intra role: raw, mma, free, mma2
         uint64_t* bs = reinterpret_cast<uint64_t*>(smem + oBarsState);
         for (int i = 0; i < 7; ++i) mbar_init(bs + i, 1);  // state role: full[3], empty[3], mma
         ctl[0] = 0u;

@@ -289,12 +289,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
             float* Pm = reinterpret_cast<float*>(smem + oP);
             // Recursive doubling.  T starts as the identity; at block size sz the lower-left sz x sz block of every
             // 2sz x 2sz diagonal block is -T22 (L21 T11), all blocks and elements in parallel.
-            for (int e = tid; e < CH * CH; e += kCompute) Tm[(e >> 6) * LS + (e & 63)] = (e >> 6) == (e & 63) ? 1.0f : 0.0f;
-            compute_sync();
-            invert_level<0>(Lm, Tm, Pm, tid);
-            invert_level<1>(Lm, Tm, Pm, tid);
-            invert_level<2>(Lm, Tm, Pm, tid);
-            invert_level<3>(Lm, Tm, Pm, tid);
+            invert_diag16(Lm, Tm, tid);
             invert_level<4>(Lm, Tm, Pm, tid);
             invert_level<5>(Lm, Tm, Pm, tid);
             // 5c. T' = T diag(beta) as bf16 hi + lo cells.  T' lands on the scratch itself, so every thread first reads

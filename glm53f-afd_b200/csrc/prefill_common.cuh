@@ -105,5 +105,33 @@ __device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* 
     compute_sync();
 }
 
+// The start of the inverse: the four 16 x 16 diagonal blocks of (I + L)^-1 by forward substitution, one thread per
+// column (a column needs only its own earlier rows, so the 64 threads never talk to each other), while the other
+// threads clear every entry outside those blocks.  Ends with a barrier; levels 4 and 5 of invert_level follow.
+__device__ __forceinline__ void invert_diag16(const float* Lm, float* Tm, int tid) {
+    if (tid < 64) {
+        const int o = (tid >> 4) * 16, j = tid & 15;
+        float t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float* Lr = Lm + (o + i) * LS + o;
+            float a0 = i == j ? 1.0f : 0.0f, a1 = 0.0f;
+#pragma unroll
+            for (int m = 0; m < i; ++m) {
+                if (m & 1) a1 = fmaf(-Lr[m], t[m], a1);
+                else a0 = fmaf(-Lr[m], t[m], a0);
+            }
+            t[i] = a0 + a1;
+            Tm[(o + i) * LS + o + j] = t[i];
+        }
+    } else {
+        for (int e = tid - 64; e < CH * CH; e += kCompute - 64) {
+            const int i = e >> 6, j = e & 63;
+            if ((i >> 4) != (j >> 4)) Tm[i * LS + j] = 0.0f;
+        }
+    }
+    compute_sync();
+}
+
 }  // namespace pf
 }  // namespace kda

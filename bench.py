@@ -38,8 +38,10 @@ STATE_BYTES_PER_LAUNCH = 2 * SLOTS * STATE_ELEMS * 2  # bf16 read + write = 64 M
 TOKEN_IN_BYTES = HEADS * DK * (2 + 2 + 2 + 4) + HEADS * 4  # q, k, v bf16 + g f32 + beta f32 per token
 TOKEN_OUT_BYTES = HEADS * DK * 2
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised
-# under profiles/ (None until a capture exists).
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# under profiles/ (a single captured launch: the 32 MiB it writes stay in the 126 MB L2, so this is mostly the reads).
+NCU_DRAM_BYTES_PER_LAUNCH = 34_925_824 + 117_504
+# The same for the prefill kernel: 601 MB per captured launch of 2,048 (chain, chunk) items = 32 chunks of all 64 heads.
+NCU_PREFILL_DRAM_BYTES_PER_TOKEN = (393_953_280 + 207_395_072) // (32 * 64)
 
 
 def peaks():
@@ -239,6 +241,11 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
     tf, tf_kind = tensor_peak()
     gbs = tokens * PREFILL_BYTES_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e9      # per GPU
     tflops = tokens * PREFILL_FLOP_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e12  # per GPU
+    chunks = (tokens + 63) // 64
+    if ws_chunks >= 2:    # workspace halves: one launch per segment of ws_chunks // 2 chunks, plus the last state role
+        kernels_per_pass = (chunks + ws_chunks // 2 - 1) // (ws_chunks // 2) + 1
+    else:                 # one chunk per launch pair, or the single-pass kernel
+        kernels_per_pass = 2 * chunks if ws_chunks == 1 else 1
     res = {
         "workload": f"config 3: one sequence of {tokens} tokens, H=64 ({hl} heads per GPU), d=128, chunk 64, FP32 state",
         "value": tokens / (ms_total * 1e-3), "unit": "tokens/s per layer", "ms_per_layer": ms_total,
@@ -247,9 +254,10 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
                      "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
                                 "flop_per_token": PREFILL_FLOP_PER_TOKEN},
                      "algorithmic_bytes_per_token": PREFILL_BYTES_PER_TOKEN,
+                     "traffic_bytes_per_token": NCU_PREFILL_DRAM_BYTES_PER_TOKEN if ws_chunks > 0 else None,
                      "kernel": "prefill_sp_kernel (state role + intra role)" if ws_chunks > 0 else "prefill_tc_kernel",
                      "workspace_bytes": 0 if ws is None else ws.numel()},
-        "gpu_launches": passes,
+        "gpu_launches": passes * kernels_per_pass,
         "collective": None if world == 1 else {"op": "all_gather of per-head outputs", "bytes_received_per_gpu": tokens * (HEADS - hl) * DK * 2,
                                               "ms": ms_total - ms_compute},
     }

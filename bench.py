@@ -173,7 +173,7 @@ def cpu_prefill_toks(seconds: float):
     return n * t / dt, cores, f"{n} x {t} tokens x {HEADS} heads, chunk-64 form, in {dt:.1f} s"
 
 
-def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
+def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, check_heads=0):
     """Config 3: chunked prefill of one long sequence, heads sharded over the ranks, outputs all-gathered."""
     import ctypes as C
 
@@ -206,13 +206,23 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
     cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
     off = torch.zeros(1, dtype=torch.int64, device="cuda")
     full = torch.empty((tokens, HEADS, DK), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    # Every rank's full output buffer mapped into every rank: the prefill kernel stores its heads' rows into all of them.
+    fused = par.GatheredOutput(tokens, HEADS) if world > 1 else None
     # Few chains (one sequence x this rank's heads): the two-pass form over a workspace keeps every SM busy.
     ws = torch.empty(core.prefill_workspace_bytes(hl, 1, ws_chunks), dtype=torch.uint8, device="cuda") if ws_chunks > 0 else None
 
     def one_pass(gather):
+        """gather: False = this rank's heads only; "nccl" = followed by an all-gather of the outputs; "fused" = the
+        kernel stores into every rank's full buffer itself, with a barrier on each side."""
         state.zero_()
+        if gather == "fused":
+            fused.barrier()
+            core.prefill_varlen(hl, tokens, cu, tokens, q, k, v, g, beta, state, off, out=None, workspace=ws,
+                                gather=(fused.addresses, HEADS, lo))
+            fused.barrier()
+            return
         core.prefill_varlen(hl, tokens, cu, tokens, q, k, v, g, beta, state, off, out=out, workspace=ws)
-        if gather and world > 1:
+        if gather == "nccl":
             par.gather_heads(out.view(tokens, hl, DK), HEADS, out=full)
 
     def timed(gather):
@@ -233,9 +243,17 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
             ms = float(t.item())
         return ms
 
-    one_pass(True)
+    one_pass("nccl" if world > 1 else False)
     ms_compute = timed(False)
-    ms_total = timed(True) if world > 1 else ms_compute
+    ms_nccl = timed("nccl") if world > 1 else ms_compute
+    ms_total = ms_compute
+    if world > 1:
+        if ws is None:
+            raise SystemExit("the fused gather needs the workspace form of the prefill (--prefill-ws-chunks > 0)")
+        one_pass("fused")
+        torch.cuda.synchronize()
+        same = torch.equal(fused.tensor.view(torch.int16), full.view(torch.int16))  # both hold the same rows, bit for bit
+        ms_total = timed("fused")
     assert core.device_status() == 0
     hbm, hbm_kind = peaks()
     tf, tf_kind = tensor_peak()
@@ -258,12 +276,44 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks):
                      "kernel": "prefill_sp_kernel (state role + intra role)" if ws_chunks > 0 else "prefill_tc_kernel",
                      "workspace_bytes": 0 if ws is None else ws.numel()},
         "gpu_launches": passes * kernels_per_pass,
-        "collective": None if world == 1 else {"op": "all_gather of per-head outputs", "bytes_received_per_gpu": tokens * (HEADS - hl) * DK * 2,
-                                              "ms": ms_total - ms_compute},
+        "collective": None if world == 1 else {
+            "op": "all-gather of the per-head outputs, fused: the state role stores each output row into every rank's full buffer over NVLink",
+            "bytes_sent_per_gpu": tokens * hl * DK * 2 * (world - 1), "ms_exposed": ms_total - ms_compute,
+            "equals_nccl_all_gather_bitwise": bool(same),
+            "nccl_all_gather_after_the_kernel": {"ms_per_layer": ms_nccl, "ms_exposed": ms_nccl - ms_compute}},
     }
-    del q, k, v, g, out, full
+    if check_heads > 0 and rank == 0:
+        res["check"] = check_prefill(torch, tokens, hl, min(check_heads, hl), q, k, v, g, beta, out, state)
+    del q, k, v, g, out, full, fused
     torch.cuda.empty_cache()
     return res
+
+
+def check_prefill(torch, tokens, hl, n_heads, q, k, v, g, beta, out, state):
+    """Full-length parity of the prefill leg: the FP32 row-by-row recurrence of the oracle on the host, from the exact
+    bytes the GPU consumed, for `n_heads` heads spread over this rank's heads: final-state rel-L2 and the outputs of
+    the last 4,096 tokens (max-abs and rel-L2 against the FP32 read-out)."""
+    import numpy as np
+
+    o = oracle_module()
+    sel = sorted({(i * hl) // n_heads for i in range(n_heads)})
+    idx = torch.tensor(sel, device="cuda")
+    pick = lambda t, w: t.view(tokens, hl, w).index_select(1, idx).contiguous().cpu()
+    qh, kh, vh = (pick(t.view(torch.int16), DK).numpy().view(np.uint16).reshape(-1) for t in (q, k, v))
+    gh = pick(g, DK).numpy().reshape(-1)
+    bh = beta.view(tokens, hl).index_select(1, idx).contiguous().cpu().numpy().reshape(-1)
+    t0 = time.perf_counter()
+    y, s_ref = o.core_forward(len(sel), qh, kh, vh, gh, bh, np.zeros(len(sel) * DK * DK, np.float32), form="recurrent",
+                              threads=min(len(sel), os.cpu_count() or 1))
+    cpu_s = time.perf_counter() - t0
+    s_gpu = state.view(hl, DK * DK).index_select(0, idx).cpu().numpy().reshape(-1)
+    tail = min(tokens, 4096)
+    y_gpu = out.view(tokens, hl, DK)[tokens - tail:].index_select(1, idx).float().cpu().numpy().reshape(-1)
+    y_ref = y.reshape(tokens, len(sel), DK)[tokens - tail:].reshape(-1)
+    return {"heads": sel, "tokens": tokens, "state_rel_l2": float(np.linalg.norm(s_gpu - s_ref) / np.linalg.norm(s_ref)),
+            "out_tail_tokens": tail, "out_max_abs": float(np.max(np.abs(y_gpu - y_ref))),
+            "out_rel_l2": float(np.linalg.norm(y_gpu - y_ref) / np.linalg.norm(y_ref)),
+            "limits": {"state_rel_l2": 1e-3, "out_max_abs": 2e-2, "out_rel_l2": 5e-3}, "cpu_seconds": cpu_s}
 
 
 def dist_env():
@@ -306,6 +356,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
+    ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
     ap.add_argument("--prefill-ws-chunks", type=int, default=128, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -426,7 +477,7 @@ def main():
     if args.prefill_tokens > 0:
         del arena, dev, outs
         torch.cuda.empty_cache()
-        prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks)
+        prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
 
     if rank != 0:
         if world > 1:

@@ -68,7 +68,8 @@ def _state_kind(state):
 def _check_tokens(heads, rows, q, k, v, g, beta, gate, norm_w, out):
     n = rows * heads * DK
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out")):
-        _need(t, name, _BF, n)
+        if t is not None or name != "out":  # only the gathering prefill may go without a local `out`
+            _need(t, name, _BF, n)
     _need(g, "g", (torch.float32,), n)
     _need(beta, "beta", (torch.float32,), rows * heads)
     if gate is not None:
@@ -132,14 +133,19 @@ def prefill_workspace_bytes(heads, batch, chunks_per_pass):
 
 
 def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, state_off, *, state_out="in_place",
-                   flags=0, gate=None, norm_w=None, eps=1e-5, out=None, workspace=None):
+                   flags=0, gate=None, norm_w=None, eps=1e-5, out=None, workspace=None, gather=None):
     """glm53f_kda_core_prefill_varlen: chunked prefill of packed variable-length sequences.  With `workspace` (a
     CUDA uint8 tensor) the two-pass glm53f_kda_core_prefill_varlen_ws runs instead; with workspace="static" the
     two passes run on the library's own fixed scratch array (glm53f_kda_core_prefill_varlen_static: for callers
-    that must not allocate; at most 64 (sequence, head) chains)."""
+    that must not allocate; at most 64 (sequence, head) chains).  `gather` = (addresses, heads_total, head0) with a
+    workspace runs glm53f_kda_core_prefill_varlen_ws_gather: this launch's heads are heads head0.. of heads_total, and
+    every output row is also stored into each [rows][heads_total][128] bf16 buffer whose device address is listed
+    (this GPU's and its peers'); `out` may then be None."""
     batch = cu_seqlens.numel() - 1
     _need(cu_seqlens, "cu_seqlens", (torch.int32,), 2)
     _need(state_off, "state_off", (torch.int64,), batch)
+    if out is None and gather is None:
+        raise Invalid("out is required")
     _check_tokens(heads, rows, q, k, v, g, beta, gate, norm_w, out)
     kind = _state_kind(state)
     so = state if isinstance(state_out, str) else state_out
@@ -154,10 +160,24 @@ def prefill_varlen(heads, rows, cu_seqlens, max_len, q, k, v, g, beta, state, st
                                                          _ptr(g), _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind,
                                                          flags, _ptr(gate), _ptr(norm_w), eps, _ptr(out), _stream())
         return _launched(code, "glm53f_kda_core_prefill_varlen_static")
+    if gather is not None and (workspace is None or isinstance(workspace, str)):
+        raise Invalid("gather needs a workspace tensor")
     if workspace is not None:
         if not workspace.is_cuda or not workspace.is_contiguous():
             raise Invalid("workspace must be a contiguous CUDA tensor")
         nbytes = workspace.numel() * workspace.element_size()
+        if gather is not None:
+            addrs, heads_total, head0 = gather
+            if not 1 <= len(addrs) <= 8:
+                raise Invalid(f"1 to 8 full buffers, got {len(addrs)}")
+            if head0 < 0 or head0 + heads > heads_total:
+                raise Invalid(f"heads [{head0}, {head0 + heads}) outside the {heads_total} of the full buffers")
+            arr = (C.c_void_p * len(addrs))(*[int(a) for a in addrs])
+            code = ffi.glm53f_kda_core_prefill_varlen_ws_gather(heads, batch, _ptr(cu_seqlens), max_len, _ptr(q), _ptr(k), _ptr(v), _ptr(g),
+                                                                _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind, flags,
+                                                                _ptr(gate), _ptr(norm_w), eps, _ptr(out), _ptr(workspace), nbytes,
+                                                                C.cast(arr, C.c_void_p), len(addrs), heads_total, head0, _stream())
+            return _launched(code, "glm53f_kda_core_prefill_varlen_ws_gather")
         code = ffi.glm53f_kda_core_prefill_varlen_ws(heads, batch, _ptr(cu_seqlens), max_len, _ptr(q), _ptr(k), _ptr(v), _ptr(g),
                                                      _ptr(beta), _ptr(state), _ptr(so), _ptr(state_off), kind, flags,
                                                      _ptr(gate), _ptr(norm_w), eps, _ptr(out), _ptr(workspace), nbytes, _stream())

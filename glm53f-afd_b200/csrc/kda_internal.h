@@ -37,11 +37,19 @@ int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
 
 // The two-pass tensor-core prefill over a workspace (kda_prefill_sp.cu).
 int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass);
+// Where a head-sharded prefill sends its outputs: into every rank's full [rows][heads_total][128] buffer, this
+// launch's heads at head0.. (up to 8 buffers; they may be peer GPUs' memory mapped into this process).
+struct PrefillScatter {
+    int ranks = 0;
+    glm53f_bf16* full[8] = {};
+    int heads_total = 0, head0 = 0;
+};
+
 int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
                            void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
                            const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const PrefillScatter* scatter = nullptr);
 
 // The two-pass prefill on the library's own fixed scratch array (no workspace argument, nothing allocated).
 int core_prefill_static_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,

@@ -141,6 +141,33 @@ extern "C" int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, c
                                   state_bf16 != 0, gate, norm_w, eps, out, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+extern "C" int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
+                                                        const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                                        const float* g, const float* beta, const void* state_in,
+                                                        void* state_out, const int64_t* state_off, int32_t state_bf16,
+                                                        int32_t flags, const glm53f_bf16* gate, const glm53f_bf16* norm_w,
+                                                        float eps, glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
+                                                        glm53f_bf16* const* full, int32_t ranks, int32_t heads_total,
+                                                        int32_t head0, glm53f_stream_t stream) {
+    if (max_len < 0 || !state_out || !workspace || !full) return kInvalid;
+    if (heads < 1 || heads > 65535 || batch < 1 || batch > 65535) return kInvalid;
+    if (ranks < 1 || ranks > 8 || heads_total < heads || heads_total > 65535 || head0 < 0 || head0 + heads > heads_total) return kInvalid;
+    if (!cu_seqlens || !q || !k || !v || !g || !beta || !state_in || !state_off) return kInvalid;
+    if (gate && !norm_w) return kInvalid;
+    if (flags != 0) return kInvalid;
+    auto aligned = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    if (!(aligned(q) && aligned(k) && aligned(v) && aligned(g) && aligned(out) && (!gate || (aligned(gate) && aligned(norm_w)))))
+        return kInvalid;
+    PrefillScatter sc;
+    sc.ranks = ranks; sc.heads_total = heads_total; sc.head0 = head0;
+    for (int r = 0; r < ranks; ++r) {
+        if (!full[r] || !aligned(full[r])) return kInvalid;
+        sc.full[r] = full[r];
+    }
+    return core_prefill_sp_launch(heads, batch, cu_seqlens, max_len, q, k, v, g, beta, state_in, state_out, state_off,
+                                  state_bf16 != 0, gate, norm_w, eps, out, workspace, workspace_bytes, (cudaStream_t)stream, &sc);
+}
+
 extern "C" int glm53f_kda_core_prefill_varlen_static(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
                                                      const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
                                                      const float* g, const float* beta, const void* state_in,

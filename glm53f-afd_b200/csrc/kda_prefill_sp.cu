@@ -67,6 +67,8 @@ struct SpParams {
     int intra_chunk0, has_intra;
     unsigned char* ws_state; // state role: chunks [state_chunk0, state_chunk0 + seg_chunks) of every sequence, or none
     int state_chunk0, has_state;
+    uint16_t* full[8];       // head-sharded launches: every rank's full [rows][heads_total][128] output buffer, or none
+    int ranks, heads_total, head0;
     unsigned int* counters;  // [2] item counters: this launch hands items out of counters[ctr], and zeroes the other
     int ctr;
     int* status;
@@ -639,10 +641,22 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
                 compute_sync();  // the partial sums are read before the next chunk's are written
             }
             if (live) {
+                uint4 o4[4];
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4)
-                    *reinterpret_cast<uint4*>(p.out + at + c4 * 8) = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
-                                                                             tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
+                    o4[c4] = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
+                                        tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
+                if (p.out != nullptr) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) *reinterpret_cast<uint4*>(p.out + at + c4 * 8) = o4[c4];
+                }
+                // The all-gather of a head-sharded prefill, done here: the row goes straight into every rank's full
+                // buffer (plain stores; a peer's buffer is reached over NVLink), so no exchange step follows the launch.
+                const long long at_full = ((gr0 + i) * p.heads_total + p.head0 + h) * DV + cg * 32;
+                for (int pe = 0; pe < p.ranks; ++pe) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) *reinterpret_cast<uint4*>(p.full[pe] + at_full + c4 * 8) = o4[c4];
+                }
             }
         }
     }
@@ -736,7 +750,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
                            void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
                            const glm53f_bf16* norm_w, float eps, glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const PrefillScatter* scatter) {
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -761,6 +775,16 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     p.state_off = reinterpret_cast<const long long*>(state_off);
     p.state_bf16 = bf16_state ? 1 : 0;
     p.gate = gate; p.norm_w = norm_w; p.eps = eps; p.out = out;
+    if (scatter != nullptr) {
+        if (scatter->ranks < 1 || scatter->ranks > 8 || scatter->head0 < 0 || scatter->head0 + heads > scatter->heads_total) return kInvalid;
+        for (int r = 0; r < scatter->ranks; ++r) {
+            if (scatter->full[r] == nullptr || (reinterpret_cast<uintptr_t>(scatter->full[r]) & 15) != 0) return kInvalid;
+            p.full[r] = scatter->full[r];
+        }
+        p.ranks = scatter->ranks; p.heads_total = scatter->heads_total; p.head0 = scatter->head0;
+    } else if (out == nullptr) {
+        return kInvalid;
+    }
     p.seg_chunks = (int)seg;
     unsigned char* base = reinterpret_cast<unsigned char*>(workspace);
     unsigned char* half[2] = {base, overlap ? base + chains * seg * kSlotBytes : base};

@@ -37,6 +37,7 @@ SIGNATURES = {
     "glm53f_kda_core_prefill_varlen": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P]),
     "glm53f_kda_core_prefill_workspace_bytes": (I64, [I32, I32, I32]),
     "glm53f_kda_core_prefill_varlen_ws": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P, I64, P]),
+    "glm53f_kda_core_prefill_varlen_ws_gather": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P, I64, P, I32, I32, I32, P]),
     "glm53f_kda_core_prefill_varlen_static": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P]),
     "glm53f_kda_device_status": (C.c_int, []),
 }

@@ -57,3 +57,27 @@ def gather_heads(local: torch.Tensor, heads: int, group=None, out: torch.Tensor 
         out = torch.empty((t, heads, d), dtype=local.dtype, device=local.device)
     out.view(t, world, hl, d).copy_(staged.view(world, t, hl, d).permute(1, 0, 2, 3))
     return out
+
+
+class GatheredOutput:
+    """The full [rows][heads][128] bf16 output of a head-sharded prefill on every rank, each rank's buffer mapped into
+    every other rank's address space (torch symmetric memory), so that the prefill kernel of each rank can store its
+    heads' rows straight into all of them: the all-gather happens inside the kernel, over NVLink, by plain stores.
+
+    `addresses` is what core.prefill_varlen(..., gather=(addresses, heads, head0)) takes.  `barrier()` orders the ranks
+    on the current stream; call it before a launch that overwrites the buffers (no rank may still be reading) and
+    after it (every rank's rows have landed) before reading `tensor`."""
+
+    def __init__(self, rows: int, heads: int, group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.tensor = symm.empty((rows, heads, 128), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm.rendezvous(self.tensor, self.group)
+        self.addresses = [int(a) for a in self.handle.buffer_ptrs]
+        self._token = torch.zeros(1, device="cuda")
+
+    def barrier(self) -> None:
+        # A one-element all-reduce in stream order: every rank's earlier work on its stream is complete before any
+        # rank's later work starts.
+        dist.all_reduce(self._token, group=self.group)

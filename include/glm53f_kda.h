@@ -267,8 +267,10 @@ int glm53f_kda_core_prefill_varlen(int32_t heads, int32_t batch, const int32_t* 
  * one long sequence, or one GPU's shard of heads -- where one block per chain would leave most SMs idle: the part
  * of every chunk that does not depend on the recurrent state is computed for many chunks at once on all SMs, then
  * one block per chain runs the short state-dependent part chunk by chunk.  `workspace` (device memory, 16-byte
- * aligned) holds 108,544 bytes per (sequence, head, chunk of 64 rows) in flight; its size sets how many chunks of
- * every sequence one pass covers (at least one: glm53f_kda_core_prefill_workspace_bytes(heads, batch, 1)).
+ * aligned) holds 108,544 bytes per (sequence, head, chunk of 64 rows) in flight plus 256 bytes of counters; its size
+ * sets how many chunks of every sequence one launch covers (at least one:
+ * glm53f_kda_core_prefill_workspace_bytes(heads, batch, 1)); with room for two or more chunks per chain the state part
+ * of one segment runs beside the state-independent part of the next.
  * Results do not depend on the workspace size and agree with glm53f_kda_core_prefill_varlen to rounding.  Inputs must be
  * 16-byte aligned and flags must be 0 (status 1 otherwise).  Not in the reference; its own prefill takes a
  * workspace the same way (reference glm53f_kda.h:198-204, 223-232). */
@@ -281,6 +283,24 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
                                       const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
                                       glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
                                       glm53f_stream_t stream);
+
+/* glm53f_kda_core_prefill_varlen_ws for a head-sharded launch (heads = this GPU's shard of heads_total heads, starting
+ * at head0) with the all-gather of the outputs done by the kernel itself: every output row is stored straight into
+ * each of the `ranks` (1..8) full buffers full[r], laid out [rows][heads_total][128] bf16 -- this GPU's own and its
+ * peers' (device addresses valid in this process: peer-mapped, IPC-opened or symmetric memory; plain stores over
+ * NVLink, no collective follows the launch).  `full` is a host array, read during the call.  `out` (the shard-local
+ * [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may still read a full
+ * buffer when another rank's launch starts writing it, and a rank may read its buffer only after every rank's launch
+ * has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
+int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
+                                             const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
+                                             const float* g, const float* beta,
+                                             const void* state_in, void* state_out, const int64_t* state_off,
+                                             int32_t state_bf16, int32_t flags,
+                                             const glm53f_bf16* gate, const glm53f_bf16* norm_w, float eps,
+                                             glm53f_bf16* out, void* workspace, int64_t workspace_bytes,
+                                             glm53f_bf16* const* full, int32_t ranks, int32_t heads_total, int32_t head0,
+                                             glm53f_stream_t stream);
 
 /* No counterpart in the reference.  glm53f_kda_core_prefill_varlen_ws for callers that cannot call cudaMalloc: an
  * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs

@@ -246,6 +246,46 @@ def test_prefill_two_pass_over_a_workspace(G, core, oracle, pkg):
     assert G.rel_l2(runs[0][1], ref_st) <= 1e-4
 
 
+# The gathering form on one GPU: two "ranks" (two head shards of one 4-head problem, run one after the other) store
+# their rows into the same two full buffers; both buffers must then hold the unsharded run's outputs, bit for bit
+# (heads never interact), and a launch without a local `out` must leave the same rows.
+def test_prefill_gathering_store_into_full_buffers(G, core, pkg):
+    heads, shard, lens = 4, 2, [200, 65, 0, 30]
+    rows, per = sum(lens), heads * DV * DK
+    tok = pkg.synth.tokens(2, 3, rows, heads)
+    states = np.concatenate([pkg.synth.state(2, 3, i, heads) for i in range(len(lens))])
+    d_cu = G.dev_i32(np.concatenate([[0], np.cumsum(lens)]))
+    ws = torch.empty(core.prefill_workspace_bytes(heads, len(lens), 4), dtype=torch.uint8, device="cuda")
+    dq, dk, dv, dg, db = upload_tokens(G, tok)
+    d_state = G.dev_f32(states)
+    d_out = torch.zeros(rows * heads * DV, dtype=torch.int16, device="cuda")
+    core.prefill_varlen(heads, rows, d_cu, max(lens), dq, dk, dv, dg, db, d_state, G.dev_i64([i * per for i in range(len(lens))]), out=d_out, workspace=ws)
+    fulls = [torch.full((rows * heads * DV + 16,), -1, dtype=torch.int16, device="cuda") for _ in range(2)]
+    for rank in range(2):
+        h0 = rank * shard
+        cut = lambda t, w: t.view(rows, heads, w)[:, h0:h0 + shard].contiguous().view(-1)
+        sq, sk, sv, sg, sb = cut(dq, DK), cut(dk, DK), cut(dv, DV), cut(dg, DK), cut(db, 1)
+        st = np.concatenate([states[i * per + h0 * DV * DK: i * per + (h0 + shard) * DV * DK] for i in range(len(lens))])
+        s_state = G.dev_f32(st)
+        local = torch.zeros(rows * shard * DV, dtype=torch.int16, device="cuda") if rank == 0 else None  # rank 1 keeps no local copy
+        core.prefill_varlen(shard, rows, d_cu, max(lens), sq, sk, sv, sg, sb, s_state, G.dev_i64([i * shard * DV * DK for i in range(len(lens))]),
+                            out=local, workspace=ws, gather=([f.data_ptr() for f in fulls], heads, h0))
+        G.check_status()
+        whole = G.host_f32(d_state).reshape(len(lens), heads, DV * DK)[:, h0:h0 + shard].reshape(-1)
+        assert np.array_equal(G.bits(G.host_f32(s_state)), G.bits(whole))
+        if local is not None:
+            assert torch.equal(local.view(rows, shard, DV), d_out.view(rows, heads, DV)[:, h0:h0 + shard])
+    for f in fulls:
+        assert torch.equal(f[:rows * heads * DV], d_out)
+        assert bool((f[rows * heads * DV:] == -1).all())
+    with pytest.raises(core.Invalid):
+        core.prefill_varlen(shard, rows, d_cu, max(lens), sq, sk, sv, sg, sb, s_state, G.dev_i64([0] * len(lens)), out=None, workspace=ws,
+                            gather=([fulls[0].data_ptr()], heads, 3))
+    with pytest.raises(core.Invalid):
+        core.prefill_varlen(shard, rows, d_cu, max(lens), sq, sk, sv, sg, sb, s_state, G.dev_i64([0] * len(lens)), out=None, workspace=None,
+                            gather=([fulls[0].data_ptr()], heads, 0))
+
+
 def test_prefill_two_pass_bf16_state_and_long_sequence(G, core, oracle, pkg):
     prefill_case(G, core, oracle, pkg.synth, 0, 2, [1100], [True], bf16=True, ws_chunks=4)
 

@@ -132,6 +132,13 @@ __device__ __forceinline__ void tensor_load_3d(void* smem_dst, const void* tmap,
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// Tiled tensor copy (rank 3) of one box from this block's shared memory to global memory (a bulk-group operation).
+__device__ __forceinline__ void tensor_store_3d(const void* tmap, int x, int y, int z, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() {

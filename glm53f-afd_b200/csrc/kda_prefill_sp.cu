@@ -49,6 +49,8 @@ __device__ __forceinline__ int box_piece(int r, int piece) { return (piece >> 3)
 
 struct SpParams {
     alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_g;  // [rows][H][128] as (128, H, rows); boxes of 64 rows x 128 bytes
+    alignas(64) CUtensorMap tm_out;                  // the shard-local output, the same way
+    alignas(64) CUtensorMap tm_full[8];              // every rank's full output buffer: (128, heads_total, rows)
     int H, batch;
     const int32_t* cu;
     const uint16_t *q, *k, *v;
@@ -80,7 +82,9 @@ __device__ __forceinline__ unsigned char* slot_of(unsigned char* ws, int seg_chu
 
 // Barriers of the two roles live apart (the state role's behind the intra role's shared-memory map), are set up once
 // per block and are never repurposed.
-constexpr int oBarsState = kSmemTc, kSmemSp = kSmemTc + 64;
+constexpr int oBarsState = kSmemTc, kSmemSp = kSmemTc + 128;
+// 16 compute warps, the loader warp, and (state role only) a warp that moves finished output rows to global memory.
+constexpr int kThreadsSp = kCompute + 64, kLoaderWarp = kCompute / 32, kOutWarp = kCompute / 32 + 1;
 static_assert(kSmemSp <= 232448, "shared memory budget");
 
 // =====================================================================================================================
@@ -119,7 +123,12 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
     // A full chunk arrives by ten tiled tensor copies issued by one lane.  A sequence's last, partial chunk is copied
     // by the warp's own loads and stores instead (rows past the sequence's end are not read, they become zero), so no
     // copy ever reaches past the rows the caller's metadata names.
-    if (warp == kCompute / 32) {
+    if (warp == kOutWarp) {  // the state role's output warp has no part in this role
+        tc::fence_before_sync();
+        __syncthreads();
+        return;
+    }
+    if (warp == kLoaderWarp) {
         uint32_t free_phase = 0;
         int it = 0;
         for (;;) {
@@ -438,13 +447,18 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
 // Shared memory mirrors a workspace slot (three groups, each with its own full/empty barrier pair, refilled by the
 // loader warp as soon as the tensor core has consumed them), then S as bf16 cells and D hi/lo.
 constexpr int sSlot = 0, sS16 = kSlotBytes, sDhi = sS16 + 2 * kTile, sDlo = sDhi + kTile, sRed = sDlo + kTile;
-static_assert(sRed + 4 * CH * 4 <= oBars, "state role shared memory");
+// Finished output rows (bf16) wait in one of two tiles for the output warp: two boxes of 64 rows x 128 bytes each (value
+// channels 0-63, 64-127) in the 128-byte swizzle of box_piece(), which is what the tiled tensor stores read.
+constexpr int sOut = sRed + 4 * CH * 4, kOutTile = 2 * kBox;
+static_assert(sOut % 1024 == 0 && sOut + 2 * kOutTile <= oBars, "state role shared memory");
 constexpr uint32_t tS = 0, tQS = 128, tD = 256, tQS1 = 384;  // QS/O accumulators alternate between chunks
 
 __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + oBarsState);  // [3]
     uint64_t* empty = full + 3;                                       // [3]
     uint64_t* bar_mma = full + 6;
+    uint64_t* out_full = full + 7;   // [2]
+    uint64_t* out_empty = full + 9;  // [2]
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = warp & 3, cg = warp >> 2;
@@ -459,7 +473,43 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
     if (j0 >= j1 && !(j0 == 0 && p.state_out != p.state_in)) return;
     const WaitCtx ctx{ctl, ctl + 1, p.status};
 
-    if (warp == kCompute / 32) {  // the loader warp
+    if (warp == kOutWarp) {
+        // The output warp: each finished tile of rows goes to the shard-local `out` and, for a head-sharded launch, into
+        // every rank's full buffer -- the all-gather, done here: a peer's buffer is reached over NVLink.  A full chunk
+        // leaves by tiled tensor stores (two per destination), off the compute warps' path; a sequence's last, partial
+        // chunk by the warp's own stores, so that no row beyond the sequence is touched.
+        for (int j = j0; j < j1; ++j) {
+            const int c = j - j0, n = min(CH, T - j * CH);
+            const long long gr0 = row0 + (long long)j * CH;
+            if (!mbar_wait(&out_full[c & 1], (uint32_t)((c >> 1) & 1), ctx, kStatusWaitPrefill)) break;
+            const unsigned char* tile = smem + sOut + (c & 1) * kOutTile;
+            if (n == CH) {
+                if (lane == 0) {
+                    for (int x = 0; x < 2; ++x) {
+                        if (p.out != nullptr) tensor_store_3d(&p.tm_out, x * 64, h, (int)gr0, tile + x * kBox);
+                        for (int pe = 0; pe < p.ranks; ++pe) tensor_store_3d(&p.tm_full[pe], x * 64, p.head0 + h, (int)gr0, tile + x * kBox);
+                    }
+                    bulk_commit();
+                    bulk_wait_read<0>();  // the tile has been read: the compute warps may refill it
+                }
+            } else {
+                for (int e = lane; e < n * 16; e += 32) {
+                    const int r = e >> 4, piece = e & 15;
+                    const uint4 v4 = *reinterpret_cast<const uint4*>(tile + box_piece(r, piece));
+                    if (p.out != nullptr) *reinterpret_cast<uint4*>(p.out + ((gr0 + r) * H + h) * DV + piece * 8) = v4;
+                    const long long at_full = ((gr0 + r) * p.heads_total + p.head0 + h) * DV + piece * 8;
+                    for (int pe = 0; pe < p.ranks; ++pe) *reinterpret_cast<uint4*>(p.full[pe] + at_full) = v4;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&out_empty[c & 1]);
+        }
+        if (lane == 0) bulk_wait_all<0>();
+        tc::fence_before_sync();
+        __syncthreads();
+        return;
+    }
+    if (warp == kLoaderWarp) {
         if (lane == 0) {
             uint32_t ph = 1;  // the empty barriers start released
             for (int j = j0; j < j1; ++j) {
@@ -640,24 +690,18 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
                 }
                 compute_sync();  // the partial sums are read before the next chunk's are written
             }
-            if (live) {
-                uint4 o4[4];
+            // Into the output tile (the output warp takes it from there).
+            if (!mbar_wait(&out_empty[c & 1], (uint32_t)(((c >> 1) & 1) ^ 1), ctx, kStatusWaitPrefill)) { alive = false; break; }
+            if (lane < 16) {
+                unsigned char* dst = smem + sOut + (c & 1) * kOutTile;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4)
-                    o4[c4] = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
-                                        tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
-                if (p.out != nullptr) {
-#pragma unroll
-                    for (int c4 = 0; c4 < 4; ++c4) *reinterpret_cast<uint4*>(p.out + at + c4 * 8) = o4[c4];
-                }
-                // The all-gather of a head-sharded prefill, done here: the row goes straight into every rank's full
-                // buffer (plain stores; a peer's buffer is reached over NVLink), so no exchange step follows the launch.
-                const long long at_full = ((gr0 + i) * p.heads_total + p.head0 + h) * DV + cg * 32;
-                for (int pe = 0; pe < p.ranks; ++pe) {
-#pragma unroll
-                    for (int c4 = 0; c4 < 4; ++c4) *reinterpret_cast<uint4*>(p.full[pe] + at_full + c4 * 8) = o4[c4];
-                }
+                    *reinterpret_cast<uint4*>(dst + box_piece(i, cg * 4 + c4)) = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
+                                                                          tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
             }
+            fence_proxy_async_smem();  // the tensor stores read the tile through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&out_full[c & 1]);
         }
     }
 
@@ -678,7 +722,7 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
 }
 
 // One launch: the state role of one segment on the chain blocks, then the intra role of the next segment on all blocks.
-__global__ void __launch_bounds__(kThreadsTc, 1) prefill_sp_kernel(const __grid_constant__ SpParams p) {
+__global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_constant__ SpParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
     uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
@@ -688,6 +732,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_sp_kernel(const __grid_
         for (int i = 0; i < 4; ++i) mbar_init(bi + i, 1);  // intra role: raw, mma, free, mma2
         uint64_t* bs = reinterpret_cast<uint64_t*>(smem + oBarsState);
         for (int i = 0; i < 7; ++i) mbar_init(bs + i, 1);  // state role: full[3], empty[3], mma
+        for (int i = 0; i < 2; ++i) mbar_init(bs + 7 + i, kCompute / 32);  // output tile full: one arrival per compute warp
+        for (int i = 0; i < 2; ++i) mbar_init(bs + 9 + i, 1);               // output tile empty
         ctl[0] = 0u;
         ctl[1] = 0u;
         mbar_init_fence();
@@ -798,6 +844,9 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     if (!row_tensor_map(&p.tm_q, q, 2, heads, rows_cap) || !row_tensor_map(&p.tm_k, k, 2, heads, rows_cap) ||
         !row_tensor_map(&p.tm_v, v, 2, heads, rows_cap) || !row_tensor_map(&p.tm_g, g, 4, heads, rows_cap))
         return (int)cudaErrorNotSupported;
+    if (out != nullptr && !row_tensor_map(&p.tm_out, out, 2, heads, rows_cap)) return (int)cudaErrorNotSupported;
+    for (int r = 0; r < p.ranks; ++r)
+        if (!row_tensor_map(&p.tm_full[r], p.full[r], 2, p.heads_total, rows_cap)) return (int)cudaErrorNotSupported;
     cudaError_t e = cudaMemsetAsync(p.counters, 0, 2 * sizeof(unsigned int), stream);
     if (e != cudaSuccess) return (int)e;
     const long long sms = sm_count();
@@ -816,7 +865,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             const long long items = chains * seg, want = items < sms ? items : sms;
             if (grid < want) grid = want;
         }
-        prefill_sp_kernel<<<(unsigned)grid, kThreadsTc, kSmemSp, stream>>>(p);
+        prefill_sp_kernel<<<(unsigned)grid, kThreadsSp, kSmemSp, stream>>>(p);
         return (int)cudaGetLastError();
     };
     if (segs == 0) return launch(-1, 0);  // nothing but empty sequences: their states are copied

@@ -16,7 +16,7 @@
 // launch.  Stream order between launches is the only synchronisation: no block ever waits on another block.
 //
 // Workspace slot of one (chain, chunk) item, bytes: Qg 0 | W 16,384 | M 32,768 | Kdec hi 40,960 | Kdec lo 57,344 |
-// U 73,728 (64 rows x 132 floats) | E_last 107,520 (128 floats); 108,544 per slot = 1,696 per row and head, inside
+// U 73,728 (FP32, 32 cells of four value channels x 64 rows) | E_last 106,496 (128 floats); 107,008 per slot = 1,672 per row and head, inside
 // the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).  The last
 // 256 bytes of the workspace hold the two item counters.
 
@@ -33,22 +33,21 @@ namespace {
 
 using namespace pf;
 
-constexpr int US = 132;  // FP32 row stride of U (rows 4 banks apart, float4 aligned)
+// U is kept in FP32 as 16-byte cells of four value channels, [32 cells][64 rows], so that both its writer (a thread
+// holds a row's channels) and its reader store and load consecutive cells.
 constexpr int wQg = 0, wW = kTile, wMm = 2 * kTile, wKdHi = wMm + kTile / 2, wKdLo = wKdHi + kTile, wU = wKdLo + kTile;
-constexpr int wEgl = wU + CH * US * 4, kSlotBytes = 108544;
-static_assert(wEgl + 512 <= kSlotBytes && wU == 73728, "workspace slot layout");
+constexpr int kUBytes = CH * DV * 4, wEgl = wU + kUBytes, kSlotBytes = wEgl + 512;
+static_assert(kSlotBytes == 107008 && wU == 73728, "workspace slot layout");
 
 // Staging of a chunk's raw rows in the intra kernel: dense boxes of 64 rows x 128 bytes written by tiled tensor copies
 // with the 128-byte swizzle (16-byte piece p of row r sits at piece p ^ (r & 7)), so that threads walking down the
 // rows of one column spread over all banks.  q, k, v: two boxes each (channels 0-63, 64-127); the log decays: four.
 constexpr int kBox = CH * 128;  // 8 KiB
-constexpr int oBoxQ = 0, oBoxK = 2 * kBox, oBoxV = 4 * kBox, oBoxG = 6 * kBox;
-static_assert(oBoxG + 4 * kBox <= oKg, "raw staging must end below the operand tiles");
 // Byte offset inside a tensor's staging of the 16-byte piece `piece` (0..15 for bf16 rows, 0..31 for f32 rows) of row r.
 __device__ __forceinline__ int box_piece(int r, int piece) { return (piece >> 3) * kBox + r * 128 + (((piece & 7) ^ (r & 7)) << 4); }
 
 struct SpParams {
-    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_g;  // [rows][H][128] as (128, H, rows); boxes of 64 rows x 128 bytes
+    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_g;  // [rows][H][128] as (128, H, rows); boxes of 64 rows x 128 bytes, 128-byte swizzle
     alignas(64) CUtensorMap tm_out;                  // the shard-local output, the same way
     alignas(64) CUtensorMap tm_full[8];              // every rank's full output buffer: (128, heads_total, rows)
     int H, batch;
@@ -88,355 +87,371 @@ constexpr int kThreadsSp = kCompute + 64, kLoaderWarp = kCompute / 32, kOutWarp 
 static_assert(kSmemSp <= 232448, "shared memory budget");
 
 // =====================================================================================================================
-// Pass 1: the state-independent part of every (chain, chunk) item of the segment, items spread over the grid.
+// Pass 1: the state-independent part of every (chain, chunk) item of the segment, items handed out by a counter.
+//
+// A block runs two items at a time: two groups of eight warps, each with its own staging, tensor-memory columns,
+// barriers and loader warp, so that one group's waits (tensor-core rounds, tensor-memory reads, its own barriers) are
+// filled by the other group's arithmetic.  To fit two items, a group keeps 96 KiB: q, k, v arrive as operand tiles
+// already (a tiled tensor copy whose box order is 8 channels, row, cell puts them in the cell layout) and are
+// turned into Qg and Kg in place; the log decays arrive in swizzled boxes and become E in place; the inverse's FP32
+// scratch goes over E and Kinv once they are dead; and everything the state role needs leaves for the workspace
+// straight from registers (Qg, Kdec hi/lo, E_last, M, W, U), so no result tile lives in shared memory.
 // =====================================================================================================================
-__device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_t tm) {
-    uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
+constexpr int kGroupThreads = 256, kGroups = 2;
+constexpr int gQ = 0, gK = kTile, gV = 2 * kTile, gG = 3 * kTile, gKi = gG + 4 * kBox;  // Q/Qg | K/Kg | V | g/E | Kinv
+constexpr int gT = gG, gL = gG + CH * LS * 4, gP = gL + CH * LS * 4, gTp = gL;            // inverse scratch over E | Kinv; T' (hi | lo box) over L
+static_assert(gTp % 1024 == 0, "swizzled tiles are 1024-byte aligned");
+constexpr int gBeta = gKi + kTile, gEgl = gBeta + CH * 4, gScan = gEgl + 128 * 4, gBars = gScan + 2 * 128 * 4, gItem = gBars + 32;
+constexpr int kGroupBytes = 101376;
+static_assert(gP + 32 * 32 * 4 <= gKi + kTile && gTp + kTile <= gP && gItem + 16 <= kGroupBytes && kGroupBytes % 1024 == 0, "group map");
+static_assert(kGroups * kGroupBytes <= oCtl, "two groups must fit below the block's control words");
+constexpr uint32_t gcL = 0, gcM = 64, gcW = 0, gcU = 128, kGroupCols = 256;
+
+template <int G>
+__device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* smem, const uint32_t tm_block, const WaitCtx& ctx) {
+    constexpr int BAR = 2 + G;
+    unsigned char* gs = smem + G * kGroupBytes;
+    const uint32_t tm = tm_block + G * kGroupCols;
+    uint64_t* bar_raw = reinterpret_cast<uint64_t*>(gs + gBars);
     uint64_t* bar_mma = bar_raw + 1;
-    uint64_t* bar_free = bar_raw + 2;
-    uint64_t* bar_mma2 = bar_raw + 3;
-    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
-    volatile int* item2 = reinterpret_cast<volatile int*>(smem + oCtl) + 4;  // the item of each staging generation
-    float* betas2 = reinterpret_cast<float*>(smem + oBeta);
-    float* egl = reinterpret_cast<float*>(smem + oEGL);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quad = warp & 3, cg = warp >> 2;
+    uint64_t* bar_mma2 = bar_raw + 2;
+    uint64_t* bar_free = bar_raw + 3;
+    volatile int* item_slot = reinterpret_cast<volatile int*>(gs + gItem);
+    float* betas = reinterpret_cast<float*>(gs + gBeta);
+    float* egl = reinterpret_cast<float*>(gs + gEgl);
+    const int gt = threadIdx.x - G * kGroupThreads, gw = gt >> 5, lane = gt & 31;
+    const int quad = gw & 3, cg = gw >> 2;  // a warp reaches tensor-memory lanes 32 * (warp % 4)..; cg picks a half of the columns
     const int lane_row64 = quad * 16 + lane;
     const int H = p.H, chains = p.batch * H;
-    const long long items = (long long)chains * p.seg_chunks;  // item = jj * chains + chain: chunk-major
-    const WaitCtx ctx{ctl, ctl + 1, p.status};
-
-    // Decodes an item; returns false when the sequence has no such chunk.
-    auto decode = [&](long long item, int& chain, int& j, long long& gr0, int& n, int& h) -> bool {
-        chain = (int)(item % chains);
-        j = p.intra_chunk0 + (int)(item / chains);
-        const int b = chain / H;
-        h = chain % H;
-        const int r0 = p.cu[b], T = p.cu[b + 1] - r0;
-        if ((long long)j * CH >= T) return false;
-        gr0 = (long long)r0 + (long long)j * CH;
-        n = min(CH, T - j * CH);
-        return true;
+    auto group_sync = [&]() { named_bar_sync(BAR, kGroupThreads); };
+    auto publish = [&]() {
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        group_sync();
+        tc::fence_after_sync();
     };
-
-    // ---- the loader warp ---------------------------------------------------------------------------------------------
-    // A full chunk arrives by ten tiled tensor copies issued by one lane.  A sequence's last, partial chunk is copied
-    // by the warp's own loads and stores instead (rows past the sequence's end are not read, they become zero), so no
-    // copy ever reaches past the rows the caller's metadata names.
-    if (warp == kOutWarp) {  // the state role's output warp has no part in this role
-        tc::fence_before_sync();
-        __syncthreads();
-        return;
-    }
-    if (warp == kLoaderWarp) {
-        uint32_t free_phase = 0;
-        int it = 0;
-        for (;;) {
-            long long item = 0;
-            if (lane == 0) item = atomicAdd(&p.counters[p.ctr], 1u);
-            item = __shfl_sync(0xffffffffu, item, 0);
-            int chain = 0, j = 0, n = 0, h = 0;
-            long long gr0 = 0;
-            const bool last = item >= items;
-            if (!last && !decode(item, chain, j, gr0, n, h)) continue;
-            if (last) {  // tell the compute warps that there is nothing more
-                if (it > 0 && !mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
-                if (lane == 0) {
-                    item2[it & 1] = -1;
-                    mbar_arrive(bar_raw);
-                }
-                break;
-            }
-            float b0 = 0.0f, b1 = 0.0f;
-            if (lane < n) b0 = p.beta[(gr0 + lane) * H + h];
-            if (lane + 32 < n) b1 = p.beta[(gr0 + lane + 32) * H + h];
-            if (it > 0) {
-                if (!mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
-                free_phase ^= 1u;
-            }
-            float* bt = betas2 + (it & 1) * CH;
-            bt[lane] = b0;
-            bt[lane + 32] = b1;
-            if (lane == 0) item2[it & 1] = (int)item;
-            if (n == CH) {
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(bar_raw, 10u * kBox);
-                    const int row = (int)gr0;
-                    for (int x = 0; x < 2; ++x) {
-                        tensor_load_3d(smem + oBoxQ + x * kBox, &p.tm_q, x * 64, h, row, bar_raw);
-                        tensor_load_3d(smem + oBoxK + x * kBox, &p.tm_k, x * 64, h, row, bar_raw);
-                        tensor_load_3d(smem + oBoxV + x * kBox, &p.tm_v, x * 64, h, row, bar_raw);
-                    }
-                    for (int x = 0; x < 4; ++x) tensor_load_3d(smem + oBoxG + x * kBox, &p.tm_g, x * 32, h, row, bar_raw);
-                }
-            } else {
-                const uint4 z = make_uint4(0, 0, 0, 0);
-                for (int e = lane; e < CH * 16; e += 32) {
-                    const int r = e >> 4, piece = e & 15;
-                    const long long at = ((gr0 + r) * H + h) * DK + piece * 8;
-                    const bool in = r < n;
-                    *reinterpret_cast<uint4*>(smem + oBoxQ + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.q + at) : z;
-                    *reinterpret_cast<uint4*>(smem + oBoxK + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.k + at) : z;
-                    *reinterpret_cast<uint4*>(smem + oBoxV + box_piece(r, piece)) = in ? *reinterpret_cast<const uint4*>(p.v + at) : z;
-                }
-                for (int e = lane; e < CH * 32; e += 32) {
-                    const int r = e >> 5, piece = e & 31;
-                    const long long at = ((gr0 + r) * H + h) * DK + piece * 4;
-                    *reinterpret_cast<uint4*>(smem + oBoxG + box_piece(r, piece)) = r < n ? *reinterpret_cast<const uint4*>(p.g + at) : z;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_raw);
-            }
-            ++it;
-        }
-        tc::fence_before_sync();
-        __syncthreads();
-        return;
-    }
-
-    uint32_t raw_phase = 0, mma_phase = 0, mma2_phase = 0;
     auto mma_issue = [&](uint64_t* bar, auto&& issue) {
-        if (tid == 0) {
+        if (gt == 0) {
             issue();
             tc::mma_commit(bar);
-            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+            atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
         }
     };
+    uint32_t raw_phase = 0, mma_phase = 0, mma2_phase = 0;
     auto mma_wait = [&](uint64_t* bar, uint32_t& phase) -> bool {
         if (!mbar_wait(bar, phase, ctx, kStatusWaitPrefill)) return false;
         phase ^= 1u;
         tc::fence_after_sync();
         return true;
     };
-    auto mma_round = [&](auto&& issue) -> bool {
-        mma_issue(bar_mma, issue);
-        return mma_wait(bar_mma, mma_phase);
-    };
-    auto publish_operands = [&]() {
-        fence_proxy_async_smem();
-        tc::fence_before_sync();
-        compute_sync();
-        tc::fence_after_sync();
-    };
 
-    for (int it = 0;; ++it) {
+    for (;;) {
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) break;
         raw_phase ^= 1u;
-        const int item = item2[it & 1];
+        const int item = *item_slot;
         if (item < 0) break;
-        int chain, j, n, h;
-        long long gr0;
-        decode(item, chain, j, gr0, n, h);
-        unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, j - p.intra_chunk0);
-        const float* betas = betas2 + (it & 1) * CH;
-        // The previous item's bulk stores must have read their tiles before this item overwrites them.
-        if (tid == 0) bulk_wait_read<0>();
-        compute_sync();
+        const int chain = item % chains, jj = item / chains;
+        unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, jj);
 
-        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging buffer --------------------------
+        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging boxes ----------------------------
         {
-            const int part = tid >> 7, d = tid & 127;
-            unsigned char* gbox = smem + oBoxG + (d & 3) * 4;
-            float* totals = reinterpret_cast<float*>(smem + oScan);
-            float loc[16], G = 0.0f;
+            const int part = gt >> 7, d = gt & 127;
+            // Row r of this thread's channel: box d / 32, piece (d % 32) / 4 swizzled by r & 7, float d % 4.
+            unsigned char* col = gs + gG + (d >> 5) * kBox + part * 32 * 128 + (d & 3) * 4;
+            const int pc = (d >> 2) & 7;
+            float* totals = reinterpret_cast<float*>(gs + gScan);
+            float run[32], acc = 0.0f;
 #pragma unroll
-            for (int r = 0; r < 16; ++r) {
-                G += *reinterpret_cast<float*>(gbox + box_piece(part * 16 + r, d >> 2));
-                loc[r] = G;
+            for (int r = 0; r < 32; ++r) {
+                acc += *reinterpret_cast<const float*>(col + r * 128 + ((pc ^ (r & 7)) << 4));
+                run[r] = acc;
             }
-            totals[part * 128 + d] = G;
-            compute_sync();
-            float base = 0.0f;
-            for (int q2 = 0; q2 < part; ++q2) base += totals[q2 * 128 + d];
+            totals[part * 128 + d] = acc;
+            group_sync();
+            const float base = part ? totals[d] : 0.0f;
             float e = 1.0f;
 #pragma unroll
-            for (int r = 0; r < 16; ++r) {
-                e = __expf(base + loc[r]);
-                *reinterpret_cast<float*>(gbox + box_piece(part * 16 + r, d >> 2)) = e;
+            for (int r = 0; r < 32; ++r) {
+                e = __expf(base + run[r]);
+                *reinterpret_cast<float*>(col + r * 128 + ((pc ^ (r & 7)) << 4)) = e;
             }
-            if (part == 3) {
+            if (part == 1) {
                 egl[d] = e;
                 if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
             }
         }
-        compute_sync();
+        group_sync();
 
-        // ---- 2a. the operands of L: Kg = K E and Kinv = K / E ---------------------------------------------------------------
+        // ---- 2a. from k: Kg = K E in place, Kinv = K / E, Kdec = K E_last / E as bf16 hi + lo out to the workspace -------
         {
-            const int r = tid & 63, cgrp = tid >> 6;
+            const int r = gt & 63, cq = gt >> 6;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = cgrp * 2 + cc;
-                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oBoxK + box_piece(r, c));
-                const float4 e0 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c));
-                const float4 e1 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c + 1));
-                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
-                uint32_t kg[4], ki[4];
-#pragma unroll
-                for (int u2 = 0; u2 < 4; ++u2) {
-                    const float k0 = __uint_as_float(kw[u2] << 16), k1 = __uint_as_float(kw[u2] & 0xffff0000u);
-                    const float ea = E[2 * u2], eb = E[2 * u2 + 1];
-                    kg[u2] = tc::bf16x2(k0 * ea, k1 * eb);
-                    ki[u2] = tc::bf16x2(k0 * __fdividef(1.0f, ea), k1 * __fdividef(1.0f, eb));
-                }
-                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
-            }
-        }
-        publish_operands();
-        // ---- 3a. L = Kg Kinv^T starts while the other operands are built ----------------------------------------------------
-        mma_issue(bar_mma, [&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-        });
-        // ---- 2b. Qg = Q E, Kdec = K E_last / E as bf16 hi + lo, V as cells --------------------------------------------------------
-        {
-            const int r = tid & 63, cgrp = tid >> 6;
-#pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = cgrp * 2 + cc;
-                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oBoxK + box_piece(r, c));
-                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oBoxQ + box_piece(r, c));
-                const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oBoxV + box_piece(r, c));
-                const float4 e0 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c));
-                const float4 e1 = *reinterpret_cast<const float4*>(smem + oBoxG + box_piece(r, 2 * c + 1));
+            for (int cc = 0; cc < 4; ++cc) {
+                const int c = cq * 4 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(gs + gK + box_piece(r, c));
+                const float4 e0 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c));
+                const float4 e1 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c + 1));
                 const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
                 const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
                 const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
                 const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
-                uint32_t qg[4], dh[4], dl[4];
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
+                uint32_t kg[4], ki[4], dh[4], dl[4];
 #pragma unroll
                 for (int u2 = 0; u2 < 4; ++u2) {
                     const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
-                    const float qf[2] = {__uint_as_float(qw[u2] << 16), __uint_as_float(qw[u2] & 0xffff0000u)};
-                    float bq[2], hi[2], lo[2];
+                    float a[2], ci[2], hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const float e = E[2 * u2 + u];
-                        bq[u] = qf[u] * e;
-                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * __fdividef(1.0f, e)), hi[u], lo[u]);
+                        const float e = E[2 * u2 + u], einv = __fdividef(1.0f, e);
+                        a[u] = kf[u] * e;
+                        ci[u] = kf[u] * einv;
+                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * einv), hi[u], lo[u]);
                     }
-                    qg[u2] = tc::bf16x2(bq[0], bq[1]);
+                    kg[u2] = tc::bf16x2(a[0], a[1]);
+                    ki[u2] = tc::bf16x2(ci[0], ci[1]);
                     dh[u2] = tc::bf16x2(hi[0], hi[1]);
                     dl[u2] = tc::bf16x2(lo[0], lo[1]);
                 }
-                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
+                *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(gs + gKi + box_piece(r, c)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(cell(slot + wKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(cell(slot + wKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
             }
         }
-        publish_operands();
-        if (tid == 0) {
-            mbar_arrive(bar_free);  // the loader may stream the next item's rows in
-            // Qg, Kdec hi/lo and exp(G_last) are final: out to the workspace while the rest of the item is computed.
-            bulk_store(slot + wQg, smem + oQg, kTile);
-            bulk_store(slot + wKdHi, smem + oKdHi, kTile);
-            bulk_store(slot + wKdLo, smem + oKdLo, kTile);
-            bulk_store(slot + wEgl, smem + oEGL, 512);
-            bulk_commit();
+        publish();
+        // ---- 3a. L = Kg Kinv^T starts while Qg is built -----------------------------------------------------------------
+        mma_issue(bar_mma, [&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + gcL, tc::desc_sw128_kmajor(gs + gK, CH, k0), tc::desc_sw128_kmajor(gs + gKi, CH, k0), id, k0 > 0);
+        });
+        // ---- 2b. Qg = Q E in place and out to the workspace; E_last out ----------------------------------------------------
+        {
+            const int r = gt & 63, cq = gt >> 6;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const int c = cq * 4 + cc;
+                const uint4 q8 = *reinterpret_cast<const uint4*>(gs + gQ + box_piece(r, c));
+                const float4 e0 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c));
+                const float4 e1 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c + 1));
+                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                const uint32_t qw[4] = {q8.x, q8.y, q8.z, q8.w};
+                uint32_t qg[4];
+#pragma unroll
+                for (int u2 = 0; u2 < 4; ++u2)
+                    qg[u2] = tc::bf16x2(__uint_as_float(qw[u2] << 16) * E[2 * u2], __uint_as_float(qw[u2] & 0xffff0000u) * E[2 * u2 + 1]);
+                const uint4 o = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+                *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = o;
+                *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = o;
+            }
+            if (gt < 32) *reinterpret_cast<float4*>(slot + wEgl + gt * 16) = *reinterpret_cast<const float4*>(egl + gt * 4);
         }
-        // ---- 3b. M = Qg Kinv^T ------------------------------------------------------------------------------------------------
+        publish();
+        // ---- 3b. M = Qg Kinv^T -------------------------------------------------------------------------------------------
         mma_issue(bar_mma2, [&] {
             constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
             for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
+                tc::mma_bf16(tm + gcM, tc::desc_sw128_kmajor(gs + gQ, CH, k0), tc::desc_sw128_kmajor(gs + gKi, CH, k0), id, k0 > 0);
         });
         if (!mma_wait(bar_mma, mma_phase)) break;
         if (!mma_wait(bar_mma2, mma2_phase)) break;
 
-        // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) --------------------------
+        // ---- 4. L (FP32, strictly lower, times beta_i) into the scratch; M (bf16 cells, lower with the diagonal) out -------
         {
-            uint32_t r[32];
-            const int half = cg & 1, i = lane_row64;
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg < 2 ? cL : cMm) + half * 32), r);
-            tc::tmem_ld_wait();
-            if (lane < 16) {
-                if (cg < 2) {
-                    float* Lr = reinterpret_cast<float*>(smem + oL) + i * LS + half * 32;
-                    const float bi = betas[i];
+            const int i = lane_row64;
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) Lr[jj] = half * 32 + jj < i ? bi * __uint_as_float(r[jj]) : 0.0f;
-                } else {
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg == 0 ? gcL : gcM) + half * 32), r);
+                tc::tmem_ld_wait();
+                if (lane < 16) {
+                    if (cg == 0) {
+                        float* Lr = reinterpret_cast<float*>(gs + gL) + i * LS + half * 32;
+                        const float bi = betas[i];
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj)
-                        if (half * 32 + jj > i) r[jj] = 0u;
+                        for (int j2 = 0; j2 < 32; ++j2) Lr[j2] = half * 32 + j2 < i ? bi * __uint_as_float(r[j2]) : 0.0f;
+                    } else {
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
+                        for (int j2 = 0; j2 < 32; ++j2)
+                            if (half * 32 + j2 > i) r[j2] = 0u;
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(slot + wMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
+                    }
                 }
             }
         }
-        compute_sync();
+        tc::fence_before_sync();
+        group_sync();
 
-        // ---- 5. T = (I + L)^-1 in FP32, T' = T diag(beta) as bf16 hi + lo cells ----------------------------------------------
+        // ---- 5. T = (I + L)^-1 in FP32, T' = T diag(beta) as bf16 hi + lo cells (over L, dead by then) -----------------------
         {
-            const float* Lm = reinterpret_cast<const float*>(smem + oL);
-            float* Tm = reinterpret_cast<float*>(smem + oT);
-            float* Pm = reinterpret_cast<float*>(smem + oP);
-            invert_diag16(Lm, Tm, tid);
-            invert_level<4>(Lm, Tm, Pm, tid);
-            invert_level<5>(Lm, Tm, Pm, tid);
-            const int i = tid & 63, c = tid >> 6;
-            float t8[8];
+            const float* Lm = reinterpret_cast<const float*>(gs + gL);
+            float* Tm = reinterpret_cast<float*>(gs + gT);
+            float* Pm = reinterpret_cast<float*>(gs + gP);
+            invert_diag16<kGroupThreads, BAR>(Lm, Tm, gt);
+            invert_level<4, kGroupThreads, BAR>(Lm, Tm, Pm, gt);
+            invert_level<5, kGroupThreads, BAR>(Lm, Tm, Pm, gt);
+            const int i = gt & 63, cq = gt >> 6;
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) t8[jj] = Tm[i * LS + c * 8 + jj] * betas[c * 8 + jj];
-            compute_sync();
-            uint32_t wh[4], wl[4];
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cq + cc * 4;
+                uint32_t wh[4], wl[4];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                float h0, l0, h1, l1;
-                tc::split_bf16(t8[2 * jj], h0, l0);
-                tc::split_bf16(t8[2 * jj + 1], h1, l1);
-                wh[jj] = tc::bf16x2(h0, h1);
-                wl[jj] = tc::bf16x2(l0, l1);
+                for (int j2 = 0; j2 < 4; ++j2) {
+                    float h0, l0, h1, l1;
+                    tc::split_bf16(Tm[i * LS + c * 8 + 2 * j2] * betas[c * 8 + 2 * j2], h0, l0);
+                    tc::split_bf16(Tm[i * LS + c * 8 + 2 * j2 + 1] * betas[c * 8 + 2 * j2 + 1], h1, l1);
+                    wh[j2] = tc::bf16x2(h0, h1);
+                    wl[j2] = tc::bf16x2(l0, l1);
+                }
+                *reinterpret_cast<uint4*>(gs + gTp + box_piece(i, c)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                *reinterpret_cast<uint4*>(gs + gTp + kBox + box_piece(i, c)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
             }
-            *reinterpret_cast<uint4*>(cell(smem + oTpHi, CH, c, i)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-            *reinterpret_cast<uint4*>(cell(smem + oTpLo, CH, c, i)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
         }
-        publish_operands();
+        publish();
 
         // ---- 6. W = T' Kg (bf16 T'), U = T' V (T' hi + lo) -------------------------------------------------------------------
-        if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + cW, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oKg, CH, 0, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + cU, tc::desc_kmajor_bf16(smem + oTpLo, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oV, CH, 0, k0), id, true);
-            })) break;
+        mma_issue(bar_mma, [&] {
+            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0);
+            const unsigned char* tph = gs + gTp;
+            const unsigned char* tpl = gs + gTp + kBox;
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + gcW, tc::desc_sw128_kmajor(tph, CH, k0), tc::desc_sw128_mnmajor(gs + gK, CH, k0), id, k0 > 0);
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + gcU, tc::desc_sw128_kmajor(tph, CH, k0), tc::desc_sw128_mnmajor(gs + gV, CH, k0), id, k0 > 0);
+            for (int k0 = 0; k0 < CH; k0 += 16)
+                tc::mma_bf16(tm + gcU, tc::desc_sw128_kmajor(tpl, CH, k0), tc::desc_sw128_mnmajor(gs + gV, CH, k0), id, true);
+        });
+        if (!mma_wait(bar_mma, mma_phase)) break;
+        // Nothing of this item is left in the group's shared memory: the loader may bring the next item in.
+        if (gt == 0) mbar_arrive(bar_free);
 
-        // ---- 7. W as bf16 cells and U as FP32 rows (over Kg | Kinv | T', all dead), then M, W, U out to the workspace ----------
+        // ---- 7. W as bf16 cells and U as FP32 rows, from tensor memory to the workspace ---------------------------------------
         {
-            uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, cW + cg * 32), r);
-            tc::tmem_ld_wait();
-            if (lane < 16) {
+            const int i = lane_row64;
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oW, CH, cg * 4 + cc, lane_row64)) = pack8(r + cc * 8);
-            }
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, cU + cg * 32), r);
-            tc::tmem_ld_wait();
-            if (lane < 16) {
-                float* Ur = reinterpret_cast<float*>(smem + oKg) + lane_row64 * US + cg * 32;
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[32];
+                const int col = cg * 64 + half * 32;
+                tc::tmem_ld32(tc::tmem_addr(tm, quad, gcW + col), r);
+                tc::tmem_ld_wait();
+                if (lane < 16) {
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj)
-                    *reinterpret_cast<uint4*>(Ur + jj * 4) = make_uint4(r[jj * 4], r[jj * 4 + 1], r[jj * 4 + 2], r[jj * 4 + 3]);
+                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(slot + wW, CH, col / 8 + cc, i)) = pack8(r + cc * 8);
+                }
+                tc::tmem_ld32(tc::tmem_addr(tm, quad, gcU + col), r);
+                tc::tmem_ld_wait();
+                if (lane < 16) {
+#pragma unroll
+                    for (int j2 = 0; j2 < 8; ++j2)
+                        *reinterpret_cast<uint4*>(cell(slot + wU, CH, col / 4 + j2, i)) = make_uint4(r[j2 * 4], r[j2 * 4 + 1], r[j2 * 4 + 2], r[j2 * 4 + 3]);
+                }
             }
         }
-        publish_operands();
-        if (tid == 0) {
-            bulk_store(slot + wMm, smem + oMm, kTile / 2);
-            bulk_store(slot + wW, smem + oW, kTile);
-            bulk_store(slot + wU, smem + oKg, CH * US * 4);
-            bulk_commit();
+        tc::fence_before_sync();
+        group_sync();
+        tc::fence_after_sync();
+    }
+}
+
+// The loader warp of group G: takes items off the counter and brings each one's rows into the group's staging.  A full
+// chunk arrives by ten tiled tensor copies issued by one lane; a sequence's last, partial chunk is copied by the
+// warp's own loads and stores (rows past the sequence's end are not read, they become zero), so no copy ever reaches
+// past the rows the caller's metadata names.
+template <int G>
+__device__ __forceinline__ void intra_loader(const SpParams& p, unsigned char* smem, const WaitCtx& ctx) {
+    unsigned char* gs = smem + G * kGroupBytes;
+    uint64_t* bar_raw = reinterpret_cast<uint64_t*>(gs + gBars);
+    uint64_t* bar_free = bar_raw + 3;
+    volatile int* item_slot = reinterpret_cast<volatile int*>(gs + gItem);
+    float* betas = reinterpret_cast<float*>(gs + gBeta);
+    const int lane = threadIdx.x & 31;
+    const int H = p.H, chains = p.batch * H;
+    const long long items = (long long)chains * p.seg_chunks;  // item = jj * chains + chain: chunk-major
+    uint32_t free_phase = 0;
+    for (int it = 0;;) {
+        long long item = 0;
+        if (lane == 0) item = atomicAdd(&p.counters[p.ctr], 1u);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        const bool last = item >= items;
+        int h = 0, n = 0;
+        long long gr0 = 0;
+        if (!last) {
+            const int chain = (int)(item % chains), j = p.intra_chunk0 + (int)(item / chains);
+            const int b = chain / H;
+            h = chain % H;
+            const int r0 = p.cu[b], T = p.cu[b + 1] - r0;
+            if ((long long)j * CH >= T) continue;  // the sequence has no such chunk
+            gr0 = (long long)r0 + (long long)j * CH;
+            n = min(CH, T - j * CH);
+        }
+        float b0 = 0.0f, b1 = 0.0f;
+        if (lane < n) b0 = p.beta[(gr0 + lane) * H + h];
+        if (lane + 32 < n) b1 = p.beta[(gr0 + lane + 32) * H + h];
+        if (it > 0) {
+            if (!mbar_wait(bar_free, free_phase, ctx, kStatusWaitPrefill)) break;
+            free_phase ^= 1u;
+        }
+        ++it;
+        if (last) {  // tell the compute warps that there is nothing more
+            if (lane == 0) {
+                *item_slot = -1;
+                mbar_arrive(bar_raw);
+            }
+            break;
+        }
+        betas[lane] = b0;
+        betas[lane + 32] = b1;
+        if (lane == 0) *item_slot = (int)item;
+        if (n == CH) {
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar_raw, 3u * kTile + 4u * kBox);
+                const int row = (int)gr0;
+                for (int x = 0; x < 4; ++x) tensor_load_3d(gs + gG + x * kBox, &p.tm_g, x * 32, h, row, bar_raw);
+                for (int x = 0; x < 2; ++x) tensor_load_3d(gs + gK + x * kBox, &p.tm_k, x * 64, h, row, bar_raw);
+                for (int x = 0; x < 2; ++x) tensor_load_3d(gs + gQ + x * kBox, &p.tm_q, x * 64, h, row, bar_raw);
+                for (int x = 0; x < 2; ++x) tensor_load_3d(gs + gV + x * kBox, &p.tm_v, x * 64, h, row, bar_raw);
+            }
+        } else {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int e = lane; e < CH * 16; e += 32) {
+                const int r = e >> 4, c = e & 15;
+                const long long at = ((gr0 + r) * H + h) * DK + c * 8;
+                const bool in = r < n;
+                *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = in ? *reinterpret_cast<const uint4*>(p.q + at) : z;
+                *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = in ? *reinterpret_cast<const uint4*>(p.k + at) : z;
+                *reinterpret_cast<uint4*>(gs + gV + box_piece(r, c)) = in ? *reinterpret_cast<const uint4*>(p.v + at) : z;
+            }
+            for (int e = lane; e < CH * 32; e += 32) {
+                const int r = e >> 5, piece = e & 31;
+                const long long at = ((gr0 + r) * H + h) * DK + piece * 4;
+                *reinterpret_cast<uint4*>(gs + gG + box_piece(r, piece)) = r < n ? *reinterpret_cast<const uint4*>(p.g + at) : z;
+            }
+            fence_proxy_async_smem();  // V is read by the tensor core as it stands
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_raw);
         }
     }
-    if (tid == 0) bulk_wait_all<0>();
+}
+
+__device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_t tm) {
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + oCtl);
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (tid == 0) {
+        for (int g = 0; g < kGroups; ++g) {
+            uint64_t* b = reinterpret_cast<uint64_t*>(smem + g * kGroupBytes + gBars);
+            for (int i = 0; i < 4; ++i) mbar_init(b + i, 1);  // raw, mma, mma2, free
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (warp == kLoaderWarp) intra_loader<0>(p, smem, ctx);
+    else if (warp == kOutWarp) intra_loader<1>(p, smem, ctx);
+    else if (warp < kGroupThreads / 32) intra_group<0>(p, smem, tm, ctx);
+    else intra_group<1>(p, smem, tm, ctx);
     tc::fence_before_sync();
     __syncthreads();
 }
@@ -446,7 +461,7 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
 // =====================================================================================================================
 // Shared memory mirrors a workspace slot (three groups, each with its own full/empty barrier pair, refilled by the
 // loader warp as soon as the tensor core has consumed them), then S as bf16 cells and D hi/lo.
-constexpr int sSlot = 0, sS16 = kSlotBytes, sDhi = sS16 + 2 * kTile, sDlo = sDhi + kTile, sRed = sDlo + kTile;
+constexpr int sSlot = 0, sS16 = (kSlotBytes + 1023) / 1024 * 1024, sDhi = sS16 + 2 * kTile, sDlo = sDhi + kTile, sRed = sDlo + kTile;
 // Finished output rows (bf16) wait in one of two tiles for the output warp: two boxes of 64 rows x 128 bytes each (value
 // channels 0-63, 64-127) in the 128-byte swizzle of box_piece(), which is what the tiled tensor stores read.
 constexpr int sOut = sRed + 4 * CH * 4, kOutTile = 2 * kBox;
@@ -519,8 +534,8 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
                 bulk_load(smem + sSlot + wQg, slot + wQg, 2 * kTile, &full[0]);
                 bulk_load(smem + sSlot + wEgl, slot + wEgl, 512, &full[0]);
                 if (!mbar_wait(&empty[1], ph, ctx, kStatusWaitPrefill)) break;
-                mbar_arrive_expect_tx(&full[1], CH * US * 4);
-                bulk_load(smem + sSlot + wU, slot + wU, CH * US * 4, &full[1]);
+                mbar_arrive_expect_tx(&full[1], kUBytes);
+                bulk_load(smem + sSlot + wU, slot + wU, kUBytes, &full[1]);
                 if (!mbar_wait(&empty[2], ph, ctx, kStatusWaitPrefill)) break;
                 mbar_arrive_expect_tx(&full[2], kTile / 2 + 2 * kTile);
                 bulk_load(smem + sSlot + wMm, slot + wMm, kTile / 2 + 2 * kTile, &full[2]);
@@ -618,10 +633,11 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
             tc::tmem_ld32(tc::tmem_addr(tm, quad, tD + cg * 32), r);
             tc::tmem_ld_wait();
             if (lane < 16) {
-                const float* Ur = reinterpret_cast<const float*>(smem + sSlot + wU) + lane_row64 * US + cg * 32;
+                unsigned char* Ut = smem + sSlot + wU;
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
-                    const float4 u0 = *reinterpret_cast<const float4*>(Ur + cc * 8), u1 = *reinterpret_cast<const float4*>(Ur + cc * 8 + 4);
+                    const float4 u0 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * 8 + cc * 2, lane_row64));
+                    const float4 u1 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * 8 + cc * 2 + 1, lane_row64));
                     const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
                     uint32_t wh[4], wl[4];
 #pragma unroll
@@ -728,8 +744,6 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
     uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
     const int tid = threadIdx.x, warp = tid >> 5;
     if (tid == 0) {
-        uint64_t* bi = reinterpret_cast<uint64_t*>(smem + oBars);
-        for (int i = 0; i < 4; ++i) mbar_init(bi + i, 1);  // intra role: raw, mma, free, mma2
         uint64_t* bs = reinterpret_cast<uint64_t*>(smem + oBarsState);
         for (int i = 0; i < 7; ++i) mbar_init(bs + i, 1);  // state role: full[3], empty[3], mma
         for (int i = 0; i < 2; ++i) mbar_init(bs + 7 + i, kCompute / 32);  // output tile full: one arrival per compute warp
@@ -897,7 +911,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
 // intra role writes every byte of a slot that the state role reads, and each call clears the counters itself.  All calls share the one array, so two calls in flight at once (two
 // streams, two threads) overwrite each other's slots; the caller serialises them.
 constexpr int kStaticSlots = 64;
-constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes + kCounterBytes;  // 6,947,072 bytes
+constexpr long long kStaticScratchBytes = (long long)kStaticSlots * kSlotBytes + kCounterBytes;  // 6,848,768 bytes
 static __device__ __align__(256) unsigned char g_prefill_scratch[kStaticScratchBytes];
 
 // The array's name is a host-side handle here, not a device address: the address a kernel can use is asked for once

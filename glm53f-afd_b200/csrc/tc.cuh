@@ -49,6 +49,16 @@ __device__ __forceinline__ uint64_t desc_kmajor_bf16(const unsigned char* tile, 
 __device__ __forceinline__ uint64_t desc_mnmajor_bf16(const unsigned char* tile, int R, int mn0, int k0) {
     return smem_desc(tile + ((size_t)(mn0 / 8) * R + k0) * 16, 128, (uint32_t)R * 16);
 }
+// Operand tiles in the 128-byte swizzle (what a tiled tensor copy with that swizzle writes): boxes of R rows x 128 bytes
+// (64 bf16), 1024-byte aligned, the 16-byte piece p of row r stored at piece p ^ (r & 7); a second box follows at R * 128.
+//   K-major : rows are M/N indices, the 128 bytes run along K.  One instruction's 16 K elements are 32 bytes of a row.
+//   MN-major: rows are K indices, the 128 bytes run along M/N; 64-wide M/N blocks are R * 128 bytes apart (R = K rows).
+__device__ __forceinline__ uint64_t desc_sw128_kmajor(const unsigned char* tile, int R, int k0) {
+    return smem_desc(tile + (size_t)(k0 / 64) * R * 128 + (k0 % 64) * 2, 16, 1024) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_sw128_mnmajor(const unsigned char* tile, int R, int k0) {
+    return smem_desc(tile + (size_t)k0 * 128, (uint32_t)R * 128, 1024) | ((uint64_t)2 << 61);
+}
 // Instruction descriptor for kind::f16 with bf16 operands and an f32 accumulator.
 __device__ __forceinline__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major, int a_negate) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_negate << 13) | ((uint32_t)a_mn_major << 15) |

@@ -267,7 +267,7 @@ int glm53f_kda_core_prefill_varlen(int32_t heads, int32_t batch, const int32_t* 
  * one long sequence, or one GPU's shard of heads -- where one block per chain would leave most SMs idle: the part
  * of every chunk that does not depend on the recurrent state is computed for many chunks at once on all SMs, then
  * one block per chain runs the short state-dependent part chunk by chunk.  `workspace` (device memory, 16-byte
- * aligned) holds 108,544 bytes per (sequence, head, chunk of 64 rows) in flight plus 256 bytes of counters; its size
+ * aligned) holds 107,008 bytes per (sequence, head, chunk of 64 rows) in flight plus 256 bytes of counters; its size
  * sets how many chunks of every sequence one launch covers (at least one:
  * glm53f_kda_core_prefill_workspace_bytes(heads, batch, 1)); with room for two or more chunks per chain the state part
  * of one segment runs beside the state-independent part of the next.
@@ -305,7 +305,7 @@ int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const
 /* No counterpart in the reference.  glm53f_kda_core_prefill_varlen_ws for callers that cannot call cudaMalloc: an
  * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs
  * where an allocation would fail or disturb its host (inside a stream capture, under an allocator lock).  It takes no
- * workspace: the two passes run on a fixed array of 6,947,072 bytes (64 workspace slots and the item counters) that lives in the library's
+ * workspace: the two passes run on a fixed array of 6,848,768 bytes (64 workspace slots and the item counters) that lives in the library's
  * device image, so every GPU on which the library is loaded holds that much until the process exits.
  *   - Limit: heads * batch <= 64 (at least one chunk per pass must fit); more is rejected with status 1
  *     (cudaErrorInvalidValue) before anything is enqueued.  A pass covers 64 / (heads * batch) chunks of every

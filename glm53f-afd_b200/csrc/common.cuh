@@ -132,13 +132,6 @@ __device__ __forceinline__ void tensor_load_3d(void* smem_dst, const void* tmap,
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
-// The same for a rank-4 tensor map.
-__device__ __forceinline__ void tensor_load_4d(void* smem_dst, const void* tmap, int c0, int c1, int c2, int c3, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
-                     smem_u32(smem_dst)),
-                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-                 : "memory");
-}
 // Tiled tensor copy (rank 3) of one box from this block's shared memory to global memory (a bulk-group operation).
 __device__ __forceinline__ void tensor_store_3d(const void* tmap, int x, int y, int z, const void* smem_src) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(

@@ -91,11 +91,12 @@ static_assert(kSmemSp <= 232448, "shared memory budget");
 //
 // A block runs two items at a time: two groups of eight warps, each with its own staging, tensor-memory columns,
 // barriers and loader warp, so that one group's waits (tensor-core rounds, tensor-memory reads, its own barriers) are
-// filled by the other group's arithmetic.  To fit two items, a group keeps 96 KiB: q, k, v arrive as operand tiles
-// already (a tiled tensor copy whose box order is 8 channels, row, cell puts them in the cell layout) and are
-// turned into Qg and Kg in place; the log decays arrive in swizzled boxes and become E in place; the inverse's FP32
-// scratch goes over E and Kinv once they are dead; and everything the state role needs leaves for the workspace
-// straight from registers (Qg, Kdec hi/lo, E_last, M, W, U), so no result tile lives in shared memory.
+// filled by the other group's arithmetic.  To fit two items, a group keeps 96 KiB: q, k, v and the log decays arrive
+// by tiled tensor copies in the 128-byte swizzle, which is an operand layout of the tensor core (K-major for the
+// products over key channels, MN-major for the products over rows), so k and q are turned into Kg and Qg in place and
+// v is used as it lands; the log decays become E in place; the inverse's FP32 scratch goes over E and Kinv once they
+// are dead; and everything the state role needs leaves for the workspace straight from registers (Qg, Kdec hi/lo,
+// E_last, M, W, U), in the un-swizzled cell layout the state role reads, so no result tile lives in shared memory.
 // =====================================================================================================================
 constexpr int kGroupThreads = 256, kGroups = 2;
 constexpr int gQ = 0, gK = kTile, gV = 2 * kTile, gG = 3 * kTile, gKi = gG + 4 * kBox;  // Q/Qg | K/Kg | V | g/E | Kinv

@@ -1,0 +1,174 @@
+"""The benchmark configurations at their full sizes, through properties that need no CPU pass over the whole input.
+
+  configuration 2   8,192 rows of packed variable-length sequences, 64 heads: one call equals two calls that cut every
+                    sequence at a chunk boundary and carry the state (bit for bit); the workspace form equals itself
+                    for two workspace sizes (bit for bit) and the single-pass kernel to rounding; two heads of one
+                    sequence against the oracle's FP32 recurrence from the bytes the GPU consumed.
+  configuration 4   48 slots x 16 draft rows x 34 layers, bf16 states: verify + commit(k) equals k serial single-row
+                    decode steps for every slot and layer, bit for bit (k drawn from 0..16); verify leaves the states
+                    untouched; verify's first k outputs equal the serial steps' outputs.
+  configuration 1   16 slots x 34 layers: covered by bench.py's own run; here the in-place decode equals the
+                    out-of-place decode bit for bit at that size.
+Inputs are generated on the device with the configurations' distributions (seeded torch generators).
+"""
+import importlib
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+DK = DV = 128
+H = 64
+
+
+@pytest.fixture(scope="module")
+def env():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    pkg = importlib.import_module("glm53f-afd_b200")
+    pkg.ffi.load()
+    return pkg, importlib.import_module("glm53f-afd_b200.core")
+
+
+def tokens(rows, heads, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    n = rows * heads
+
+    def unit(scale):
+        x = torch.randn(n, DK, device="cuda", generator=g)
+        return (x * (scale / torch.sqrt((x * x).sum(1, keepdim=True) + 1e-6))).to(torch.bfloat16).reshape(-1)
+
+    q, k = unit(DK ** -0.5), unit(1.0)
+    v = torch.randn(n * DK, device="cuda", generator=g).to(torch.bfloat16)
+    lg = torch.nn.functional.logsigmoid(torch.randn(n * DK, device="cuda", generator=g) + 3.0)
+    beta = torch.sigmoid(torch.randn(n, device="cuda", generator=g))
+    return q, k, v, lg, beta
+
+
+def test_config2_packed_prefill_properties(env, oracle):
+    pkg, core = env
+    lens = pkg.synth.varlen_lengths(2, 8192)
+    rows, batch, per = sum(lens), len(lens), H * DV * DK
+    assert rows == 8192
+    q, k, v, g, beta = tokens(rows, H, 0x53454546)
+    gs = torch.Generator(device="cuda").manual_seed(7)
+    carried = [i % 2 == 1 for i in range(batch)]
+    s0 = torch.zeros(batch * per, device="cuda")
+    for i in range(batch):
+        if carried[i]:
+            s0[i * per:(i + 1) * per] = torch.randn(per, device="cuda", generator=gs) * 0.05
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    off = torch.arange(batch, dtype=torch.int64, device="cuda") * per
+
+    def run(workspace_chunks):
+        st, out = s0.clone(), torch.zeros(rows * H * DV, dtype=torch.bfloat16, device="cuda")
+        ws = None if workspace_chunks is None else torch.empty(core.prefill_workspace_bytes(H, batch, workspace_chunks), dtype=torch.uint8, device="cuda")
+        core.prefill_varlen(H, rows, cu, max(lens), q, k, v, g, beta, st, off, out=out, workspace=ws)
+        torch.cuda.synchronize()
+        assert core.device_status() == 0
+        return out, st
+
+    out_a, st_a = run(8)
+    out_b, st_b = run(3)
+    assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16)) and torch.equal(st_a, st_b)
+    out_1, st_1 = run(None)  # the single-pass kernel: one block per (sequence, head)
+    assert float((out_a.float() - out_1.float()).abs().max()) <= float(out_1.float().abs().max()) / 128.0
+    assert float((st_a - st_1).norm() / st_1.norm()) <= 1e-4
+
+    # every sequence cut at a chunk boundary: prefixes in one call, then suffixes from the carried states
+    cuts = [(n // 2) // 64 * 64 for n in lens]
+    st2, out2 = s0.clone(), torch.zeros_like(out_a)
+    ws = torch.empty(core.prefill_workspace_bytes(H, batch, 8), dtype=torch.uint8, device="cuda")
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    for part in (0, 1):
+        seg = [(int(starts[i]), cuts[i]) if part == 0 else (int(starts[i]) + cuts[i], lens[i] - cuts[i]) for i in range(batch)]
+        idx = torch.cat([torch.arange(a, a + n, device="cuda") for a, n in seg])
+        take = lambda t, w: t.view(rows, H * w)[idx].contiguous().view(-1)
+        n_rows = int(idx.numel())
+        cu_p = torch.tensor(np.concatenate([[0], np.cumsum([n for _, n in seg])]), dtype=torch.int32, device="cuda")
+        o_p = torch.zeros(n_rows * H * DV, dtype=torch.bfloat16, device="cuda")
+        core.prefill_varlen(H, n_rows, cu_p, max(n for _, n in seg), take(q, DK), take(k, DK), take(v, DV), take(g, DK), take(beta, 1), st2, off,
+                            out=o_p, workspace=ws)
+        out2.view(rows, H * DV)[idx] = o_p.view(n_rows, H * DV)
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    assert torch.equal(out2.view(torch.int16), out_a.view(torch.int16)) and torch.equal(st2, st_a)
+
+    # two heads of the longest sequence against the FP32 recurrence, from the GPU's bytes
+    i = int(np.argmax(lens))
+    r0, n = int(starts[i]), lens[i]
+    heads = torch.tensor([5, 40], device="cuda")
+    pick = lambda t, w: t.view(rows, H, w)[r0:r0 + n].index_select(1, heads).contiguous().cpu()
+    y, s_ref = oracle.core_forward(2, pick(q.view(torch.int16), DK).numpy().view(np.uint16).reshape(-1), pick(k.view(torch.int16), DK).numpy().view(np.uint16).reshape(-1),
+                                   pick(v.view(torch.int16), DV).numpy().view(np.uint16).reshape(-1), pick(g, DK).numpy().reshape(-1),
+                                   beta.view(rows, H)[r0:r0 + n].index_select(1, heads).contiguous().cpu().numpy().reshape(-1),
+                                   s0.view(batch, H, DV * DK)[i].index_select(0, heads).cpu().numpy().reshape(-1), form="recurrent", threads=2)
+    got = out_a.view(rows, H, DV)[r0:r0 + n].index_select(1, heads).float().cpu().numpy().reshape(-1)
+    s_got = st_a.view(batch, H, DV * DK)[i].index_select(0, heads).cpu().numpy().reshape(-1)
+    assert np.max(np.abs(got - y)) <= 2e-2 and np.linalg.norm(got - y) / np.linalg.norm(y) <= 5e-3
+    assert np.linalg.norm(s_got - s_ref) / np.linalg.norm(s_ref) <= 1e-3
+
+
+def test_config4_verify_and_rollback_at_full_size(env):
+    pkg, core = env
+    slots, window, layers = 48, 16, 34
+    per, rows = H * DV * DK, slots * window
+    rng = np.random.default_rng(0x53454548)
+    keeps = [int(x) for x in rng.integers(0, window + 1, slots)]
+    keeps[0], keeps[1] = 0, window
+    gs = torch.Generator(device="cuda").manual_seed(11)
+    arena = (torch.randn(layers * slots * per, device="cuda", generator=gs) * 0.05).to(torch.bfloat16)
+    serial = arena.clone()
+    before = arena.clone()
+    cu = torch.arange(slots + 1, dtype=torch.int32, device="cuda") * window
+    keep_d = torch.tensor(keeps, dtype=torch.int32, device="cuda")
+    off = torch.arange(slots, dtype=torch.int64, device="cuda") * per
+    nkv, nb = rows * H * DK, rows * H
+    ks = torch.zeros(layers * nkv, device="cuda")
+    gsv = torch.zeros(layers * nkv, device="cuda")
+    vs = torch.zeros(layers * nkv, dtype=torch.bfloat16, device="cuda")
+    bs = torch.zeros(layers * nb, device="cuda")
+    out = torch.zeros(rows * H * DV, dtype=torch.bfloat16, device="cuda")
+    step_out = torch.zeros(slots * H * DV, dtype=torch.bfloat16, device="cuda")
+    for l in range(layers):
+        q, k, v, g, beta = tokens(rows, H, 1000 + l)
+        layer_states = arena[l * slots * per:(l + 1) * slots * per]
+        core.decode_batch(H, rows, cu, q, k, v, g, beta, layer_states, off, state_out=None, out=out,
+                          saves=(ks[l * nkv:], vs[l * nkv:], gsv[l * nkv:], bs[l * nb:]))
+        # the serial run: step t decodes row t of every slot that keeps more than t rows
+        ser = serial[l * slots * per:(l + 1) * slots * per]
+        view = lambda t, w: t.view(slots, window, H * w)
+        for t in range(max(keeps)):
+            live = [s for s in range(slots) if keeps[s] > t]
+            idx = torch.tensor(live, device="cuda")
+            tk = lambda x, w: view(x, w)[idx, t].contiguous().view(-1)
+            cu_t = torch.arange(len(live) + 1, dtype=torch.int32, device="cuda")
+            core.decode_batch(H, len(live), cu_t, tk(q, DK), tk(k, DK), tk(v, DV), tk(g, DK), tk(beta, 1), ser, off[idx].contiguous(),
+                              out=step_out[:len(live) * H * DV])
+            assert torch.equal(step_out[:len(live) * H * DV].view(len(live), H * DV).view(torch.int16),
+                               view(out, DV)[idx, t].view(torch.int16)), (l, t)
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    assert torch.equal(arena.view(torch.int16), before.view(torch.int16)), "verify must not touch the states"
+    core.commit_batch(H, layers, cu, keep_d, arena, slots * per, off, (ks, vs, gsv, bs), nkv, nb)
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    assert torch.equal(arena.view(torch.int16), serial.view(torch.int16))
+
+
+def test_config1_decode_in_place_equals_out_of_place(env):
+    pkg, core = env
+    slots, layers, per = 16, 34, H * DV * DK
+    gs = torch.Generator(device="cuda").manual_seed(13)
+    cu = torch.arange(slots + 1, dtype=torch.int32, device="cuda")
+    off = torch.arange(slots, dtype=torch.int64, device="cuda") * per
+    for l in range(layers):
+        st = (torch.randn(slots * per, device="cuda", generator=gs) * 0.05).to(torch.bfloat16)
+        q, k, v, g, beta = tokens(slots, H, 2000 + l)
+        dst, o1, o2 = torch.zeros_like(st), torch.zeros(slots * H * DV, dtype=torch.bfloat16, device="cuda"), torch.zeros(slots * H * DV, dtype=torch.bfloat16, device="cuda")
+        core.decode_batch(H, slots, cu, q, k, v, g, beta, st, off, state_out=dst, out=o1)
+        core.decode_batch(H, slots, cu, q, k, v, g, beta, st, off, out=o2)
+        assert torch.equal(o1.view(torch.int16), o2.view(torch.int16)) and torch.equal(dst.view(torch.int16), st.view(torch.int16)), l
+    assert core.device_status() == 0

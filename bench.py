@@ -139,6 +139,84 @@ def cpu_decode_gbs(seconds: float, layers_sample: int = 2):
     return gbs, cores, f"{steps} steps x {layers_sample} of 34 layers x {SLOTS} slots x {HEADS} heads in {dt:.1f} s"
 
 
+VERIFY_SLOTS, VERIFY_WINDOW = 48, 16  # config 4: draft verification and rollback over all layers
+
+
+def run_verify(torch, lib, rank, layers, steps):
+    """Config 4: per step, every layer verifies 16 draft rows for each of 48 slots (states read, not written; replay
+    inputs saved), then one commit over all layers rolls every slot's state forward to its accepted prefix (drawn from
+    0..16).  Algorithmic bytes: verify reads each bf16 state once; the commit reads and writes it once."""
+    import ctypes as C
+
+    import numpy as np
+
+    slots, window = VERIFY_SLOTS, VERIFY_WINDOW
+    rows, per = slots * window, STATE_ELEMS
+    gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 4 + 97 * rank)
+    n = rows * HEADS
+
+    def unit(scale):
+        x = torch.randn(n, DK, device="cuda", generator=gen)
+        return (x * (scale / torch.sqrt((x * x).sum(1, keepdim=True) + 1e-6))).to(torch.bfloat16).reshape(-1)
+
+    # one set of draft inputs serves every layer (the timing does not depend on the values); states are per layer
+    q, k = unit(DK ** -0.5), unit(1.0)
+    v = torch.randn(n * DK, device="cuda", generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(n * DK, device="cuda", generator=gen) + 3.0)
+    beta = torch.sigmoid(torch.randn(n, device="cuda", generator=gen))
+    arena = (torch.randn(layers * slots * per, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    keeps = np.random.default_rng(0x53454548).integers(0, window + 1, slots)
+    cu = torch.arange(slots + 1, dtype=torch.int32, device="cuda") * window
+    keep = torch.tensor(keeps, dtype=torch.int32, device="cuda")
+    off = torch.arange(slots, dtype=torch.int64, device="cuda") * per
+    nkv, nb = rows * HEADS * DK, rows * HEADS
+    ks, gs_ = torch.empty(layers * nkv, device="cuda"), torch.empty(layers * nkv, device="cuda")
+    vs = torch.empty(layers * nkv, dtype=torch.bfloat16, device="cuda")
+    bs = torch.empty(layers * nb, device="cuda")
+    out = torch.empty(rows * HEADS * DK, dtype=torch.bfloat16, device="cuda")
+    P = lambda t, byte_off=0: C.c_void_p(t.data_ptr() + byte_off)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def verify():
+        for l in range(layers):
+            rc = lib.glm53f_kda_core_verify_batch(HEADS, slots, P(cu), P(q), P(k), P(v), P(g), P(beta), P(arena, 2 * l * slots * per), None, P(off),
+                                                  1, 0, None, None, 1e-5, P(out), P(ks, 4 * l * nkv), P(vs, 2 * l * nkv), P(gs_, 4 * l * nkv),
+                                                  P(bs, 4 * l * nb), stream)
+            if rc != 0:
+                raise RuntimeError(f"verify launch failed: {rc}")
+
+    def commit():
+        rc = lib.glm53f_kda_core_commit_batch(HEADS, layers, slots, P(cu), P(keep), P(arena), P(arena), slots * per, P(off), 1, P(ks), P(vs),
+                                              P(gs_), P(bs), nkv, nb, stream)
+        if rc != 0:
+            raise RuntimeError(f"commit launch failed: {rc}")
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    for _ in range(3):
+        verify()
+        commit()
+    ms_v, ms_c = timed(verify), timed(commit)
+    state_bytes = layers * slots * per * 2
+    hbm, kind = peaks()
+    res = {"workload": f"config 4: {slots} slots x {window} draft rows x {layers} layers, bf16 states, accepted prefixes drawn from 0..{window}",
+           "verify": {"ms_per_step": ms_v, "rows_per_s": rows * layers / (ms_v * 1e-3), "state_gbs": state_bytes / (ms_v * 1e-3) / 1e9,
+                      "algorithmic_bytes": state_bytes + layers * rows * (TOKEN_IN_BYTES + TOKEN_OUT_BYTES + HEADS * 1284), "gpu_launches": layers},
+           "commit": {"ms_per_step": ms_c, "state_gbs": 2 * state_bytes / (ms_c * 1e-3) / 1e9, "frac_of_hbm": 2 * state_bytes / (ms_c * 1e-3) / 1e9 / hbm,
+                      "peak_source": kind, "mean_kept_rows": float(keeps.mean()), "gpu_launches": 1}}
+    del arena, ks, gs_, vs, bs
+    torch.cuda.empty_cache()
+    return res
+
+
 PREFILL_T = 1_048_576           # config 3: one sequence, H = 64, d = 128, chunk 64
 PREFILL_BYTES_PER_TOKEN = 98_560  # q, k, v, out bf16 + g f32 + beta f32, all 64 heads
 PREFILL_FLOP_PER_TOKEN = 8.94e6   # causal-exact count of the chunk-64 form, all 64 heads
@@ -356,6 +434,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
+    ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4)")
     ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
     ap.add_argument("--prefill-ws-chunks", type=int, default=128, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
@@ -473,10 +552,12 @@ def main():
     e2e_value = world * per_rank_bytes / (e2e_ms * 1e-3) / 1e9
     assert core.device_status() == 0
 
+    del arena, dev, outs
+    torch.cuda.empty_cache()
+    verify = run_verify(torch, lib, rank, layers, max(3, args.steps // 4)) if not args.no_verify else None
+    assert core.device_status() == 0
     prefill = None
     if args.prefill_tokens > 0:
-        del arena, dev, outs
-        torch.cuda.empty_cache()
         prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
 
     if rank != 0:
@@ -498,6 +579,7 @@ def main():
                 "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES},
         "gpu_launches": timed_launches,
         "clocks": clocks,
+        "verify": verify,
         "prefill": prefill,
     }
     if not args.no_cpu:

@@ -70,6 +70,7 @@ struct SpParams {
     int state_chunk0, has_state;
     uint16_t* full[8];       // head-sharded launches: every rank's full [rows][heads_total][128] output buffer, or none
     int ranks, heads_total, head0;
+    int parts;               // state-role blocks per chain: 1, or 2 (each owns half of the value channels)
     unsigned int* counters;  // [2] item counters: this launch hands items out of counters[ctr], and zeroes the other
     int ctr;
     int* status;
@@ -469,7 +470,13 @@ constexpr int sOut = sRed + 4 * CH * 4, kOutTile = 2 * kBox;
 static_assert(sOut % 1024 == 0 && sOut + 2 * kOutTile <= oBars, "state role shared memory");
 constexpr uint32_t tS = 0, tQS = 128, tD = 256, tQS1 = 384;  // QS/O accumulators alternate between chunks
 
-__device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain) {
+// NV = the value channels this block owns (all 128, or 64: a chain's value columns never interact, so two blocks can
+// share a chain when chains are few and the serial walk over the chunks is what takes the time); value channels
+// [vpart * NV, vpart * NV + NV).  A warp then covers C = NV / 4 accumulator columns.
+template <int NV>
+__device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain, const int vpart) {
+    constexpr int C = NV / 4, CELLS = C / 8;
+    const int v0 = vpart * NV;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + oBarsState);  // [3]
     uint64_t* empty = full + 3;                                       // [3]
     uint64_t* bar_mma = full + 6;
@@ -501,19 +508,19 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
             const unsigned char* tile = smem + sOut + (c & 1) * kOutTile;
             if (n == CH) {
                 if (lane == 0) {
-                    for (int x = 0; x < 2; ++x) {
-                        if (p.out != nullptr) tensor_store_3d(&p.tm_out, x * 64, h, (int)gr0, tile + x * kBox);
-                        for (int pe = 0; pe < p.ranks; ++pe) tensor_store_3d(&p.tm_full[pe], x * 64, p.head0 + h, (int)gr0, tile + x * kBox);
+                    for (int x = 0; x < NV / 64; ++x) {
+                        if (p.out != nullptr) tensor_store_3d(&p.tm_out, v0 + x * 64, h, (int)gr0, tile + x * kBox);
+                        for (int pe = 0; pe < p.ranks; ++pe) tensor_store_3d(&p.tm_full[pe], v0 + x * 64, p.head0 + h, (int)gr0, tile + x * kBox);
                     }
                     bulk_commit();
                     bulk_wait_read<0>();  // the tile has been read: the compute warps may refill it
                 }
             } else {
-                for (int e = lane; e < n * 16; e += 32) {
-                    const int r = e >> 4, piece = e & 15;
+                for (int e = lane; e < n * (NV / 8); e += 32) {
+                    const int r = e / (NV / 8), piece = e % (NV / 8);
                     const uint4 v4 = *reinterpret_cast<const uint4*>(tile + box_piece(r, piece));
-                    if (p.out != nullptr) *reinterpret_cast<uint4*>(p.out + ((gr0 + r) * H + h) * DV + piece * 8) = v4;
-                    const long long at_full = ((gr0 + r) * p.heads_total + p.head0 + h) * DV + piece * 8;
+                    if (p.out != nullptr) *reinterpret_cast<uint4*>(p.out + ((gr0 + r) * H + h) * DV + v0 + piece * 8) = v4;
+                    const long long at_full = ((gr0 + r) * p.heads_total + p.head0 + h) * DV + v0 + piece * 8;
                     for (int pe = 0; pe < p.ranks; ++pe) *reinterpret_cast<uint4*>(p.full[pe] + at_full) = v4;
                 }
             }
@@ -535,8 +542,8 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
                 bulk_load(smem + sSlot + wQg, slot + wQg, 2 * kTile, &full[0]);
                 bulk_load(smem + sSlot + wEgl, slot + wEgl, 512, &full[0]);
                 if (!mbar_wait(&empty[1], ph, ctx, kStatusWaitPrefill)) break;
-                mbar_arrive_expect_tx(&full[1], kUBytes);
-                bulk_load(smem + sSlot + wU, slot + wU, kUBytes, &full[1]);
+                mbar_arrive_expect_tx(&full[1], NV * CH * 4);
+                bulk_load(smem + sSlot + wU, slot + wU + (size_t)(v0 / 4) * CH * 16, NV * CH * 4, &full[1]);
                 if (!mbar_wait(&empty[2], ph, ctx, kStatusWaitPrefill)) break;
                 mbar_arrive_expect_tx(&full[2], kTile / 2 + 2 * kTile);
                 bulk_load(smem + sSlot + wMm, slot + wMm, kTile / 2 + 2 * kTile, &full[2]);
@@ -575,25 +582,25 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         if (!mbar_wait(&full[0], (uint32_t)(c & 1), ctx, kStatusWaitPrefill)) return false;
         const float* egl = reinterpret_cast<const float*>(smem + sSlot + wEgl);
         {
-            uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+            uint32_t r[C];
+            tc::tmem_ld<C>(tc::tmem_addr(tm, quad, tS + cg * C), r);
             tc::tmem_ld_wait();
             if (p.state_bf16) {
 #pragma unroll
-                for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(bf16_round(__uint_as_float(r[jj])));
+                for (int jj = 0; jj < C; ++jj) r[jj] = __float_as_uint(bf16_round(__uint_as_float(r[jj])));
             }
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + sS16, 128, cg * 4 + cc, lane_row128)) = pack8(r + cc * 8);
+            for (int cc = 0; cc < CELLS; ++cc) *reinterpret_cast<uint4*>(cell(smem + sS16, 128, cg * CELLS + cc, lane_row128)) = pack8(r + cc * 8);
             const float el = egl[lane_row128];
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(__uint_as_float(r[jj]) * el);
-            tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+            for (int jj = 0; jj < C; ++jj) r[jj] = __float_as_uint(__uint_as_float(r[jj]) * el);
+            tc::tmem_st<C>(tc::tmem_addr(tm, quad, tS + cg * C), r);
             tc::tmem_st_wait();
         }
         publish_operands();
         const uint32_t tO = (c & 1) ? tQS1 : tQS;
         mma_issue([&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), idn = tc::idesc_bf16(64, 128, 0, 1, 1);
+            constexpr uint32_t id = tc::idesc_bf16(64, NV, 0, 1, 0), idn = tc::idesc_bf16(64, NV, 0, 1, 1);
             for (int k0 = 0; k0 < DK; k0 += 16)
                 tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
             for (int k0 = 0; k0 < DK; k0 += 16)
@@ -605,14 +612,14 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
     // ---- the incoming state into tensor memory: lane = key channel, columns = value channel -----------------------
     {
         const void* src = j0 == 0 ? p.state_in : p.state_out;
-        uint32_t r[32];
+        uint32_t r[C];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+        for (int j = 0; j < C; ++j) {
+            const long long at = s_elem + (long long)(v0 + cg * C + j) * DK + lane_row128;
             const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
             r[j] = __float_as_uint(x);
         }
-        tc::tmem_st32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+        tc::tmem_st<C>(tc::tmem_addr(tm, quad, tS + cg * C), r);
         tc::tmem_st_wait();
     }
     tc::fence_before_sync();
@@ -630,15 +637,15 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         // ---- D = U - W S as bf16 hi + lo cells ---------------------------------------------------------------------------
         if (!mbar_wait(&full[1], par, ctx, kStatusWaitPrefill)) { alive = false; break; }
         {
-            uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, tD + cg * 32), r);
+            uint32_t r[C];
+            tc::tmem_ld<C>(tc::tmem_addr(tm, quad, tD + cg * C), r);
             tc::tmem_ld_wait();
             if (lane < 16) {
-                unsigned char* Ut = smem + sSlot + wU;
+                unsigned char* Ut = smem + sSlot + wU;  // this block's slice of U: NV / 4 cells of four value channels
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const float4 u0 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * 8 + cc * 2, lane_row64));
-                    const float4 u1 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * 8 + cc * 2 + 1, lane_row64));
+                for (int cc = 0; cc < CELLS; ++cc) {
+                    const float4 u0 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * (C / 4) + cc * 2, lane_row64));
+                    const float4 u1 = *reinterpret_cast<const float4*>(cell(Ut, CH, cg * (C / 4) + cc * 2 + 1, lane_row64));
                     const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
                     uint32_t wh[4], wl[4];
 #pragma unroll
@@ -649,8 +656,8 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
                         wh[jj] = tc::bf16x2(h0, h1);
                         wl[jj] = tc::bf16x2(l0, l1);
                     }
-                    *reinterpret_cast<uint4*>(cell(smem + sDhi, CH, cg * 4 + cc, lane_row64)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                    *reinterpret_cast<uint4*>(cell(smem + sDlo, CH, cg * 4 + cc, lane_row64)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                    *reinterpret_cast<uint4*>(cell(smem + sDhi, CH, cg * CELLS + cc, lane_row64)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4*>(cell(smem + sDlo, CH, cg * CELLS + cc, lane_row64)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
             }
         }
@@ -660,7 +667,7 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         // ---- O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------
         if (!mbar_wait(&full[2], par, ctx, kStatusWaitPrefill)) { alive = false; break; }
         mma_issue([&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
+            constexpr uint32_t id = tc::idesc_bf16(64, NV, 0, 1, 0), ids = tc::idesc_bf16(128, NV, 1, 1, 0);
             const unsigned char* kdhi = smem + sSlot + wKdHi;
             const unsigned char* kdlo = smem + sSlot + wKdLo;
             for (int k0 = 0; k0 < CH; k0 += 16)
@@ -680,28 +687,28 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
 
         // ---- outputs: bf16(y), or the gated RMSNorm of bf16(y) ------------------------------------------------------------------
         {
-            uint32_t r[32];
-            tc::tmem_ld32(tc::tmem_addr(tm, quad, tO + cg * 32), r);
+            uint32_t r[C];
+            tc::tmem_ld<C>(tc::tmem_addr(tm, quad, tO + cg * C), r);
             tc::tmem_ld_wait();
             const int i = lane_row64;
             const bool live = lane < 16 && i < n;
-            const long long at = ((gr0 + i) * H + h) * DV + cg * 32;
-            float y[32];
+            const long long at = ((gr0 + i) * H + h) * DV + v0 + cg * C;
+            float y[C];
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj) y[jj] = bf16_round(__uint_as_float(r[jj]));
-            if (p.gate != nullptr) {
+            for (int jj = 0; jj < C; ++jj) y[jj] = bf16_round(__uint_as_float(r[jj]));
+            if (NV == DV && p.gate != nullptr) {  // the norm needs a row's every value channel: whole-head blocks only
                 float* red = reinterpret_cast<float*>(smem + sRed);
                 float ss = 0.0f;
 #pragma unroll
-                for (int jj = 0; jj < 32; ++jj) ss = fmaf(y[jj], y[jj], ss);
+                for (int jj = 0; jj < C; ++jj) ss = fmaf(y[jj], y[jj], ss);
                 if (lane < 16) red[cg * CH + i] = ss;
                 compute_sync();
                 if (live) {
                     const float tot = (red[i] + red[CH + i]) + (red[2 * CH + i] + red[3 * CH + i]);
                     const float rinv = 1.0f / sqrtf(tot / (float)DV + p.eps);
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const float gt = bf16_bits_to_f32(p.gate[at + jj]), w = bf16_bits_to_f32(p.norm_w[cg * 32 + jj]);
+                    for (int jj = 0; jj < C; ++jj) {
+                        const float gt = bf16_bits_to_f32(p.gate[at + jj]), w = bf16_bits_to_f32(p.norm_w[cg * C + jj]);
                         y[jj] = w * (y[jj] * rinv) * (1.0f / (1.0f + __expf(-gt)));
                     }
                 }
@@ -712,8 +719,8 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
             if (lane < 16) {
                 unsigned char* dst = smem + sOut + (c & 1) * kOutTile;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4)
-                    *reinterpret_cast<uint4*>(dst + box_piece(i, cg * 4 + c4)) = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
+                for (int c4 = 0; c4 < CELLS; ++c4)
+                    *reinterpret_cast<uint4*>(dst + box_piece(i, cg * CELLS + c4)) = make_uint4(tc::bf16x2(y[c4 * 8], y[c4 * 8 + 1]), tc::bf16x2(y[c4 * 8 + 2], y[c4 * 8 + 3]),
                                                                           tc::bf16x2(y[c4 * 8 + 4], y[c4 * 8 + 5]), tc::bf16x2(y[c4 * 8 + 6], y[c4 * 8 + 7]));
             }
             fence_proxy_async_smem();  // the tensor stores read the tile through the async proxy
@@ -724,12 +731,12 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
 
     // ---- the outgoing state ---------------------------------------------------------------------------------------------
     if (alive) {
-        uint32_t r[32];
-        tc::tmem_ld32(tc::tmem_addr(tm, quad, tS + cg * 32), r);
+        uint32_t r[C];
+        tc::tmem_ld<C>(tc::tmem_addr(tm, quad, tS + cg * C), r);
         tc::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const long long at = s_elem + (long long)(cg * 32 + j) * DK + lane_row128;
+        for (int j = 0; j < C; ++j) {
+            const long long at = s_elem + (long long)(v0 + cg * C + j) * DK + lane_row128;
             if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
             else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
         }
@@ -759,8 +766,9 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tm = *tmem_slot;
-    if (p.has_state && blockIdx.x < (unsigned)(p.batch * p.H)) {
-        state_role(p, smem, tm, (int)blockIdx.x);
+    if (p.has_state && blockIdx.x < (unsigned)(p.batch * p.H * p.parts)) {
+        if (p.parts == 2) state_role<64>(p, smem, tm, (int)(blockIdx.x >> 1), (int)(blockIdx.x & 1));
+        else state_role<DV>(p, smem, tm, (int)blockIdx.x, 0);
         tc::fence_after_sync();
     }
     if (p.has_intra && ctl[1] == 0u) intra_role(p, smem, tm);
@@ -846,6 +854,9 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     } else if (out == nullptr) {
         return kInvalid;
     }
+    // Few chains: the serial walk over a chain's chunks is the critical path, so two blocks share each chain.  (Not with
+    // the fused output norm, which needs a row's every value channel in one block.)
+    p.parts = (gate == nullptr && chains * 2 <= 64) ? 2 : 1;
     p.seg_chunks = (int)seg;
     unsigned char* base = reinterpret_cast<unsigned char*>(workspace);
     unsigned char* half[2] = {base, overlap ? base + chains * seg * kSlotBytes : base};
@@ -875,7 +886,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
         p.ws_intra = half[intra_seg & 1];
         p.ws_state = half[state_seg & 1];
         p.ctr = launch_no++ & 1;
-        long long grid = p.has_state ? chains : 0;
+        long long grid = p.has_state ? chains * p.parts : 0;
         if (p.has_intra) {
             const long long items = chains * seg, want = items < sms ? items : sms;
             if (grid < want) grid = want;

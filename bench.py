@@ -415,7 +415,8 @@ def run_reference(args):
         "impl": "reference", "metric": "KDA decode state GB/s (16 slots x 34 layers, bf16 states)", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 1: batched single-token decode, 16 slots, H=64, d=128, 34 layers, bf16-stored states"},
+        "config": {"workload": "config 1: batched single-token decode, 16 slots per GPU, H=64, d=128, 34 layers, bf16-stored states",
+                   "layers": LAYERS, "sample": "the same step on the host cores, a bounded number of repetitions of 2 of the 34 layers"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's CPU path is Rust (no toolchain here): this is the C++ port in oracle/, all host threads",

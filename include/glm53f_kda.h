@@ -287,8 +287,8 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
 /* glm53f_kda_core_prefill_varlen_ws for a head-sharded launch (heads = this GPU's shard of heads_total heads, starting
  * at head0) with the all-gather of the outputs done by the kernel itself: every output row is stored straight into
  * each of the `ranks` (1..8) full buffers full[r], laid out [rows][heads_total][128] bf16 -- this GPU's own and its
- * peers' (device addresses valid in this process: peer-mapped, IPC-opened or symmetric memory; plain stores over
- * NVLink, no collective follows the launch).  `full` is a host array, read during the call.  `out` (the shard-local
+ * peers' (device addresses valid in this process: peer-mapped, IPC-opened or symmetric memory; tiled tensor stores,
+ * over NVLink for a peer's buffer; no collective follows the launch).  `full` is a host array, read during the call.  `out` (the shard-local
  * [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may still read a full
  * buffer when another rank's launch starts writing it, and a rank may read its buffer only after every rank's launch
  * has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
@@ -304,12 +304,12 @@ int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const
 
 /* No counterpart in the reference.  glm53f_kda_core_prefill_varlen_ws for callers that cannot call cudaMalloc: an
  * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs
- * where an allocation would fail or disturb its host (inside a stream capture, under an allocator lock).  It takes no
- * workspace: the two passes run on a fixed array of 6,848,768 bytes (64 workspace slots and the item counters) that lives in the library's
- * device image, so every GPU on which the library is loaded holds that much until the process exits.
- *   - Limit: heads * batch <= 64 (at least one chunk per pass must fit); more is rejected with status 1
- *     (cudaErrorInvalidValue) before anything is enqueued.  A pass covers 64 / (heads * batch) chunks of every
- *     sequence, so the entry point suits few chains: one sequence on one GPU's shard of heads.
+ * where an allocation would fail or stall its host (under an allocator lock, in a latency-critical loop).  It takes
+ * no workspace: it runs on a fixed array of 6,848,768 bytes (64 workspace slots and the item counters) that lives in
+ * the library's device image, so every GPU on which the library is loaded holds that much until the process exits.
+ *   - Limit: heads * batch <= 64 (at least one chunk per chain must fit); more is rejected with status 1
+ *     (cudaErrorInvalidValue) before anything is enqueued.  A launch covers at most 64 / (heads * batch) chunks of
+ *     every sequence, so the entry point suits few chains: one sequence on one GPU's shard of heads.
  *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
  *     current) and remembers it; make that first call outside any stream capture.
  *   - The call allocates and frees nothing.

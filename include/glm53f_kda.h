@@ -288,8 +288,8 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
  * at head0) with the all-gather of the outputs done by the kernel itself: every output row is stored straight into
  * each of the `ranks` (1..8) full buffers full[r], laid out [rows][heads_total][128] bf16 -- this GPU's own and its
  * peers' (device addresses valid in this process: peer-mapped, IPC-opened or symmetric memory; tiled tensor stores,
- * over NVLink for a peer's buffer; no collective follows the launch).  `full` is a host array, read during the call.  `out` (the shard-local
- * [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may still read a full
+ * over NVLink for a peer's buffer; no collective follows the launch).  `full` is a host array, read during the call.
+ * `out` (the shard-local [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may still read a full
  * buffer when another rank's launch starts writing it, and a rank may read its buffer only after every rank's launch
  * has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
 int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,

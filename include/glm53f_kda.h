@@ -289,9 +289,9 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
  * each of the `ranks` (1..8) full buffers full[r], laid out [rows][heads_total][128] bf16 -- this GPU's own and its
  * peers' (device addresses valid in this process: peer-mapped, IPC-opened or symmetric memory; tiled tensor stores,
  * over NVLink for a peer's buffer; no collective follows the launch).  `full` is a host array, read during the call.
- * `out` (the shard-local [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may still read a full
- * buffer when another rank's launch starts writing it, and a rank may read its buffer only after every rank's launch
- * has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
+ * `out` (the shard-local [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may
+ * still read a full buffer when another rank's launch starts writing it, and a rank may read its buffer only after
+ * every rank's launch has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
 int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
                                              const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
                                              const float* g, const float* beta,

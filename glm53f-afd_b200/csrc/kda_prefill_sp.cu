@@ -80,8 +80,9 @@ __device__ __forceinline__ unsigned char* slot_of(unsigned char* ws, int seg_chu
     return ws + ((size_t)chain * seg_chunks + jj) * kSlotBytes;
 }
 
-// Barriers of the two roles live apart (the state role's behind the intra role's shared-memory map), are set up once
-// per block and are never repurposed.
+// The state role's barriers sit behind every tile (set up once at kernel entry, never repurposed).  The intra role's
+// live inside its two groups' areas, which the state role -- it runs first in a block -- uses as tile space, so they are
+// set up when the intra role starts.
 constexpr int oBarsState = kSmemTc, kSmemSp = kSmemTc + 128;
 // 16 compute warps, the loader warp, and (state role only) a warp that moves finished output rows to global memory.
 constexpr int kThreadsSp = kCompute + 64, kLoaderWarp = kCompute / 32, kOutWarp = kCompute / 32 + 1;

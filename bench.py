@@ -437,7 +437,7 @@ def main():
     ap.add_argument("--prefill-passes", type=int, default=3)
     ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4)")
     ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
-    ap.add_argument("--prefill-ws-chunks", type=int, default=128, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
+    ap.add_argument("--prefill-ws-chunks", type=int, default=256, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -286,6 +286,49 @@ def test_prefill_gathering_store_into_full_buffers(G, core, pkg):
                             gather=([fulls[0].data_ptr()], heads, 0))
 
 
+# Stronger gates than the benchmark's (mean log decay -0.45 per row, -29 per chunk, single channels far below) and beta
+# pushed towards 1: still inside the tensor-core kernels' range, still within the task's tolerances; both kernels.
+@pytest.mark.parametrize("ws_chunks", [None, 5])
+def test_prefill_strong_gates_and_large_beta(G, core, oracle, pkg, ws_chunks):
+    o = oracle
+    heads, t = 3, 400
+    q, k, v, g, beta = pkg.synth.tokens(0, 7, t, heads)
+    rng = np.random.default_rng(99)
+    g = np.log(1.0 / (1.0 + np.exp(-rng.normal(1.0, 1.0, g.size)))).astype(np.float32)
+    beta = (1.0 / (1.0 + np.exp(-rng.normal(2.0, 1.0, beta.size)))).astype(np.float32)
+    s0 = pkg.synth.state(0, 7, 0, heads)
+    dq, dk, dv, dg, db = upload_tokens(G, (q, k, v, g, beta))
+    d_state, d_out = G.dev_f32(s0), torch.zeros(t * heads * DV, dtype=torch.int16, device="cuda")
+    ws = None if ws_chunks is None else torch.empty(core.prefill_workspace_bytes(heads, 1, ws_chunks), dtype=torch.uint8, device="cuda")
+    core.prefill_varlen(heads, t, G.dev_i32([0, t]), t, dq, dk, dv, dg, db, d_state, G.dev_i64([0]), out=d_out, workspace=ws)
+    G.check_status()
+    y, s_ref = o.core_forward(heads, q, k, v, g, beta, s0, form="recurrent", threads=4)
+    got = G.host_bf16(d_out)
+    assert G.max_abs(got, y) <= OUT_MAX_ABS and G.rel_l2(got, y) <= OUT_REL_L2
+    assert G.rel_l2(G.host_f32(d_state), s_ref) <= STATE_REL_L2
+
+
+# Gates beyond the range the chunk-64 kernels cover (a chunk's cumulative decay below ~e^-78) are not computed wrongly
+# in silence: every form records status 121, which the status call returns once and clears.  Nothing faults: the
+# arithmetic merely overflows.
+def test_prefill_reports_gates_outside_its_range(G, core, pkg):
+    heads, t = 2, 130
+    q, k, v, g, beta = pkg.synth.tokens(0, 8, t, heads)
+    g = np.full_like(g, -2.0)   # -128 per chunk
+    dq, dk, dv, dg, db = upload_tokens(G, (q, k, v, g, beta))
+    for workspace in (None, torch.empty(core.prefill_workspace_bytes(heads, 1, 2), dtype=torch.uint8, device="cuda"), "static"):
+        d_state, d_out = torch.zeros(heads * DV * DK, device="cuda"), torch.zeros(t * heads * DV, dtype=torch.int16, device="cuda")
+        core.prefill_varlen(heads, t, G.dev_i32([0, t]), t, dq, dk, dv, dg, db, d_state, G.dev_i64([0]), out=d_out, workspace=workspace)
+        torch.cuda.synchronize()
+        assert core.device_status() == 121
+        assert core.device_status() == 0
+    # and the same call with gates inside the range is clean afterwards
+    dg = G.dev_f32(np.full_like(g, -0.5))
+    d_state, d_out = torch.zeros(heads * DV * DK, device="cuda"), torch.zeros(t * heads * DV, dtype=torch.int16, device="cuda")
+    core.prefill_varlen(heads, t, G.dev_i32([0, t]), t, dq, dk, dv, dg, db, d_state, G.dev_i64([0]), out=d_out)
+    G.check_status()
+
+
 def test_prefill_two_pass_bf16_state_and_long_sequence(G, core, oracle, pkg):
     prefill_case(G, core, oracle, pkg.synth, 0, 2, [1100], [True], bf16=True, ws_chunks=4)
 

@@ -175,6 +175,7 @@ template <int MODE>
 struct UnitIter {
     unsigned long long u;
     unsigned b, h, layer;
+    unsigned step_b, step_h;  // gridDim.x = step_b * H + step_h
     bool ok;
     Unit nxt;
 
@@ -183,6 +184,8 @@ struct UnitIter {
         ok = u < (unsigned long long)p.units;
         const unsigned H = (unsigned)p.H, L = (unsigned)p.layers;
         h = blockIdx.x % H;
+        step_b = gridDim.x / H;
+        step_h = gridDim.x - step_b * H;
         const unsigned q = blockIdx.x / H;
         layer = MODE == kReplay ? q % L : 0u;
         b = MODE == kReplay ? q / L : q;
@@ -221,14 +224,19 @@ struct UnitIter {
         u += gridDim.x;
         ok = u < (unsigned long long)p.units;
         const unsigned H = (unsigned)p.H;
-        const unsigned nh = h + gridDim.x, dq = nh / H;
-        h = nh - dq * H;
         if (MODE == kReplay) {
+            const unsigned nh = h + gridDim.x, dq = nh / H;
+            h = nh - dq * H;
             const unsigned L = (unsigned)p.layers, nl = layer + dq, lq = nl / L;
             layer = nl - lq * L;
             b += lq;
-        } else {
-            b += dq;
+        } else {  // the stride in (request, head) is fixed for the launch: no division per unit
+            h += step_h;
+            b += step_b;
+            if (h >= H) {
+                h -= H;
+                ++b;
+            }
         }
         if (ok) nxt = fetch(p);
         return cur;

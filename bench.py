@@ -217,6 +217,52 @@ def run_verify(torch, lib, rank, layers, steps):
     return res
 
 
+def run_packed_prefill(torch, pkg, core, rank, passes=10):
+    """Config 2: 8,192 rows of packed variable-length sequences (lengths 256..2,048), 64 heads, half of the sequences
+    from a carried state: tokens/s per layer through the single-pass kernel (one block per (sequence, head)) and
+    through the workspace form."""
+    import numpy as np
+
+    lens = pkg.synth.varlen_lengths(2, 8192)
+    rows, batch, per = sum(lens), len(lens), STATE_ELEMS
+    gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 2 + 97 * rank)
+    n = rows * HEADS
+
+    def unit(scale):
+        x = torch.randn(n, DK, device="cuda", generator=gen)
+        return (x * (scale / torch.sqrt((x * x).sum(1, keepdim=True) + 1e-6))).to(torch.bfloat16).reshape(-1)
+
+    q, k = unit(DK ** -0.5), unit(1.0)
+    v = torch.randn(n * DK, device="cuda", generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(n * DK, device="cuda", generator=gen) + 3.0)
+    beta = torch.sigmoid(torch.randn(n, device="cuda", generator=gen))
+    s0 = torch.zeros(batch * per, device="cuda")
+    for i in range(1, batch, 2):
+        s0[i * per:(i + 1) * per] = torch.randn(per, device="cuda", generator=gen) * 0.05
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    off = torch.arange(batch, dtype=torch.int64, device="cuda") * per
+    out = torch.empty(n * DK, dtype=torch.bfloat16, device="cuda")
+    state = s0.clone()
+    res = {"workload": f"config 2: {rows} rows in {batch} packed sequences of {min(lens)}..{max(lens)} rows, H=64, d=128, chunk 64, FP32 states"}
+    for name, ws in (("single_pass", None), ("workspace", torch.empty(core.prefill_workspace_bytes(HEADS, batch, 32), dtype=torch.uint8, device="cuda"))):
+        def once():
+            state.copy_(s0)
+            core.prefill_varlen(HEADS, rows, cu, max(lens), q, k, v, g, beta, state, off, out=out, workspace=ws)
+        for _ in range(3):
+            once()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(passes):
+            once()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / passes
+        res[name] = {"ms_per_layer": ms, "tokens_per_s": rows / (ms * 1e-3), "gbs": rows * PREFILL_BYTES_PER_TOKEN / (ms * 1e-3) / 1e9}
+    assert core.device_status() == 0
+    return res
+
+
 PREFILL_T = 1_048_576           # config 3: one sequence, H = 64, d = 128, chunk 64
 PREFILL_BYTES_PER_TOKEN = 98_560  # q, k, v, out bf16 + g f32 + beta f32, all 64 heads
 PREFILL_FLOP_PER_TOKEN = 8.94e6   # causal-exact count of the chunk-64 form, all 64 heads
@@ -435,7 +481,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
-    ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4)")
+    ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4) and the packed-prefill leg (config 2)")
     ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
     ap.add_argument("--prefill-ws-chunks", type=int, default=256, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
@@ -594,6 +640,7 @@ def main():
     torch.cuda.empty_cache()
     verify = run_verify(torch, lib, rank, layers, max(3, args.steps // 4)) if not args.no_verify else None
     assert core.device_status() == 0
+    packed = run_packed_prefill(torch, pkg, core, rank) if not args.no_verify else None
     prefill = None
     if args.prefill_tokens > 0:
         prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
@@ -618,6 +665,7 @@ def main():
         "gpu_launches": timed_launches,
         "clocks": clocks,
         "verify": verify,
+        "prefill_packed": packed,
         "prefill": prefill,
     }
     if not args.no_cpu:

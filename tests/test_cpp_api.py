@@ -23,3 +23,14 @@ def test_host_checks_without_a_gpu(tmp_path):
     exe = build(tmp_path, "host_checks.cpp")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "all host checks passed" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_flows_on_the_gpu(tmp_path):
+    torch = pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = build(tmp_path, "gpu_flows.cpp", ["-I", os.path.join(cuda, "include"), "-L", os.path.join(cuda, "lib64"), "-lcudart", f"-Wl,-rpath,{os.path.join(cuda, 'lib64')}"])
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "all GPU flows passed" in r.stdout, r.stdout + r.stderr

@@ -217,6 +217,102 @@ def run_verify(torch, lib, rank, layers, steps):
     return res
 
 
+def cpu_marks_gbs(pkg, reps=5):
+    """The oracle's copy_mark (numpy row copies through the page list, one host thread) on one whole-model mark."""
+    import importlib
+
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import rows_oracle as ro
+
+    marks = importlib.import_module(pkg.__name__ + ".marks")
+    l = marks.KvLayout.glm53_flash().with_kda_state_bf16(True)
+    rng = np.random.default_rng(7)
+    parts = [rng.integers(0, 256, r[1], dtype=np.uint8) for r in l.mark_regions()]
+    need = l.mark_pages()
+    page_list = np.sort(rng.permutation(2 * need)[:need])
+    pool = np.zeros(2 * need * l.page_bytes, np.uint8)
+    ro.copy_mark(pool, l.page_bytes, page_list, parts, True)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        ro.copy_mark(pool, l.page_bytes, page_list, parts, True)
+        ro.copy_mark(pool, l.page_bytes, page_list, parts, False)
+    dt = (time.perf_counter() - t0) / (2 * reps)
+    return 2 * l.mark_bytes() / dt / 1e9, 1, f"{2 * reps} copies of one whole-model mark ({l.mark_bytes()} B, {need} pages) by the numpy oracle"
+
+
+def run_marks(torch, pkg, rank, slots=16, reps=5):
+    """The state snapshot of config 1's slots: every slot's positional state of the whole model (34 layers of bf16
+    KDA states, the conv windows, the DSA tails: 73.4 MiB) saved into pool pages and restored, one launch per slot
+    and direction.  Algorithmic bytes per copy: the mark read once and written once.  `host_api` times GlmKv.mark() +
+    rewind() (page allocation and the index upload included); `reference_sequence` the reference's three launches and
+    three copies per mark through the same row kernels."""
+    import ctypes as C
+    import importlib
+
+    import numpy as np
+
+    marks = importlib.import_module(pkg.__name__ + ".marks")
+    lib = pkg.ffi.load()
+    l = marks.KvLayout.glm53_flash().with_kda_state_bf16(True)
+    need = l.mark_pages()
+    hbm, kind = peaks()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    res = {"workload": f"{slots} slots x whole-model positional state ({l.mark_bytes()} B = {need} pool pages of {l.page_bytes} B each), "
+                       "save into scattered pool pages and restore; 2.3 GiB touched per pass, larger than L2",
+           "algorithmic_bytes_per_copy": 2 * l.mark_bytes(), "peak_source": kind}
+    for fused in (True, False):
+        pool = marks.KvPool(marks.KvConfig(l, slots, slots * need + 64), fused=fused)
+        kvs = [pool.slot() for _ in range(slots)]
+        pool.state.t.random_(0, 256)
+        pool.conv.t.random_(0, 256)
+        rng = np.random.default_rng(0x53454544 + rank)
+        # scattered pages, as a pool in use hands them out: every mark draws its pages from a shuffle of the pool
+        order = rng.permutation(slots * need + 64)
+        lists = [torch.tensor(np.sort(order[i * need:(i + 1) * need]).astype(np.int32), device="cuda") for i in range(slots)]
+        sizes = (C.c_int64 * 3)(*[n for _, n, _ in l.mark_regions()])
+
+        def device_pass(save):
+            for kv, idx in zip(kvs, lists):
+                parts = (C.c_void_p * 3)(*[a.as_ptr() + at for a, at in kv._arenas()])
+                rc = lib.glm53f_kda_mark_copy(pool.pages.as_ptr(), l.page_bytes, idx.data_ptr(), parts, sizes, save, st)
+                if rc != 0:
+                    raise RuntimeError(f"mark copy failed: {rc}")
+
+        def api_pass():
+            ms = [kv.mark() for kv in kvs]
+            for kv, m in zip(kvs, ms):
+                kv.rewind(kv.tokens(), m)
+            for m in ms:
+                m.drop()
+
+        def timed(fn, n):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        if fused:
+            for name, save in (("save", 1), ("restore", 0)):
+                for _ in range(3):
+                    device_pass(save)
+                ms = timed(lambda: device_pass(save), reps) / slots
+                gbs = 2 * l.mark_bytes() / (ms * 1e-3) / 1e9
+                res[name] = {"us_per_mark": ms * 1e3, "gbs": gbs, "frac_of_hbm": gbs / hbm, "gpu_launches_per_mark": 1}
+        for _ in range(2):
+            api_pass()
+        ms = timed(api_pass, 3) / slots
+        res["host_api" if fused else "reference_sequence"] = {"us_per_mark_and_rewind": ms * 1e3, "gbs": 4 * l.mark_bytes() / (ms * 1e-3) / 1e9}
+        del pool, kvs, lists
+        torch.cuda.empty_cache()
+    return res
+
+
 def run_packed_prefill(torch, pkg, core, rank, passes=10):
     """Config 2: 8,192 rows of packed variable-length sequences (lengths 256..2,048), 64 heads, half of the sequences
     from a carried state: tokens/s per layer through the single-pass kernel (one block per (sequence, head)) and
@@ -481,6 +577,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
+    ap.add_argument("--no-marks", action="store_true", help="skip the state snapshot / restore leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4) and the packed-prefill leg (config 2)")
     ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
     ap.add_argument("--prefill-ws-chunks", type=int, default=256, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
@@ -641,6 +738,7 @@ def main():
     verify = run_verify(torch, lib, rank, layers, max(3, args.steps // 4)) if not args.no_verify else None
     assert core.device_status() == 0
     packed = run_packed_prefill(torch, pkg, core, rank) if not args.no_verify else None
+    marks = run_marks(torch, pkg, rank) if not args.no_marks else None
     prefill = None
     if args.prefill_tokens > 0:
         prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
@@ -666,11 +764,15 @@ def main():
         "clocks": clocks,
         "verify": verify,
         "prefill_packed": packed,
+        "marks": marks,
         "prefill": prefill,
     }
     if not args.no_cpu:
         v, cores, sample = cpu_decode_gbs(args.cpu_seconds)
         line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        if marks is not None:
+            v, cores, sample = cpu_marks_gbs(pkg)
+            marks["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
         if prefill is not None:
             v, cores, sample = cpu_prefill_toks(args.cpu_seconds)
             prefill["cpu_baseline"] = {"value": v, "unit": "tokens/s per layer", "cores": cores, "kind": "port", "sample": sample}

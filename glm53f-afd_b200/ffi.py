@@ -1,4 +1,4 @@
-"""Raw bindings of the C ABI (include/glm53f_kda.h), one Python callable per `extern "C"` symbol.
+"""Raw bindings of the C ABI (include/glm53f_kda.h, include/glm53f_fwd_rows.h), one Python callable per `extern "C"` symbol.
 
 The counterpart of the reference crate's `ffi` module (crates/glm53f-kda/src/ffi.rs:16-287): no checks, raw device
 addresses as integers, the launcher's int status returned as is.  The library must exist: there is no CPU path.
@@ -40,10 +40,14 @@ SIGNATURES = {
     "glm53f_kda_core_prefill_varlen_ws_gather": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P, I64, P, I32, I32, I32, P]),
     "glm53f_kda_core_prefill_varlen_static": (C.c_int, [I32, I32, P, I32, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P]),
     "glm53f_kda_device_status": (C.c_int, []),
+    # include/glm53f_fwd_rows.h: the forward crate's row movers (crates/glm53f-forward/src/ffi.rs:75-95) and the mark copy
+    "glm53f_fwd_gather_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
+    "glm53f_fwd_scatter_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
+    "glm53f_kda_mark_copy": (I32, [P, I64, P, P, P, I32, P]),
 }
 
 # The reference's thirteen (crates/glm53f-kda/tests/provenance.rs:41-69 asserts exactly these).
-REFERENCE_SYMBOLS = [n for n in SIGNATURES if "_core_" not in n and n != "glm53f_kda_device_status"]
+REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy")]
 
 
 def library_path() -> str:

@@ -37,7 +37,10 @@ extern "C" {
 #endif
 
 struct CUstream_st;
+#ifndef GLM53F_STREAM_T_DEFINED
+#define GLM53F_STREAM_T_DEFINED
 typedef struct CUstream_st* glm53f_stream_t; /* cudaStream_t; NULL = the legacy default stream */
+#endif
 typedef uint16_t glm53f_bf16;                /* raw bfloat16 bits */
 
 #define GLM53F_KDA_DK 128

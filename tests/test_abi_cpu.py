@@ -1,4 +1,4 @@
-"""The C-ABI library loads without a GPU and exports exactly what include/glm53f_kda.h declares (no compute calls).
+"""The C-ABI library loads without a GPU and exports exactly what include/*.h declare (no compute calls).
 
 Mirrors the reference crate's provenance test (crates/glm53f-kda/tests/provenance.rs:41-69): the header and the
 bindings must list the same functions, thirteen of them the reference's."""
@@ -9,9 +9,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared():
-    text = open(os.path.join(ROOT, "include", "glm53f_kda.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(glm53f_kda_\w+)\s*\(", text)))
+    names = set()
+    for header in ("glm53f_kda.h", "glm53f_fwd_rows.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(glm53f_(?:kda|fwd)_\w+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_bindings_and_library_agree(pkg):
@@ -31,6 +34,33 @@ def test_host_side_rejections_need_no_gpu(pkg):
     assert lib.glm53f_kda_prefill_workspace_bytes(0, 1, 16) == 0
     assert lib.glm53f_kda_conv_shift(0, 0, None, None, 0, None) == 1
     assert lib.glm53f_kda_replay(0, 0, None, None, None, None, None, None, None) == 1
+
+
+def test_row_movers_reject_on_the_host_like_the_reference(pkg):
+    """kernels/glue.cu:222-233: layout errors are cudaErrorInvalidValue (1) before any launch; nothing to move is 0."""
+    import ctypes as C
+
+    lib = pkg.ffi.load()
+    a, b = 4096, 8192  # stand-ins for 16-byte aligned device addresses: never dereferenced on these paths
+    for fn in (lib.glm53f_fwd_gather_rows, lib.glm53f_fwd_scatter_rows):
+        assert fn(a, 64, a, b, 48, 0, 48, None) == 0       # no rows
+        assert fn(a, 64, a, b, 48, 3, 0, None) == 0        # no bytes
+        assert fn(a, 64, a, b, 48, -1, 48, None) == 1
+        assert fn(a, 64, a, b, 48, 3, -16, None) == 1
+        assert fn(a, 64, a, b, 48, 3, 40, None) == 1       # bytes not a multiple of 16
+        assert fn(a, 72, a, b, 48, 3, 48, None) == 1       # stride not a multiple of 16
+        assert fn(a, 64, a, b, 32, 3, 48, None) == 1       # stride below the row
+        assert fn(a + 8, 64, a, b, 48, 3, 48, None) == 1   # pointer not aligned
+        assert fn(a, 64, None, b, 48, 3, 48, None) == 1    # no index list
+    parts = (C.c_void_p * 3)(a, a, a)
+    sizes = (C.c_int64 * 3)(0, 0, 0)
+    assert lib.glm53f_kda_mark_copy(a, 1024, a, parts, sizes, 1, None) == 0    # an empty mark
+    assert lib.glm53f_kda_mark_copy(a, 1000, a, parts, sizes, 1, None) == 1    # page size not a multiple of 16
+    sizes = (C.c_int64 * 3)(32, 8, 0)
+    assert lib.glm53f_kda_mark_copy(a, 1024, a, parts, sizes, 1, None) == 1    # part size not a multiple of 16
+    sizes = (C.c_int64 * 3)(32, 16, 0)
+    assert lib.glm53f_kda_mark_copy(a, 1024, None, parts, sizes, 1, None) == 1  # no page list
+    assert lib.glm53f_kda_mark_copy(None, 1024, a, parts, sizes, 1, None) == 1
 
 
 def test_missing_library_fails_loudly(pkg, tmp_path):

@@ -18,6 +18,7 @@ SOURCES = {
     "kda_prefill.cu": IEEE,
     "kda_prefill_tc.cu": [],
     "kda_prefill_sp.cu": [],
+    "proj_gemm.cu": [],      # the projections: tcgen05 GEMM
     "fwd_rows.cu": [],       # row gather / scatter and the mark copy: data movement only  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
 }
 
@@ -35,7 +36,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    headers += [os.path.join(INCLUDE, "glm53f_kda.h"), os.path.join(INCLUDE, "glm53f_fwd_rows.h")]
+    headers += [os.path.join(INCLUDE, "glm53f_kda.h"), os.path.join(INCLUDE, "glm53f_fwd_rows.h"), os.path.join(INCLUDE, "glm53f_proj.h")]
     objs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     for src, flags in SOURCES.items():

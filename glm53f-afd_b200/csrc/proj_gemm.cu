@@ -1,0 +1,280 @@
+// The projections either side of the KDA core as a tcgen05 GEMM: out[g][r][o] = sum_k x[g][r][k] * w[g][o][k], bf16
+// operands, f32 accumulation in tensor memory, bf16 or f32 results.
+//
+// What it stands in for: the reference's Gemm::bf16 (crates/glm53f-forward/src/gemm.rs:212-235), which sends up to 8
+// rows to its CUDA-core GEMV (kernels/glm53f_forward.h:19-40) and more rows to cuBLAS, at the call sites of a KDA
+// layer (crates/glm53f-forward/src/forward.rs:3494-3542: the fused [q|k|v|b] projection 4096 -> 24,640 and the
+// low-rank gate pair 4096 -> 256 -> 2 x 8192; 3772-3790: o_proj 8192 -> 4096).
+//
+// Shape of the kernel.  The weight is the M operand: a tile is 128 output features x NR activation rows, NR in
+// {16, 32, 64, 128, 256} chosen from the row count, so a decode step's 16 rows waste nothing and the weight -- which
+// dominates the traffic at few rows (202 MB for the fused projection) -- streams through once.  Both operands are
+// K-major in global memory ([o][k] and [r][k]), so tiled tensor copies in the 128-byte swizzle feed tcgen05.mma
+// in place: a stage is 64 k of the weight tile (16 KiB) and of the row tile (NR x 128 bytes).  Roles per block:
+//   warp 0  producer: tensor copies into a ring of stages, each completing a stage's mbarrier;
+//   warp 1  one elected thread issues 4 MMAs (K = 16) per stage and commits the stage back to the producer, and the
+//           tile's accumulator to the epilogue when its last stage is in; owns the TMEM allocation;
+//   warps 2-5  epilogue: tcgen05.ld of the finished accumulator (lane = feature, column = row), convert, store.
+// Two accumulators alternate, so the epilogue of a tile overlaps the MMAs of the next; blocks walk the tile list with
+// the row tile fastest (blocks that run together share a weight tile in L2).  With NR <= 64 a block needs under
+// 113 KiB, so two are resident per SM and every tile of a decode-size launch is in flight at once.
+//
+// A row's result depends on that row's inputs and on (n, k) only -- the accumulation order over k is fixed by the
+// stage loop -- never on how many rows the launch has or which NR it picked (tests hold this bitwise).
+//
+// Every wait is bounded (codes 130-133 in the device status word); TMEM is freed on every path.
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "glm53f_proj.h"
+#include "kda_internal.h"
+#include "tc.cuh"
+
+namespace kda {
+namespace {
+
+constexpr int kBM = 128;            // output features per tile (UMMA M)
+constexpr int kBK = 64;             // k per stage: one 128-byte swizzle row of bf16
+constexpr int kGemmThreads = 192;   // producer, MMA, 4 epilogue warps
+constexpr int kEpiThreads = 128;
+constexpr int kABytes = kBM * 128;  // a stage's weight tile
+
+enum : int { kStatusGemmEmpty = 130, kStatusGemmFull = 131, kStatusGemmAccFull = 132, kStatusGemmAccEmpty = 133 };
+
+template <int NR>
+struct Cfg {
+    static constexpr int kBBytes = NR * 128;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = NR == 16 ? 6 : NR == 32 ? 5 : NR == 64 ? 4 : NR == 128 ? 6 : 4;
+    static constexpr int kTmemCols = 2 * NR < 32 ? 32 : 2 * NR;
+    static constexpr int oBars = kStages * kStageBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
+    static constexpr int oCtl = oBars + (2 * kStages + 4) * 8;
+    static constexpr int kBytes = oCtl + 16 + 1024;      // + slack to align the stages to 1024 bytes
+    static constexpr int kBlocksPerSm = NR <= 64 ? 2 : 1;
+};
+
+struct GemmParams {
+    CUtensorMap tm_w, tm_x;
+    void* out;
+    long long ldo, o_gstride;
+    int rows, n, kblocks, out_f32;
+    int n_tiles, r_tiles;
+    int w_swapped, x_swapped;  // the map's coordinates are (k, group, row) instead of (k, row, group)
+    long long tiles;
+    int* status;
+};
+
+template <int NR>
+__global__ void __launch_bounds__(kGemmThreads, Cfg<NR>::kBlocksPerSm) proj_gemm_kernel(const __grid_constant__ GemmParams p) {
+    using C = Cfg<NR>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::oBars);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* acc_full = empty + C::kStages;
+    uint64_t* acc_empty = acc_full + 2;
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + C::oCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < C::kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], kEpiThreads / 32);
+        }
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, C::kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x) {
+                const int rt = (int)(t % p.r_tiles);
+                const long long u = t / p.r_tiles;
+                const int nt = (int)(u % p.n_tiles), g = (int)(u / p.n_tiles);
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&empty[s], ph ^ 1u, ctx, kStatusGemmEmpty)) goto done;
+                    unsigned char* st = smem + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                    if (p.w_swapped) tensor_load_3d(st, &p.tm_w, kb * kBK, g, nt * kBM, &full[s]);
+                    else tensor_load_3d(st, &p.tm_w, kb * kBK, nt * kBM, g, &full[s]);
+                    if (p.x_swapped) tensor_load_3d(st + kABytes, &p.tm_x, kb * kBK, g, rt * NR, &full[s]);
+                    else tensor_load_3d(st + kABytes, &p.tm_x, kb * kBK, rt * NR, g, &full[s]);
+                    if (++s == C::kStages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::idesc_bf16(kBM, NR, 0, 0, 0);
+            int s = 0, buf = 0;
+            uint32_t ph = 0, acc_ph[2] = {0, 0};
+            for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x) {
+                if (!mbar_wait(&acc_empty[buf], acc_ph[buf] ^ 1u, ctx, kStatusGemmAccEmpty)) goto done;
+                tc::fence_after_sync();
+                const uint32_t d = tm + (uint32_t)(buf * NR);
+                for (int kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&full[s], ph, ctx, kStatusGemmFull)) goto done;
+                    tc::fence_after_sync();
+                    const unsigned char* st = smem + s * C::kStageBytes;
+#pragma unroll
+                    for (int i = 0; i < kBK / 16; ++i)
+                        tc::mma_bf16(d, tc::desc_sw128_kmajor(st, kBM, 16 * i), tc::desc_sw128_kmajor(st + kABytes, NR, 16 * i), idesc, kb > 0 || i > 0);
+                    tc::mma_commit(&empty[s]);
+                    if (++s == C::kStages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                tc::mma_commit(&acc_full[buf]);
+                acc_ph[buf] ^= 1u;
+                buf ^= 1;
+                ctl[0] = ctl[0] + 1u;
+            }
+        }
+    } else {
+        const int q = warp & 3;  // the TMEM lane quarter this warp may read
+        int buf = 0;
+        uint32_t acc_ph[2] = {0, 0};
+        for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x) {
+            const int rt = (int)(t % p.r_tiles);
+            const long long u = t / p.r_tiles;
+            const int nt = (int)(u % p.n_tiles), g = (int)(u / p.n_tiles);
+            if (!mbar_wait(&acc_full[buf], acc_ph[buf], ctx, kStatusGemmAccFull)) goto done;
+            acc_ph[buf] ^= 1u;
+            tc::fence_after_sync();
+            const int f = nt * kBM + q * 32 + lane;
+            const bool f_ok = f < p.n;
+            const long long row0 = (long long)rt * NR;
+            unsigned char* base = reinterpret_cast<unsigned char*>(p.out) + ((long long)g * p.o_gstride + f) * (p.out_f32 ? 4 : 2);
+#pragma unroll 1
+            for (int c0 = 0; c0 < NR; c0 += 16) {
+                uint32_t r[16];
+                tc::tmem_ld16(tc::tmem_addr(tm, q, buf * NR + c0), r);
+                tc::tmem_ld_wait();
+                if (f_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const long long row = row0 + c0 + j;
+                        if (row < p.rows) {
+                            if (p.out_f32) *reinterpret_cast<float*>(base + row * p.ldo * 4) = __uint_as_float(r[j]);
+                            else *reinterpret_cast<uint16_t*>(base + row * p.ldo * 2) = f32_to_bf16_bits(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            buf ^= 1;
+        }
+    }
+done:
+    // After an abort, copies into this block's shared memory may still be in flight: give them a bounded time.
+    if (ctl[1]) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tm, C::kTmemCols);
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) f = nullptr;
+        return reinterpret_cast<EncodeTiled>(f);
+    }();
+    return fn;
+}
+
+// A [groups][rows][k] bf16 matrix (row stride ld, group stride gstride, in elements) as a 3-D map with boxes of
+// 64 k x box_rows rows in the 128-byte swizzle; rows past the extent read as zero.  The dimensions are ordered by
+// stride -- (k, rows, groups), or (k, groups, rows) when the groups interleave inside a row (`swapped`).
+bool matrix_map(CUtensorMap* tm, int* swapped, const void* base, long long k, long long rows, long long groups, long long ld, long long gstride,
+                int box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (enc == nullptr) return false;
+    const long long gs = groups > 1 ? gstride : rows * ld;
+    *swapped = groups > 1 && gs < ld;
+    if (groups > 1 && !*swapped && gs < rows * ld) return false;  // neither nesting: not a layout the callers have
+    const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)(*swapped ? groups : rows), (cuuint64_t)(*swapped ? rows : groups)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(*swapped ? gs : ld) * 2, (cuuint64_t)(*swapped ? ld : gs) * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)kBK, *swapped ? 1u : (cuuint32_t)box_rows, *swapped ? (cuuint32_t)box_rows : 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NR>
+int launch_gemm(GemmParams& p, const void* x, long long ldx, long long x_gstride, int groups, int k, cudaStream_t stream) {
+    using C = Cfg<NR>;
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(proj_gemm_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured_dev = dev;
+    }
+    if (!matrix_map(&p.tm_x, &p.x_swapped, x, k, p.rows, groups, ldx, x_gstride, NR)) return (int)cudaErrorNotSupported;
+    p.r_tiles = (p.rows + NR - 1) / NR;
+    p.tiles = (long long)groups * p.n_tiles * p.r_tiles;
+    const long long cap = (long long)sm_count() * C::kBlocksPerSm;
+    const unsigned grid = (unsigned)(p.tiles < cap ? p.tiles : cap);
+    proj_gemm_kernel<NR><<<grid, kGemmThreads, C::kBytes, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace kda
+
+extern "C" int32_t glm53f_kda_proj_bf16(const uint16_t* x, int64_t ldx, int64_t x_gstride, const uint16_t* w, int64_t ldw, int64_t w_gstride,
+                                        int32_t groups, int32_t rows, int32_t n, int32_t k, void* out, int32_t out_f32, int64_t ldo,
+                                        int64_t o_gstride, glm53f_stream_t stream) {
+    using namespace kda;
+    if (groups < 1 || rows < 0 || n < 1 || k < kBK || k % kBK || n % 8 || ldx % 8 || ldw % 8 || ldx < k || ldw < k || ldo < n) return kInvalid;
+    if (groups > 1 && (x_gstride % 8 || w_gstride % 8 || x_gstride < 0 || w_gstride < 0 || o_gstride < 0)) return kInvalid;
+    if (rows == 0) return 0;
+    if (!x || !w || !out || !aligned16(x) || !aligned16(w) || (reinterpret_cast<uintptr_t>(out) & (out_f32 ? 3 : 1))) return kInvalid;
+    GemmParams p{};
+    p.out = out;
+    p.ldo = ldo;
+    p.o_gstride = groups > 1 ? o_gstride : 0;
+    p.rows = rows;
+    p.n = n;
+    p.kblocks = k / kBK;
+    p.out_f32 = out_f32 != 0;
+    p.n_tiles = (n + kBM - 1) / kBM;
+    p.status = status_word();
+    if (p.status == nullptr) return (int)cudaErrorUnknown;
+    if (!matrix_map(&p.tm_w, &p.w_swapped, w, k, n, groups, ldw, w_gstride, kBM)) return (int)cudaErrorNotSupported;
+    if (rows <= 16) return launch_gemm<16>(p, x, ldx, x_gstride, groups, k, stream);
+    if (rows <= 32) return launch_gemm<32>(p, x, ldx, x_gstride, groups, k, stream);
+    if (rows <= 64) return launch_gemm<64>(p, x, ldx, x_gstride, groups, k, stream);
+    if (rows <= 128) return launch_gemm<128>(p, x, ldx, x_gstride, groups, k, stream);
+    return launch_gemm<256>(p, x, ldx, x_gstride, groups, k, stream);
+}

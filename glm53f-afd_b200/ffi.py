@@ -1,4 +1,4 @@
-"""Raw bindings of the C ABI (include/glm53f_kda.h, include/glm53f_fwd_rows.h), one Python callable per `extern "C"` symbol.
+"""Raw bindings of the C ABI (include/glm53f_kda.h, include/glm53f_fwd_rows.h, include/glm53f_proj.h), one Python callable per `extern "C"` symbol.
 
 The counterpart of the reference crate's `ffi` module (crates/glm53f-kda/src/ffi.rs:16-287): no checks, raw device
 addresses as integers, the launcher's int status returned as is.  The library must exist: there is no CPU path.
@@ -44,10 +44,12 @@ SIGNATURES = {
     "glm53f_fwd_gather_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
     "glm53f_fwd_scatter_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
     "glm53f_kda_mark_copy": (I32, [P, I64, P, P, P, I32, P]),
+    # include/glm53f_proj.h: the projections' GEMM (the arguments of glm53f_fwd_gemv_bf16 without its split-K scratch)
+    "glm53f_kda_proj_bf16": (I32, [P, I64, I64, P, I64, I64, I32, I32, I32, I32, P, I32, I64, I64, P]),
 }
 
 # The reference's thirteen (crates/glm53f-kda/tests/provenance.rs:41-69 asserts exactly these).
-REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy")]
+REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy", "glm53f_kda_proj_bf16")]
 
 
 def library_path() -> str:

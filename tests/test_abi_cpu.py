@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared():
     names = set()
-    for header in ("glm53f_kda.h", "glm53f_fwd_rows.h"):
+    for header in ("glm53f_kda.h", "glm53f_fwd_rows.h", "glm53f_proj.h"):
         text = open(os.path.join(ROOT, "include", header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names |= set(re.findall(r"\b(glm53f_(?:kda|fwd)_\w+)\s*\(", text))
@@ -68,3 +68,27 @@ def test_missing_library_fails_loudly(pkg, tmp_path):
 
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         pkg.ffi.load(str(tmp_path / "libglm53f_kda.so"))
+
+
+def test_projection_gemm_rejects_on_the_host(pkg):
+    lib = pkg.ffi.load()
+    a = 4096  # a stand-in for an aligned device address: never dereferenced on these paths
+    ok = dict(x=a, ldx=4096, xg=0, w=a, ldw=4096, wg=0, groups=1, rows=0, n=64, k=4096, out=a, f32=0, ldo=64, og=0)
+
+    def call(**kw):
+        v = {**ok, **kw}
+        return lib.glm53f_kda_proj_bf16(v["x"], v["ldx"], v["xg"], v["w"], v["ldw"], v["wg"], v["groups"], v["rows"], v["n"], v["k"],
+                                        v["out"], v["f32"], v["ldo"], v["og"], None)
+
+    assert call() == 0                 # no rows: nothing to do
+    assert call(rows=-1) == 1
+    assert call(groups=0) == 1
+    assert call(k=4000) == 1           # k not a multiple of 64
+    assert call(k=0) == 1
+    assert call(n=60) == 1             # n not a multiple of 8
+    assert call(ldx=4100) == 1 and call(ldw=4100) == 1
+    assert call(ldx=2048) == 1         # a row stride below k
+    assert call(ldo=32) == 1           # an output stride below n
+    assert call(groups=2, xg=12) == 1  # group stride not a multiple of 8
+    assert call(rows=4, x=a + 8) == 1 and call(rows=4, w=a + 2) == 1
+    assert call(rows=4, x=None) == 1 and call(rows=4, out=None) == 1

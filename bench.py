@@ -313,6 +313,70 @@ def run_marks(torch, pkg, rank, slots=16, reps=5):
     return res
 
 
+def run_projections(torch, pkg, rank, layers=6):
+    """The GEMMs either side of the KDA core at the model's widths, on the tcgen05 kernel: the fused [q|k|v|b]
+    projection 4096 -> 24,640 and o_proj 8192 -> 4096, for a decode step's 16 rows (bound by the weight's bytes: one
+    distinct weight per layer, so they stream from HBM) and for a 2,048-row prefill lane (bound by the tensor cores).
+    Each shape is a CUDA graph of `layers` launches; the library GEMM (torch.matmul) is timed the same way beside it."""
+    import importlib
+
+    proj = importlib.import_module(pkg.__name__ + ".proj")
+    g = torch.Generator(device="cuda").manual_seed(0x53454544 + 11 + rank)
+    hbm, kind = peaks()
+    try:  # a GEMM timed alone: the burst figure of the measured bf16 peak
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf = (float(json.load(f)["bf16_tflops"]), "measured")
+    except Exception:
+        tf = (1590.0, "fallback")
+    res = {"workload": f"x[rows][k] . w[n][k]^T, bf16 in, f32 accumulate, bf16 out; {layers} distinct weights per shape",
+           "peak_source": kind, "shapes": []}
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            fn()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n / layers
+
+    for name, n, k in (("qkvb", proj.KDA_P_COLS, proj.HIDDEN), ("o_proj", proj.HIDDEN, proj.KDA_WIDTH)):
+        ws = [(torch.randn(n, k, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(layers)]
+        mats = [proj.Bf16Mat.dense(w) for w in ws]
+        for rows in (SLOTS, 2048):
+            x = torch.randn(rows, k, device="cuda", generator=g).to(torch.bfloat16)
+            out = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+
+            def ours():
+                for m in mats:
+                    proj.bf16(x, k, 0, m, rows, out, n, 0)
+
+            def library():
+                for w in ws:
+                    torch.matmul(x, w.T, out=out)
+
+            ms, ms_lib = timed(ours), timed(library)
+            flops, nbytes = 2.0 * rows * n * k, 2.0 * (n * k + rows * (n + k))
+            entry = {"gemm": name, "rows": rows, "n": n, "k": k, "us": ms * 1e3, "library_us": ms_lib * 1e3,
+                     "tflops": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9, "gpu_launches": 1}
+            if rows <= 64:
+                entry.update(bound="hbm", frac=entry["gbs"] / hbm, algorithmic_bytes=nbytes)
+            else:
+                entry.update(bound="tensor", frac=entry["tflops"] / tf[0], peak_tflops=tf[0], tensor_peak_source=tf[1], flops=flops)
+            res["shapes"].append(entry)
+        del ws, mats
+        torch.cuda.empty_cache()
+    return res
+
+
 def run_packed_prefill(torch, pkg, core, rank, passes=10):
     """Config 2: 8,192 rows of packed variable-length sequences (lengths 256..2,048), 64 heads, half of the sequences
     from a carried state: tokens/s per layer through the single-pass kernel (one block per (sequence, head)) and
@@ -577,6 +641,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers per step (profiling runs use fewer)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="sequence length of the prefill leg (0 skips it)")
     ap.add_argument("--prefill-passes", type=int, default=3)
+    ap.add_argument("--no-proj", action="store_true", help="skip the projection GEMM leg")
     ap.add_argument("--no-marks", action="store_true", help="skip the state snapshot / restore leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4) and the packed-prefill leg (config 2)")
     ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
@@ -739,6 +804,7 @@ def main():
     assert core.device_status() == 0
     packed = run_packed_prefill(torch, pkg, core, rank) if not args.no_verify else None
     marks = run_marks(torch, pkg, rank) if not args.no_marks else None
+    projections = run_projections(torch, pkg, rank) if not args.no_proj else None
     prefill = None
     if args.prefill_tokens > 0:
         prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
@@ -765,6 +831,7 @@ def main():
         "verify": verify,
         "prefill_packed": packed,
         "marks": marks,
+        "projections": projections,
         "prefill": prefill,
     }
     if not args.no_cpu:

@@ -2,6 +2,8 @@
 
 `ffi`     raw bindings of include/glm53f_kda.h (the drop-in boundary);
 `kernel`  checked wrappers mirroring the reference crate's host API (crates/glm53f-kda/src/kernel.rs);
+`core`    wrappers of the post-conv ("core") entry points; `marks` state snapshot / restore over pool pages;
+`proj`    the projections' GEMM; `verify` the verify / commit round over pool slots;
 `synth`   seeded synthetic inputs of the benchmark configurations;
 `build()` compiles csrc/ into libglm53f_kda.so (nvcc, sm_100a).
 """

@@ -26,6 +26,9 @@ namespace {
 #define ROWS_VECS 8
 #define ROWS_BLOCKS_PER_SM 16
 #endif
+#ifndef ROWS_MIN_BLOCKS
+#define ROWS_MIN_BLOCKS 1
+#endif
 constexpr int kCopyThreads = ROWS_THREADS;
 constexpr int kVecs = ROWS_VECS;                       // 16-byte loads in flight per thread
 constexpr int kTileChunks = kCopyThreads * kVecs;      // 16-byte chunks per tile: 32 KiB
@@ -49,7 +52,7 @@ __device__ __forceinline__ void copy_vecs(const uint4* __restrict__ s, uint4* __
     }
 }
 
-__global__ void __launch_bounds__(kCopyThreads) rows_tile_kernel(const uint8_t* __restrict__ src, long long src_stride, const int32_t* __restrict__ idx,
+__global__ void __launch_bounds__(kCopyThreads, ROWS_MIN_BLOCKS) rows_tile_kernel(const uint8_t* __restrict__ src, long long src_stride, const int32_t* __restrict__ idx,
                                                                  uint8_t* __restrict__ dst, long long dst_stride, long long chunks, int tiles_per_row,
                                                                  long long units, int scatter) {
     for (long long u = blockIdx.x; u < units; u += gridDim.x) {
@@ -81,7 +84,7 @@ struct MarkParts {
     int first_page[3];        // the part's first entry of page_idx
 };
 
-__global__ void __launch_bounds__(kCopyThreads) mark_copy_kernel(uint8_t* __restrict__ pages, long long page_chunks, int tiles_per_page,
+__global__ void __launch_bounds__(kCopyThreads, ROWS_MIN_BLOCKS) mark_copy_kernel(uint8_t* __restrict__ pages, long long page_chunks, int tiles_per_page,
                                                                  const int32_t* __restrict__ page_idx, const MarkParts m, int save) {
     for (long long u = blockIdx.x; u < m.first_unit[3]; u += gridDim.x) {
         const int p = u >= m.first_unit[2] ? 2 : u >= m.first_unit[1] ? 1 : 0;

@@ -19,6 +19,7 @@ SOURCES = {
     "kda_prefill_tc.cu": [],
     "kda_prefill_sp.cu": [],
     "proj_gemm.cu": [],      # the projections: tcgen05 GEMM
+    "proj_gemm_pair.cu": [], # the same on SM pairs (cta_group::2) for many rows
     "fwd_rows.cu": [],       # row gather / scatter and the mark copy: data movement only  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
 }
 

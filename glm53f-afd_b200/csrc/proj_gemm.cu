@@ -32,12 +32,19 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "glm53f_proj.h"
 #include "kda_internal.h"
 #include "tc.cuh"
 
 namespace kda {
+
+// proj_gemm_pair.cu: 256 x 256 tiles on SM pairs, for launches with many rows.
+int proj_gemm_pair_launch(const CUtensorMap& tm_w, int w_swapped, const CUtensorMap& tm_x, int x_swapped, void* out, long long ldo, long long o_gstride,
+                          int groups, int rows, int n, int k, int out_f32, int* status, cudaStream_t stream);
+
 namespace {
 
 constexpr int kBM = 128;            // output features per tile (UMMA M)
@@ -413,6 +420,17 @@ extern "C" int32_t glm53f_kda_proj_bf16(const uint16_t* x, int64_t ldx, int64_t 
     if (rows <= 128) return launch_gemm<128>(p, x, ldx, x_gstride, groups, k, stream);
     // Wide row tiles once there are rows enough to fill the GPU with them; otherwise narrower ones, two blocks per SM,
     // which quantise better (measured for n = 24,640: 384 rows 81 us against 96 us, 768 rows 144 us against 141 us).
-    if (rows > 512 && (long long)groups * p.n_tiles * ((rows + 255) / 256) >= sm_count()) return launch_gemm<256>(p, x, ldx, x_gstride, groups, k, stream);
+    if (rows > 512 && (long long)groups * p.n_tiles * ((rows + 255) / 256) >= sm_count()) {
+        // Enough 256 x 256 tiles for every SM pair: the two-block kernel (GLM53F_KDA_PROJ_PAIR=0 keeps one block per tile).
+        static const bool pair = [] {
+            const char* e = getenv("GLM53F_KDA_PROJ_PAIR");
+            return e == nullptr || e[0] != '0';
+        }();
+        if (pair) {
+            if (!matrix_map(&p.tm_x, &p.x_swapped, x, k, rows, groups, ldx, x_gstride, 128)) return (int)cudaErrorNotSupported;
+            return proj_gemm_pair_launch(p.tm_w, p.w_swapped, p.tm_x, p.x_swapped, out, ldo, o_gstride, groups, rows, n, k, out_f32 != 0, p.status, stream);
+        }
+        return launch_gemm<256>(p, x, ldx, x_gstride, groups, k, stream);
+    }
     return launch_gemm<128>(p, x, ldx, x_gstride, groups, k, stream);
 }

@@ -136,3 +136,18 @@ def test_kda_layer_projections(proj, rows):
     # the library GEMM agrees within the same bound (reported by the reference's test for cuBLAS)
     lib = (normed.float() @ w.qkvb.t.float().T)
     assert go.rel_rms(p.float().cpu().numpy(), lib.to(torch.bfloat16).float().cpu().numpy()) < 2e-3
+
+
+@pytest.mark.parametrize("f32_out", [True, False])
+def test_many_rows_on_sm_pairs(proj, f32_out):
+    """Above 512 rows with enough tiles the 256 x 256 tiles run on SM pairs (cta_group::2): ragged features (n not a
+    multiple of 128), ragged rows, padded output rows, guards."""
+    rng = go.Rng(21)
+    groups, n, k, R = 1, 2568, 512, 2050
+    w = rng.bf16s(n * k, 0.05).reshape(1, n, k)
+    x = rng.bf16s(R * k, 1.0).reshape(1, R, k)
+    got = run(proj, x, w, R, f32_out, ldo=n + 8, pad=64)
+    check(got, x, w, f32_out)
+    # a second launch on the same buffers gives the same bits
+    again = run(proj, x, w, R, f32_out, ldo=n + 8, pad=64)
+    assert (got.view(np.uint32) == again.view(np.uint32)).all()

@@ -203,6 +203,10 @@ struct UnitIter {
             const int r0 = p.cu_rows[b];
             x.row0 = r0;
             x.rows = p.cu_rows[b + 1] - r0;
+            if (p.keep) {  // a commit by recomputation: only the request's first keep[b] rows
+                const int kept = p.keep[b];
+                if (kept < x.rows) x.rows = kept;
+            }
         } else {
             x.row0 = 0;
             x.rows = p.rows1;
@@ -903,7 +907,7 @@ bool saves_ok(const void* k, const void* v, const void* g, const void* b) {
 }
 
 // Reference kda.cu:290-299, 310-312, 329-332.
-int chain_entry(int32_t heads, int32_t batch, bool batched, const int32_t* cu_rows, int32_t rows, const glm53f_bf16* p,
+int chain_entry(int32_t heads, int32_t batch, bool batched, const int32_t* cu_rows, const int32_t* keep, int32_t rows, const glm53f_bf16* p,
                 int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* g,
                 int64_t g_stride, const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w,
                 const void* state_in, void* state_out, const int64_t* state_off, bool bf16_state, const float* a_log,
@@ -923,6 +927,7 @@ int chain_entry(int32_t heads, int32_t batch, bool batched, const int32_t* cu_ro
     q.layers = 1;
     q.units = (long long)heads * batch;
     q.cu_rows = cu_rows;
+    q.keep = keep;
     q.rows1 = rows;
     q.P = p; q.p_stride = p_stride; q.b_off = b_off;
     q.A = a; q.a_stride = a_stride;
@@ -1027,7 +1032,7 @@ extern "C" int glm53f_kda_chain(int32_t heads, int32_t rows, const glm53f_bf16* 
                                 float* state_out, const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
                                 float eps, float lower, glm53f_bf16* out, int64_t out_stride, float* k_save,
                                 glm53f_bf16* v_save, float* g_save, float* b_save, glm53f_stream_t stream) {
-    return chain_entry(heads, 1, false, nullptr, rows, p, p_stride, b_off, a, a_stride, g, g_stride, conv, nullptr, conv_w,
+    return chain_entry(heads, 1, false, nullptr, nullptr, rows, p, p_stride, b_off, a, a_stride, g, g_stride, conv, nullptr, conv_w,
                        state_in, state_out, nullptr, false, a_log, dt_bias, norm_w, eps, lower, out, out_stride, k_save,
                        v_save, g_save, b_save, stream);
 }
@@ -1040,7 +1045,7 @@ extern "C" int glm53f_kda_chain_batch(int32_t heads, int32_t batch, const int32_
                                       const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower,
                                       glm53f_bf16* out, int64_t out_stride, float* k_save, glm53f_bf16* v_save,
                                       float* g_save, float* b_save, glm53f_stream_t stream) {
-    return chain_entry(heads, batch, true, cu_rows, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
+    return chain_entry(heads, batch, true, cu_rows, nullptr, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
                        conv_w, state_in, state_out, state_off, false, a_log, dt_bias, norm_w, eps, lower, out,
                        out_stride, k_save, v_save, g_save, b_save, stream);
 }
@@ -1055,9 +1060,22 @@ extern "C" int glm53f_kda_chain_batch_bf16state(int32_t heads, int32_t batch, co
                                                 float lower, glm53f_bf16* out, int64_t out_stride, float* k_save,
                                                 glm53f_bf16* v_save, float* g_save, float* b_save,
                                                 glm53f_stream_t stream) {
-    return chain_entry(heads, batch, true, cu_rows, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
+    return chain_entry(heads, batch, true, cu_rows, nullptr, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off,
                        conv_w, state_in, state_out, state_off, true, a_log, dt_bias, norm_w, eps, lower, out, out_stride,
                        k_save, v_save, g_save, b_save, stream);
+}
+
+extern "C" int glm53f_kda_chain_commit_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, const int32_t* keep,
+                                             const glm53f_bf16* p, int64_t p_stride, int64_t b_off, const glm53f_bf16* a,
+                                             int64_t a_stride, const glm53f_bf16* g, int64_t g_stride, const glm53f_bf16* conv,
+                                             const int64_t* conv_off, const glm53f_bf16* conv_w, void* state,
+                                             const int64_t* state_off, int32_t state_bf16, const float* a_log,
+                                             const float* dt_bias, const glm53f_bf16* norm_w, float eps, float lower,
+                                             glm53f_bf16* out, int64_t out_stride, glm53f_stream_t stream) {
+    if (!keep || !state) return kInvalid;
+    return chain_entry(heads, batch, true, cu_rows, keep, 0, p, p_stride, b_off, a, a_stride, g, g_stride, conv, conv_off, conv_w,
+                       state, state, state_off, state_bf16 != 0, a_log, dt_bias, norm_w, eps, lower, out, out_stride, nullptr,
+                       nullptr, nullptr, nullptr, stream);
 }
 
 extern "C" int glm53f_kda_replay(int32_t heads, int32_t rows, const float* state_in, float* state_out,

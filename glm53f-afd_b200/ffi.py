@@ -31,6 +31,7 @@ SIGNATURES = {
     "glm53f_kda_prefill": (C.c_int, [I32, I32, *_CHAIN_TAIL, P, P, P, P, P, P, P, F32, F32, P, I64, I32, P, I64, P]),
     "glm53f_kda_prefill_batch": (C.c_int, [I32, I32, P, I32, *_CHAIN_TAIL, P, P, P, P, P, P, P, P, P, F32, F32, P, I64, I32, P, I64, P]),
     "glm53f_kda_prefill_batch_bf16state": (C.c_int, [I32, I32, P, I32, *_CHAIN_TAIL, P, P, P, P, P, P, P, P, P, F32, F32, P, I64, I32, P, I64, P]),
+    "glm53f_kda_chain_commit_batch": (C.c_int, [I32, I32, P, P, *_CHAIN_TAIL, P, P, P, P, P, I32, P, P, P, F32, F32, P, I64, P]),
     "glm53f_kda_core_decode_batch": (C.c_int, [I32, I32, P, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P]),
     "glm53f_kda_core_verify_batch": (C.c_int, [I32, I32, P, P, P, P, P, P, P, P, P, I32, I32, P, P, F32, P, P, P, P, P, P]),
     "glm53f_kda_core_commit_batch": (C.c_int, [I32, I32, I32, P, P, P, P, I64, P, I32, P, P, P, P, I64, I64, P]),
@@ -49,7 +50,7 @@ SIGNATURES = {
 }
 
 # The reference's thirteen (crates/glm53f-kda/tests/provenance.rs:41-69 asserts exactly these).
-REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy", "glm53f_kda_proj_bf16")]
+REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy", "glm53f_kda_proj_bf16", "glm53f_kda_chain_commit_batch")]
 
 
 def library_path() -> str:

@@ -33,16 +33,26 @@ MAX_WINDOW = 8  # forward.rs:1908
 
 class VerifyScratch:
     """Buffers a verify round keeps until its commit (forward.rs:777-815, the KDA layers' part): every layer's
-    projection rows (the conv shift reads them) and replay inputs."""
+    projection rows (the conv shift reads them) and replay inputs.  With `recompute` the replay inputs (82,176 bytes
+    per row and layer) are not kept: the commit recomputes them from the projection rows and the decay-gate rows
+    (16,384 bytes per row and layer), which are kept instead."""
 
-    def __init__(self, rows: int, kda_layers: int):
-        self.rows, self.layers = rows, kda_layers
+    def __init__(self, rows: int, kda_layers: int, recompute: bool = False):
+        self.rows, self.layers, self.recompute = rows, kda_layers, recompute
         self.p = K.DeviceBuffer.zeroed(kda_layers * rows * KDA_P_COLS * 2)
-        self.saves = K.LayerSaves.alloc(kda_layers, KDA_HEADS, rows)
+        self.saves = None if recompute else K.LayerSaves.alloc(kda_layers, KDA_HEADS, rows)
+        self.a = K.DeviceBuffer.zeroed(kda_layers * rows * KDA_WIDTH * 2) if recompute else None
+        self.sink = K.DeviceBuffer.zeroed(rows * KDA_WIDTH * 2) if recompute else None  # the recomputed rows' outputs
 
     def bytes(self) -> int:
+        if self.recompute:
+            return self.p.bytes() + self.a.bytes() + self.sink.bytes()
         s = self.saves
         return self.p.bytes() + s.k.bytes() + s.v.bytes() + s.g.bytes() + s.b.bytes()
+
+    def a_rows(self, layer: int) -> K.RowView:
+        """Layer `layer`'s decay-gate rows [rows][8192] (recompute mode: the caller's gate GEMM writes them here)."""
+        return K.RowView.new(self.a, layer * self.rows * KDA_WIDTH, KDA_WIDTH)
 
     def p_rows(self, layer: int) -> K.RowView:
         """Layer `layer`'s projection rows [rows][24,640]: the caller's projection GEMM writes them here."""
@@ -65,12 +75,12 @@ class _Req:
 class KdaVerify:
     """Verify and commit over the KDA layers of the slots of one pool."""
 
-    def __init__(self, pool: marks.KvPool, weights: Sequence[K.Weights], max_verify_rows: int, max_requests: int):
+    def __init__(self, pool: marks.KvPool, weights: Sequence[K.Weights], max_verify_rows: int, max_requests: int, recompute: bool = False):
         l = pool.cfg.layout
         if len(weights) != l.kda_layers:
             raise Invalid(f"{len(weights)} layers of weights for a pool of {l.kda_layers} KDA layers")
         self.pool, self.weights = pool, list(weights)
-        self.v = VerifyScratch(max_verify_rows, l.kda_layers)
+        self.v = VerifyScratch(max_verify_rows, l.kda_layers, recompute)
         self.meta = K.BatchMeta.new(max_requests)
         self.pending: Optional[list[_Req]] = None
         self._st = K.StateType.Bf16 if l.kda_state_bf16 else K.StateType.F32
@@ -103,7 +113,10 @@ class KdaVerify:
         if self.pending is None:
             raise Invalid("no verify is open")
         state, conv = self._layer_views(j)
-        cb = K.ChainBatch(self.weights[j], self.v.p_rows(j), KDA_QKV, a, g, conv, state, K.StateOut.Skip, out, self.v.layer_saves(j))
+        if self.v.recompute and not (a.buf is self.v.a and a.offset == self.v.a_rows(j).offset):
+            raise Invalid("recompute mode: layer j's decay-gate rows live in scratch.a_rows(j)")
+        cb = K.ChainBatch(self.weights[j], self.v.p_rows(j), KDA_QKV, a, g, conv, state, K.StateOut.Skip, out,
+                          None if self.v.recompute else self.v.layer_saves(j))
         stream = stream or self.pool.stream
         if self._st is K.StateType.Bf16:
             cb.launch_bf16_state(self.meta, stream)
@@ -131,10 +144,22 @@ class KdaVerify:
         # to the entry points directly (forward.rs:1972-2031).
         sn, cn = l.state_elems_per_layer(), l.conv_elems_per_layer()
         sv, m = self.v.saves, self.meta
-        fn = ffi.glm53f_kda_replay_batch_bf16state if self._st is K.StateType.Bf16 else ffi.glm53f_kda_replay_batch
-        K._launched(fn(KDA_HEADS, l.kda_layers, m.batch(), m.cu_rows.ptr(), m.keep_d.ptr(), self.pool.state.ptr(), self.pool.state.ptr(), sn,
-                       m.state_off.ptr(), sv.k.ptr(), sv.v.ptr(), sv.g.ptr(), sv.b.ptr(), sv.kv_stride(), sv.b_stride(), stream.raw()),
-                    "glm53f_kda_replay_batch")
+        if self.v.recompute:
+            # No saves: every layer's chain again over the kept rows, in place, from the rows the round kept.  The decay
+            # rows stand in for the output-gate rows: the outputs go to a sink.
+            for j, w in enumerate(self.weights):
+                state, conv = self._layer_views(j)
+                pr, ar = self.v.p_rows(j), self.v.a_rows(j)
+                K._launched(ffi.glm53f_kda_chain_commit_batch(
+                    KDA_HEADS, m.batch(), m.cu_rows.ptr(), m.keep_d.ptr(), pr.ptr(), pr.stride, KDA_QKV, ar.ptr(), ar.stride, ar.ptr(), ar.stride,
+                    conv.ptr(), m.conv_off.ptr(), w.conv_w.ptr(), state.ptr(), m.state_off.ptr(), 1 if self._st is K.StateType.Bf16 else 0,
+                    w.a_log.ptr(), w.dt_bias.ptr(), w.norm_w.ptr(), w.eps, w.lower, self.v.sink.ptr(), KDA_WIDTH, stream.raw()),
+                    "glm53f_kda_chain_commit_batch")
+        else:
+            fn = ffi.glm53f_kda_replay_batch_bf16state if self._st is K.StateType.Bf16 else ffi.glm53f_kda_replay_batch
+            K._launched(fn(KDA_HEADS, l.kda_layers, m.batch(), m.cu_rows.ptr(), m.keep_d.ptr(), self.pool.state.ptr(), self.pool.state.ptr(), sn,
+                           m.state_off.ptr(), sv.k.ptr(), sv.v.ptr(), sv.g.ptr(), sv.b.ptr(), sv.kv_stride(), sv.b_stride(), stream.raw()),
+                        "glm53f_kda_replay_batch")
         K._launched(ffi.glm53f_kda_conv_shift_batch(KDA_QKV, l.kda_layers, m.batch(), m.cu_rows.ptr(), m.keep_d.ptr(), self.pool.conv.ptr(), cn,
                                                     m.conv_off.ptr(), self.v.p.ptr(), self.v.rows * KDA_P_COLS, KDA_P_COLS, stream.raw()),
                     "glm53f_kda_conv_shift_batch")

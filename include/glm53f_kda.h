@@ -245,6 +245,23 @@ int glm53f_kda_core_verify_batch(int32_t heads, int32_t batch, const int32_t* cu
                                  float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save,
                                  glm53f_stream_t stream);
 
+/* A commit without saved replay inputs (an addition): one layer's states advanced in place over the first
+ * keep[b] rows of each request, recomputed from the projection rows the verify round kept -- glm53f_kda_chain_batch
+ * (same arguments, same arithmetic, so the bits of keep[b] single-row calls) limited to keep[b] <= rows of each
+ * request.  The conv windows must still be the verify round's (shift them afterwards).  A verify round then keeps,
+ * per row and layer, the 49,280-byte projection row it keeps anyway (crates/glm53f-forward/src/forward.rs:777-790)
+ * and the 16,384-byte decay-gate row instead of 82,176 bytes of k, v, g and beta.  `out` receives the kept rows'
+ * outputs again (any [rows][out_stride] buffer); `state_bf16` selects the state type. */
+int glm53f_kda_chain_commit_batch(int32_t heads, int32_t batch, const int32_t* cu_rows, const int32_t* keep,
+                                  const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                                  const glm53f_bf16* a, int64_t a_stride,
+                                  const glm53f_bf16* g, int64_t g_stride,
+                                  const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w,
+                                  void* state, const int64_t* state_off, int32_t state_bf16,
+                                  const float* a_log, const float* dt_bias, const glm53f_bf16* norm_w,
+                                  float eps, float lower, glm53f_bf16* out, int64_t out_stride,
+                                  glm53f_stream_t stream);
+
 /* The commit after a verify round, for every layer at once: glm53f_kda_replay_batch with the state type as
  * an argument.  Keeping keep[b] rows gives the bits of keep[b] single-row decode calls. */
 int glm53f_kda_core_commit_batch(int32_t heads, int32_t layers, int32_t batch,

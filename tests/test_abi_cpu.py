@@ -34,6 +34,10 @@ def test_host_side_rejections_need_no_gpu(pkg):
     assert lib.glm53f_kda_prefill_workspace_bytes(0, 1, 16) == 0
     assert lib.glm53f_kda_conv_shift(0, 0, None, None, 0, None) == 1
     assert lib.glm53f_kda_replay(0, 0, None, None, None, None, None, None, None) == 1
+    a = 4096  # a stand-in for a device address: never dereferenced when a check rejects
+    args = [a, 24640, 24576, a, 8192, a, 8192, a, a, a, a, a, 1, a, a, a, 1e-5, -5.0, a, 8192, None]
+    assert lib.glm53f_kda_chain_commit_batch(64, 2, a, None, *args) == 1   # a commit names the rows each request keeps
+    assert lib.glm53f_kda_chain_commit_batch(0, 2, a, a, *args) == 1
 
 
 def test_row_movers_reject_on_the_host_like_the_reference(pkg):

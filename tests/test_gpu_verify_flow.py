@@ -34,8 +34,8 @@ def rows_on_device(K, rows):
             K.RowView.dense(K.DeviceBuffer.from_slice(K._bf16_encode(rows.gate)), h * DK))
 
 
-@pytest.mark.parametrize("bf16", [True, False])
-def test_verify_then_commit_equals_serial_decode(mods, oracle, bf16):
+@pytest.mark.parametrize("bf16,recompute", [(True, False), (False, False), (True, True), (False, True)])
+def test_verify_then_commit_equals_serial_decode(mods, oracle, bf16, recompute):
     K, marks, verify = mods["kernel"], mods["marks"], mods["verify"]
     o, layers = oracle, 2
     windows, keep = [5, 8, 1], [3, 8, 1]
@@ -60,7 +60,8 @@ def test_verify_then_commit_equals_serial_decode(mods, oracle, bf16):
 
     # ---- pool 0: one verify round over all layers, then the commit
     kv0 = kvs[0]
-    vf = verify.KdaVerify(pools[0], weights, 16, 4)
+    vf = verify.KdaVerify(pools[0], weights, 16, 4, recompute=recompute)
+    assert vf.v.bytes() == (2 * 16 * (24_640 * 2 + 8192 * 2) + 16 * 8192 * 2 if recompute else 2 * 16 * (24_640 * 2 + 64 * 1_284))
     with pytest.raises(verify.Invalid, match="commit without a verify"):
         vf.commit(kv0, keep)
     with pytest.raises(verify.Invalid, match="1..=8 rows"):
@@ -76,7 +77,13 @@ def test_verify_then_commit_equals_serial_decode(mods, oracle, bf16):
     for j in range(layers):
         vf.v.p.upload_at(j * vf.v.rows * verify.KDA_P_COLS, dev[j][0])
         out = K.RowView.dense(K.DeviceBuffer.zeroed(total * H * DK * 2), H * DK)
-        vf.layer(j, dev[j][1], dev[j][2], out)
+        a_rows = dev[j][1]
+        if recompute:  # the decay-gate rows are kept in the scratch for the commit
+            vf.v.a.upload_at(j * vf.v.rows * H * DK, dev[j][1].buf.download(np.uint16, total * H * DK))
+            a_rows = vf.v.a_rows(j)
+            with pytest.raises(verify.Invalid, match="decay-gate rows live in scratch"):
+                vf.layer(j, dev[j][1], dev[j][2], out)
+        vf.layer(j, a_rows, dev[j][2], out)
         outs.append(out)
     pools[0].stream.synchronize()
     assert torch.equal(pools[0].state.t, before)  # a verify reads the states, it does not write them

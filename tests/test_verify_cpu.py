@@ -15,6 +15,7 @@ def test_round_bookkeeping_and_rejections(pkg, monkeypatch):
         verify.KdaVerify(pool, [None, None], 16, 4)
     vf = verify.KdaVerify(pool, [None], 12, 4)
     assert vf.v.bytes() == 12 * (24_640 * 2 + 64 * 1_284)  # projection rows + 1,284 B of replay inputs per row and head
+    assert verify.VerifyScratch(12, 1, recompute=True).bytes() == 12 * (24_640 * 2 + 8_192 * 2) + 12 * 8_192 * 2
     a, b, c = pool.slot(), pool.slot(), pool.slot()
     with pytest.raises(verify.Invalid, match="commit without a verify"):
         vf.commit([a], [1])

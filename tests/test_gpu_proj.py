@@ -151,3 +151,19 @@ def test_many_rows_on_sm_pairs(proj, f32_out):
     # a second launch on the same buffers gives the same bits
     again = run(proj, x, w, R, f32_out, ldo=n + 8, pad=64)
     assert (got.view(np.uint32) == again.view(np.uint32)).all()
+
+
+def test_wide_weight_mid_range_rows(proj):
+    """A wide weight (150 feature tiles) at 65..300 rows (128-row tiles, two blocks per SM): parity, and the rows that
+    a 64-row launch also computes have the same bits -- the accumulation over k is the same sequence in every tile
+    shape that does not split k."""
+    rng = go.Rng(23)
+    n, k, R = 19_200, 256, 300
+    w = rng.bf16s(n * k, 0.05).reshape(1, n, k)
+    x = rng.bf16s(R * k, 1.0).reshape(1, R, k)
+    small = run(proj, x, w, 64, True)
+    check(small, x, w, True)
+    for rows in (65, 128, 129, 300):
+        got = run(proj, x, w, rows, True, ldo=n + 8, pad=16)
+        check(got, x, w, True)
+        assert (got[:, :64].view(np.uint32) == small.view(np.uint32)).all(), rows

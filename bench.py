@@ -304,6 +304,25 @@ def run_marks(torch, pkg, rank, slots=16, reps=5):
                 ms = timed(lambda: device_pass(save), reps) / slots
                 gbs = 2 * l.mark_bytes() / (ms * 1e-3) / 1e9
                 res[name] = {"us_per_mark": ms * 1e3, "gbs": gbs, "frac_of_hbm": gbs / hbm, "gpu_launches_per_mark": 1}
+        if fused:
+            # all 16 slots' marks by one launch (glm53f_kda_mark_copy_slots)
+            all_lists = torch.cat(lists)
+            slot_ids = torch.tensor([kv.slot for kv in kvs], dtype=torch.int32, device="cuda")
+            arenas = (C.c_void_p * 3)(pool.state.as_ptr(), pool.conv.as_ptr(), pool.tails.as_ptr())
+            strides = (C.c_int64 * 3)(l.kda_state_bytes(), l.conv_bytes(), max(l.tails_bytes(), 16))
+
+            def batched(save):
+                rc = lib.glm53f_kda_mark_copy_slots(pool.pages.as_ptr(), l.page_bytes, all_lists.data_ptr(), arenas, sizes, strides,
+                                                    slot_ids.data_ptr(), slots, save, st)
+                if rc != 0:
+                    raise RuntimeError(f"mark copy failed: {rc}")
+
+            for name, save in (("save_all_slots_one_launch", 1), ("restore_all_slots_one_launch", 0)):
+                for _ in range(3):
+                    batched(save)
+                ms = timed(lambda: batched(save), reps) / slots
+                gbs = 2 * l.mark_bytes() / (ms * 1e-3) / 1e9
+                res[name] = {"us_per_mark": ms * 1e3, "gbs": gbs, "frac_of_hbm": gbs / hbm, "gpu_launches": 1}
         for _ in range(2):
             api_pass()
         ms = timed(api_pass, 3) / slots

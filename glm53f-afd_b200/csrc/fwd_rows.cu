@@ -78,15 +78,20 @@ __global__ void __launch_bounds__(kCopyThreads) rows_warp_kernel(const uint8_t* 
 }
 
 struct MarkParts {
-    uint8_t* part[3];
+    uint8_t* part[3];         // one mark: the slot's parts; several: the arenas' bases
     long long chunks[3];      // 16-byte chunks of each part
-    long long first_unit[4];  // prefix sums of the parts' (page, tile) units
-    int first_page[3];        // the part's first entry of page_idx
+    long long first_unit[4];  // prefix sums of the parts' (page, tile) units; [3] = units of one mark
+    int first_page[3];        // the part's first entry of a mark's page list
+    long long slot_chunks[3]; // several marks: 16-byte chunks from one slot's part to the next slot's
+    const int32_t* slots;     // several marks: the slot of each (device), or null for one mark at part[]
+    int mark_pages;           // entries of page_idx per mark
+    long long units;          // all marks' units
 };
 
 __global__ void __launch_bounds__(kCopyThreads, ROWS_MIN_BLOCKS) mark_copy_kernel(uint8_t* __restrict__ pages, long long page_chunks, int tiles_per_page,
                                                                  const int32_t* __restrict__ page_idx, const MarkParts m, int save) {
-    for (long long u = blockIdx.x; u < m.first_unit[3]; u += gridDim.x) {
+    for (long long u0 = blockIdx.x; u0 < m.units; u0 += gridDim.x) {
+        const long long mark = u0 / m.first_unit[3], u = u0 - mark * m.first_unit[3];
         const int p = u >= m.first_unit[2] ? 2 : u >= m.first_unit[1] ? 1 : 0;
         const long long v = u - m.first_unit[p];
         const long long page = v / tiles_per_page;
@@ -94,8 +99,8 @@ __global__ void __launch_bounds__(kCopyThreads, ROWS_MIN_BLOCKS) mark_copy_kerne
         // What this page holds of the part: a whole page, or the part's remainder.
         const long long left = m.chunks[p] - page * page_chunks;
         const long long n = left < page_chunks ? left : page_chunks;
-        uint4* in_pool = reinterpret_cast<uint4*>(pages) + (long long)page_idx[m.first_page[p] + page] * page_chunks;
-        uint4* in_arena = reinterpret_cast<uint4*>(m.part[p]) + page * page_chunks;
+        uint4* in_pool = reinterpret_cast<uint4*>(pages) + (long long)page_idx[mark * m.mark_pages + m.first_page[p] + page] * page_chunks;
+        uint4* in_arena = reinterpret_cast<uint4*>(m.part[p]) + (m.slots ? (long long)m.slots[mark] * m.slot_chunks[p] : 0) + page * page_chunks;
         const long long c0 = (long long)tile * kTileChunks + threadIdx.x;
         if (save) copy_vecs(in_arena, in_pool, c0, kCopyThreads, n);
         else copy_vecs(in_pool, in_arena, c0, kCopyThreads, n);
@@ -143,10 +148,11 @@ extern "C" int32_t glm53f_fwd_scatter_rows(const uint8_t* src, int64_t src_strid
     return kda::gather_scatter(src, src_stride, idx, dst, dst_stride, rows, bytes, 1, stream);
 }
 
-extern "C" int32_t glm53f_kda_mark_copy(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const part[3],
-                                        const int64_t part_bytes[3], int32_t save, glm53f_stream_t stream) {
-    using namespace kda;
-    if (!part || !part_bytes || page_bytes <= 0 || page_bytes % 16) return cudaErrorInvalidValue;
+namespace kda {
+namespace {
+int32_t mark_copy_launch(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const part[3], const int64_t part_bytes[3],
+                         const int64_t* slot_stride, const int32_t* slots, int32_t marks, int32_t save, cudaStream_t stream) {
+    if (!part || !part_bytes || page_bytes <= 0 || page_bytes % 16 || marks < 0) return cudaErrorInvalidValue;
     MarkParts m{};
     const long long page_chunks = page_bytes / 16;
     const long long tiles = (page_chunks + kTileChunks - 1) / kTileChunks;
@@ -155,9 +161,11 @@ extern "C" int32_t glm53f_kda_mark_copy(uint8_t* pages, int64_t page_bytes, cons
     for (int p = 0; p < 3; ++p) {
         if (part_bytes[p] < 0 || part_bytes[p] % 16) return cudaErrorInvalidValue;
         if (part_bytes[p] > 0 && (!part[p] || !aligned16(part[p]))) return cudaErrorInvalidValue;
+        if (slot_stride && part_bytes[p] > 0 && (slot_stride[p] % 16 || slot_stride[p] < part_bytes[p])) return cudaErrorInvalidValue;
         const long long n_pages = (part_bytes[p] + page_bytes - 1) / page_bytes;
         m.part[p] = part[p];
         m.chunks[p] = part_bytes[p] / 16;
+        m.slot_chunks[p] = slot_stride ? slot_stride[p] / 16 : 0;
         m.first_unit[p] = unit;
         m.first_page[p] = (int)page;
         unit += n_pages * tiles;
@@ -165,8 +173,25 @@ extern "C" int32_t glm53f_kda_mark_copy(uint8_t* pages, int64_t page_bytes, cons
         if (page > 0x7fffffffLL) return cudaErrorInvalidValue;
     }
     m.first_unit[3] = unit;
-    if (unit == 0) return cudaSuccess;
+    m.mark_pages = (int)page;
+    m.slots = slots;
+    m.units = unit * marks;
+    if (m.units == 0) return cudaSuccess;
     if (!pages || !aligned16(pages) || !page_idx) return cudaErrorInvalidValue;
-    mark_copy_kernel<<<grid_for(unit), kCopyThreads, 0, stream>>>(pages, page_chunks, (int)tiles, page_idx, m, save != 0);
+    mark_copy_kernel<<<grid_for(m.units), kCopyThreads, 0, stream>>>(pages, page_chunks, (int)tiles, page_idx, m, save != 0);
     return cudaGetLastError();
+}
+}  // namespace
+}  // namespace kda
+
+extern "C" int32_t glm53f_kda_mark_copy(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const part[3],
+                                        const int64_t part_bytes[3], int32_t save, glm53f_stream_t stream) {
+    return kda::mark_copy_launch(pages, page_bytes, page_idx, part, part_bytes, nullptr, nullptr, 1, save, stream);
+}
+
+extern "C" int32_t glm53f_kda_mark_copy_slots(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const arena[3],
+                                              const int64_t part_bytes[3], const int64_t slot_stride[3], const int32_t* slots, int32_t marks,
+                                              int32_t save, glm53f_stream_t stream) {
+    if (!slot_stride || (marks > 0 && !slots)) return cudaErrorInvalidValue;
+    return kda::mark_copy_launch(pages, page_bytes, page_idx, arena, part_bytes, slot_stride, slots, marks, save, stream);
 }

@@ -45,12 +45,13 @@ SIGNATURES = {
     "glm53f_fwd_gather_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
     "glm53f_fwd_scatter_rows": (I32, [P, I64, P, P, I64, I32, I64, P]),
     "glm53f_kda_mark_copy": (I32, [P, I64, P, P, P, I32, P]),
+    "glm53f_kda_mark_copy_slots": (I32, [P, I64, P, P, P, P, P, I32, I32, P]),
     # include/glm53f_proj.h: the projections' GEMM (the arguments of glm53f_fwd_gemv_bf16 without its split-K scratch)
     "glm53f_kda_proj_bf16": (I32, [P, I64, I64, P, I64, I64, I32, I32, I32, I32, P, I32, I64, I64, P]),
 }
 
 # The reference's thirteen (crates/glm53f-kda/tests/provenance.rs:41-69 asserts exactly these).
-REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy", "glm53f_kda_proj_bf16", "glm53f_kda_chain_commit_batch")]
+REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_mark_copy", "glm53f_kda_mark_copy_slots", "glm53f_kda_proj_bf16", "glm53f_kda_chain_commit_batch")]
 
 
 def library_path() -> str:

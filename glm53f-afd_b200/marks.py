@@ -192,6 +192,50 @@ class KvPool:
     def bytes(self) -> int:
         return self.pages.bytes()
 
+    # ---- several slots in one launch (an addition: the reference marks slot by slot) -------------------------------
+    def _copy_marks(self, kvs, marks_, save: bool) -> None:
+        torch = kernel._torch()
+        l = self.cfg.layout
+        if any(m._pool is not self or kv.pool is not self for kv, m in zip(kvs, marks_)):
+            raise Invalid("a mark or a slot of another pool")
+        if len({kv.slot for kv in kvs}) != len(kvs):
+            raise Invalid("the same slot twice in one batch")
+        n = len(kvs)
+        lists = torch.tensor([m._pages for m in marks_], dtype=torch.int32).reshape(-1).to(self.pages.t.device)
+        slots = torch.tensor([kv.slot for kv in kvs], dtype=torch.int32).to(self.pages.t.device)
+        arenas = (C.c_void_p * 3)(self.state.as_ptr(), self.conv.as_ptr(), self.tails.as_ptr())
+        sizes = (C.c_int64 * 3)(*[r[1] for r in l.mark_regions()])
+        strides = (C.c_int64 * 3)(l.kda_state_bytes(), l.conv_bytes(), max(l.tails_bytes(), 16))
+        _launched(ffi.load().glm53f_kda_mark_copy_slots(self.pages.as_ptr(), l.page_bytes, lists.data_ptr(), arenas, sizes, strides, slots.data_ptr(),
+                                                        n, 1 if save else 0, self.stream.raw()), "mark pages")
+        self._keep = (lists, slots)  # alive until the next batch: the launch reads them in stream order
+
+    def mark_many(self, kvs) -> list:
+        """A mark of every slot of `kvs` (each as GlmKv.mark), copied by one launch; OutOfMemory before anything is
+        allocated when the pool has too few free pages for all of them."""
+        if any(kv.pending != 0 for kv in kvs):
+            raise Invalid("mark inside an uncommitted verify window")
+        need = self.cfg.layout.mark_pages()
+        if self.alloc.free() < need * len(kvs):
+            raise OutOfMemory(f"{len(kvs)} snapshot marks take {need * len(kvs)} pages of the KV pool, {self.alloc.free()} are free")
+        out = [KvMark(kv.tokens(), sorted(self.alloc.alloc() for _ in range(need)), self) for kv in kvs]
+        if kvs:
+            self._copy_marks(kvs, out, True)
+        return out
+
+    def rewind_many(self, kvs, marks_) -> None:
+        """GlmKv.rewind(mark.tokens, mark) for every (slot, mark), the states restored by one launch."""
+        if len(kvs) != len(marks_):
+            raise Invalid("one mark per slot")
+        for kv, m in zip(kvs, marks_):
+            if m.tokens > kv.tokens():
+                raise Invalid(f"rewind to {m.tokens} with a mark at {m.tokens} (the slot holds {kv.tokens()})")
+        if kvs:
+            self._copy_marks(kvs, marks_, False)
+        for kv, m in zip(kvs, marks_):
+            kv._tokens = m.tokens
+            kv.pending = 0
+
     def slot(self) -> "GlmKv":
         """A new empty slot, or OutOfMemory when every slot is taken (kv.rs:174-200)."""
         if not self._free_slots:

@@ -61,6 +61,14 @@ int32_t glm53f_fwd_scatter_rows(const uint8_t* src, int64_t src_stride, const in
 int32_t glm53f_kda_mark_copy(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const part[3],
                              const int64_t part_bytes[3], int32_t save, glm53f_stream_t stream);
 
+/* The same for several slots in one launch (an addition): mark i (i < marks) saves or restores slot slots[i] (a device
+ * array), whose part p lies at arena[p] + slots[i] * slot_stride[p]; its pages are page_idx[i * mark_pages ..] with
+ * mark_pages = the sum over p of ceil(part_bytes[p] / page_bytes).  slot_stride[p] is a multiple of 16 and at least
+ * part_bytes[p].  The slots are distinct, and so are all pages.  marks == 0 launches nothing. */
+int32_t glm53f_kda_mark_copy_slots(uint8_t* pages, int64_t page_bytes, const int32_t* page_idx, uint8_t* const arena[3],
+                                   const int64_t part_bytes[3], const int64_t slot_stride[3], const int32_t* slots,
+                                   int32_t marks, int32_t save, glm53f_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

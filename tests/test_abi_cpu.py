@@ -65,6 +65,12 @@ def test_row_movers_reject_on_the_host_like_the_reference(pkg):
     sizes = (C.c_int64 * 3)(32, 16, 0)
     assert lib.glm53f_kda_mark_copy(a, 1024, None, parts, sizes, 1, None) == 1  # no page list
     assert lib.glm53f_kda_mark_copy(None, 1024, a, parts, sizes, 1, None) == 1
+    strides = (C.c_int64 * 3)(64, 16, 16)
+    assert lib.glm53f_kda_mark_copy_slots(a, 1024, a, parts, sizes, strides, a, 0, 1, None) == 0     # no marks
+    assert lib.glm53f_kda_mark_copy_slots(a, 1024, a, parts, sizes, None, a, 2, 1, None) == 1        # no strides
+    assert lib.glm53f_kda_mark_copy_slots(a, 1024, a, parts, sizes, strides, None, 2, 1, None) == 1  # no slot list
+    assert lib.glm53f_kda_mark_copy_slots(a, 1024, a, parts, sizes, (C.c_int64 * 3)(16, 16, 16), a, 2, 1, None) == 1  # slots overlap
+    assert lib.glm53f_kda_mark_copy_slots(a, 1024, a, parts, sizes, strides, a, -1, 1, None) == 1
 
 
 def test_missing_library_fails_loudly(pkg, tmp_path):

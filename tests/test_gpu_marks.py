@@ -239,3 +239,51 @@ def test_a_rewound_slot_continues_bit_for_bit(G, marks):
     assert all(torch.equal(x, y) for x, y in zip(first, again))
     assert torch.equal(pool.state.t[a._state_at():a._state_at() + l.kda_state_bytes()], after)
     assert after.any()
+
+
+@pytest.mark.parametrize("bf16", [True, False])
+def test_marks_of_several_slots_in_one_launch(marks, bf16):
+    """mark_many / rewind_many (one launch for all slots) write and restore the bytes of slot-by-slot marks."""
+    l = marks.KvLayout.new(2, 3).with_kda_state_bf16(bf16)
+    need = l.mark_pages()
+    pool = marks.KvPool(marks.KvConfig(l, 5, 8 * need + 3))
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for arena in (pool.state, pool.conv, pool.tails):
+        arena.t.copy_(torch.randint(0, 256, (arena.t.numel(),), dtype=torch.uint8, device="cuda", generator=g))
+    kvs = [pool.slot() for _ in range(5)]
+    for arena in (pool.state, pool.conv, pool.tails):  # slot() zeroes a slot's state: fill again
+        arena.t.copy_(torch.randint(0, 256, (arena.t.numel(),), dtype=torch.uint8, device="cuda", generator=g))
+    for i, kv in enumerate(kvs):
+        kv.advance(10 + i)
+    # interleave allocations so that the marks' pages are scattered, then take marks of slots 4, 1, 3 in one launch
+    spare = [pool.alloc.alloc() for _ in range(7)]
+    for p in spare[::2]:
+        pool.alloc.release(p)
+    chosen = [kvs[4], kvs[1], kvs[3]]
+    free0 = pool.free_pages()
+    batch = pool.mark_many(chosen)
+    assert pool.free_pages() == free0 - 3 * need and [m.tokens for m in batch] == [14, 11, 13]
+    single = [kv.mark() for kv in chosen]
+    pool.stream.synchronize()
+    pages = pool.pages.t.cpu().numpy().reshape(-1, l.page_bytes)
+    for mb, ms in zip(batch, single):
+        sizes = [r[1] for r in l.mark_regions()]
+        a = ro.export_state(pages.reshape(-1), l.page_bytes, mb.page_list(), sizes, 0)
+        b = ro.export_state(pages.reshape(-1), l.page_bytes, ms.page_list(), sizes, 0)
+        assert (a == b).all()
+    before = [arena.t.clone() for arena in (pool.state, pool.conv, pool.tails)]
+    for kv in chosen:
+        kv.advance(2)
+        pool.state.t[kv._state_at():kv._state_at() + l.kda_state_bytes()].zero_()
+        pool.conv.t[kv._conv_at():kv._conv_at() + l.conv_bytes()] ^= 0x55
+        pool.tails.t[kv._tails_at():kv._tails_at() + l.tails_bytes()].zero_()
+    pool.rewind_many(chosen, batch)
+    pool.stream.synchronize()
+    for arena, want in zip((pool.state, pool.conv, pool.tails), before):
+        assert torch.equal(arena.t, want)  # the chosen slots are back, the others were never touched
+    assert [kv.tokens() for kv in chosen] == [14, 11, 13]
+    with pytest.raises(marks.Invalid, match="same slot twice"):
+        pool.mark_many([kvs[0], kvs[0]])
+    with pytest.raises(marks.OutOfMemory):
+        pool.mark_many(kvs)
+    assert pool.mark_many([]) == []

@@ -203,7 +203,7 @@ struct UnitIter {
             const int r0 = p.cu_rows[b];
             x.row0 = r0;
             x.rows = p.cu_rows[b + 1] - r0;
-            if (p.keep) {  // a commit by recomputation: only the request's first keep[b] rows
+            if (MODE == kLayer && p.keep) {  // a commit by recomputation: only the request's first keep[b] rows
                 const int kept = p.keep[b];
                 if (kept < x.rows) x.rows = kept;
             }

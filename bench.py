@@ -12,8 +12,11 @@ so every launch streams its states from HBM: the working set is ~8x the 126 MB L
   roofline  algorithmic state bytes per launch / mean launch time, against the measured HBM copy bandwidth
   cpu_baseline   the CPU oracle (the reference's recurrence restated in C++) on all host cores, on a bounded sample
 
-`--impl reference` times the reference's CPU formulation instead (the oracle port: the reference is Rust and no
-Rust toolchain exists on this machine) and prints the same line with "impl": "reference".
+`--impl reference` times the reference instead and prints the same line with "impl": "reference": the reference's
+OWN CUDA kernels (compiled from the reference tree by `make -C oracle ref` into oracle/_ref, unmodified, for sm_100a)
+on the same GPU, same shapes, same CUDA-graph and event timing, entered through the reference's own symbol for this
+step (glm53f_kda_chain_batch_bf16state); its CPU formulation (the oracle port: the reference's CPU code is Rust and
+no Rust toolchain exists on this machine) is the line's `cpu_baseline`, and the whole arm when oracle/_ref is absent.
 With torchrun (N > 1) every rank decodes its own 16 slots (slots are independent units: no collective on the data
 path); the time is the maximum over ranks and `value` the whole job's.
 """
@@ -101,6 +104,166 @@ def oracle_module():
 
     kda_oracle.build()
     return kda_oracle
+
+
+# ---- the layer ABI (the thirteen drop-in symbols) on the engine's argument values --------------------------------------
+P_STRIDE, B_OFF, AG_STRIDE, OUT_STRIDE, CONV_CH = 24_640, 24_576, 16_384, 8_192, 3 * HEADS * DK  # crates/glm53f-forward/src/shape.rs:22-32
+LAYER_IN_BYTES = (P_STRIDE + AG_STRIDE) * 2   # one token's projection row and gate rows
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libglm53f_kda_ref.so")
+
+
+def reference_library(pkg):
+    """The reference's own kernels (oracle/_ref, built from the reference tree), typed like the product's; None when absent."""
+    if not os.path.exists(REF_LIB):
+        return None
+    lib = C.CDLL(REF_LIB)
+    for name in pkg.ffi.REFERENCE_SYMBOLS:
+        res, argtypes = pkg.ffi.SIGNATURES[name]
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, argtypes
+    return lib
+
+
+class LayerAbi:
+    """Inputs of the layer entry points with the forward's argument values (p rows [q|k|v|b] of 24,640, beta logits at
+    24,576, the interleaved [a|g] gate rows of 16,384, out rows of 8,192, eps 1e-5, lower -5; slot-major state and conv
+    arenas per layer), and the three steps of the engine through them, for any library exporting the thirteen symbols."""
+
+    def __init__(self, torch, rank, slots, rows_per_slot, layers, bf16_state=True, seed=0):
+        self.torch, self.slots, self.rps, self.layers, self.bf16 = torch, slots, rows_per_slot, layers, bf16_state
+        gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 31 + 97 * rank + seed)
+        rows = self.rows = slots * rows_per_slot
+        rn = lambda n, s=1.0: (torch.randn(n, device="cuda", generator=gen) * s)
+        self.p = rn(layers * rows * P_STRIDE).to(torch.bfloat16)
+        self.ag = rn(layers * rows * AG_STRIDE).to(torch.bfloat16)
+        self.conv = rn(layers * slots * 3 * CONV_CH).to(torch.bfloat16)
+        self.conv_w = rn(CONV_CH * 4, 0.5).to(torch.bfloat16)
+        self.a_log, self.dt_bias = rn(HEADS, 0.5), rn(HEADS * DK)
+        self.norm_w = (1.0 + rn(DK, 0.1)).to(torch.bfloat16)
+        st = rn(layers * slots * STATE_ELEMS, 0.05)
+        self.state = st.to(torch.bfloat16) if bf16_state else st
+        self.out = torch.empty(layers * rows * OUT_STRIDE, dtype=torch.bfloat16, device="cuda")
+        self.cu = torch.arange(slots + 1, dtype=torch.int32, device="cuda") * rows_per_slot
+        self.conv_off = torch.arange(slots, dtype=torch.int64, device="cuda") * (3 * CONV_CH)
+        self.state_off = torch.arange(slots, dtype=torch.int64, device="cuda") * STATE_ELEMS
+
+    def at(self, t, elems):
+        return C.c_void_p(t.data_ptr() + elems * t.element_size())
+
+    def chain(self, lib, l, stream, write_state=True, saves=None, p=None, ag=None, out=None):
+        """One layer's chain over every slot's rows (decode: one row each; verify: the window, states untouched)."""
+        r, P = self.rows, lambda t: C.c_void_p(t.data_ptr())
+        p_at = self.at(self.p, l * r * P_STRIDE) if p is None else p
+        ag_t, ag_e = (self.ag, l * r * AG_STRIDE) if ag is None else ag
+        st = self.at(self.state, l * self.slots * STATE_ELEMS)
+        fn = lib.glm53f_kda_chain_batch_bf16state if self.bf16 else lib.glm53f_kda_chain_batch
+        sv = [None] * 4 if saves is None else saves
+        rc = fn(HEADS, self.slots, P(self.cu), p_at, P_STRIDE, B_OFF, self.at(ag_t, ag_e), AG_STRIDE, self.at(ag_t, ag_e + 8192), AG_STRIDE,
+                self.at(self.conv, l * self.slots * 3 * CONV_CH), P(self.conv_off), P(self.conv_w), st, st if write_state else None,
+                P(self.state_off), P(self.a_log), P(self.dt_bias), P(self.norm_w), 1e-5, -5.0,
+                self.at(self.out, l * r * OUT_STRIDE) if out is None else out, OUT_STRIDE, *sv, stream)
+        if rc != 0:
+            raise RuntimeError(f"chain launch failed: {rc}")
+
+    def prefill(self, lib, l, stream, ws, ws_bytes, max_rows, value_blocks=0):
+        r, P = self.rows, lambda t: C.c_void_p(t.data_ptr())
+        st = self.at(self.state, l * self.slots * STATE_ELEMS)
+        fn = lib.glm53f_kda_prefill_batch_bf16state if self.bf16 else lib.glm53f_kda_prefill_batch
+        rc = fn(HEADS, self.slots, P(self.cu), max_rows, self.at(self.p, l * r * P_STRIDE), P_STRIDE, B_OFF,
+                self.at(self.ag, l * r * AG_STRIDE), AG_STRIDE, self.at(self.ag, l * r * AG_STRIDE + 8192), AG_STRIDE,
+                self.at(self.conv, l * self.slots * 3 * CONV_CH), P(self.conv_off), P(self.conv_w), st, st, P(self.state_off),
+                P(self.a_log), P(self.dt_bias), P(self.norm_w), 1e-5, -5.0, self.at(self.out, l * r * OUT_STRIDE), OUT_STRIDE,
+                value_blocks, P(ws), ws_bytes, stream)
+        if rc != 0:
+            raise RuntimeError(f"prefill launch failed: {rc}")
+
+
+def graph_ms(torch, fn, reps, warm=3):
+    """`fn(stream)` captured once in a CUDA graph on a side stream, replayed `reps` times between events."""
+    side = torch.cuda.Stream()
+    st = C.c_void_p(side.cuda_stream)
+    with torch.cuda.stream(side):
+        for _ in range(warm):
+            fn(st)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fn(st)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps, graph
+
+
+def run_layer_abi(torch, lib, rank, layers, steps, prefill_lib_ok=True):
+    """The engine's three steps through the drop-in symbols of `lib` (the product, or the reference's own kernels):
+    decode (config 1's shape: 16 slots x 1 row x `layers` layers, bf16 states), verify + commit (config 4's shape:
+    48 slots x 16 rows, saves written, states untouched, then glm53f_kda_replay_batch_bf16state over every layer)
+    and the prefill lanes (config 2's engine shape: 4 lanes x 2,048 rows, glm53f_kda_prefill_batch[_bf16state])."""
+    import numpy as np
+
+    hbm, kind = peaks()
+    res = {"arguments": {"p_stride": P_STRIDE, "b_off": B_OFF, "ag_stride": AG_STRIDE, "out_stride": OUT_STRIDE, "eps": 1e-5, "lower": -5.0}}
+    # decode
+    d = LayerAbi(torch, rank, SLOTS, 1, layers)
+    ms, _g = graph_ms(torch, lambda st: [d.chain(lib, l, st) for l in range(layers)], steps)
+    gbs = layers * STATE_BYTES_PER_LAUNCH / (ms * 1e-3) / 1e9
+    res["decode"] = {"entry": "glm53f_kda_chain_batch_bf16state", "ms_per_step": ms, "state_gbs": gbs, "frac_of_hbm": gbs / hbm, "gpu_launches": layers}
+    del d, _g
+    torch.cuda.empty_cache()
+    # verify + commit
+    v = LayerAbi(torch, rank, VERIFY_SLOTS, VERIFY_WINDOW, layers)
+    nkv, nb = v.rows * HEADS * DK, v.rows * HEADS
+    ks, gs_ = torch.empty(layers * nkv, device="cuda"), torch.empty(layers * nkv, device="cuda")
+    vs, bs = torch.empty(layers * nkv, dtype=torch.bfloat16, device="cuda"), torch.empty(layers * nb, device="cuda")
+    keep = torch.tensor(np.random.default_rng(0x53454548).integers(0, VERIFY_WINDOW + 1, VERIFY_SLOTS), dtype=torch.int32, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())
+
+    def verify(st):
+        for l in range(layers):
+            v.chain(lib, l, st, write_state=False, saves=[v.at(ks, l * nkv), v.at(vs, l * nkv), v.at(gs_, l * nkv), v.at(bs, l * nb)])
+
+    def commit(st):
+        rc = lib.glm53f_kda_replay_batch_bf16state(HEADS, layers, VERIFY_SLOTS, P(v.cu), P(keep), P(v.state), P(v.state), VERIFY_SLOTS * STATE_ELEMS,
+                                                   P(v.state_off), P(ks), P(vs), P(gs_), P(bs), nkv, nb, st)
+        if rc != 0:
+            raise RuntimeError(f"replay launch failed: {rc}")
+
+    n = max(2, steps // 5)
+    ms_v, _g1 = graph_ms(torch, verify, n, warm=2)
+    ms_c, _g2 = graph_ms(torch, commit, n, warm=2)
+    sb = layers * VERIFY_SLOTS * STATE_ELEMS * 2
+    res["verify"] = {"entry": "glm53f_kda_chain_batch_bf16state (state_out NULL, saves)", "ms_per_step": ms_v, "rows_per_s": v.rows * layers / (ms_v * 1e-3),
+                     "state_gbs": sb / (ms_v * 1e-3) / 1e9, "frac_of_hbm": sb / (ms_v * 1e-3) / 1e9 / hbm}
+    res["commit"] = {"entry": "glm53f_kda_replay_batch_bf16state", "ms_per_step": ms_c, "state_gbs": 2 * sb / (ms_c * 1e-3) / 1e9,
+                     "frac_of_hbm": 2 * sb / (ms_c * 1e-3) / 1e9 / hbm}
+    del v, ks, gs_, vs, bs, _g1, _g2
+    torch.cuda.empty_cache()
+    # prefill lanes: 4 lanes x 2,048 rows in one call, and one lane per call; f32 and bf16 states
+    lanes, lane_rows, pl = 4, 2048, min(layers, 2)
+    res["prefill_layer"] = {"workload": f"{lanes} lanes x {lane_rows} rows, 64 heads, through glm53f_kda_prefill_batch[_bf16state]; ms per lane and layer",
+                            "reference_published_ms_per_lane": {"value": 0.983, "where": "RTX 5090, docs/PERFORMANCE.md:374-378"}}
+    for bf16 in (False, True):
+        for batch in (lanes, 1):
+            f = LayerAbi(torch, rank, batch, lane_rows, pl, bf16_state=bf16, seed=5)
+            wsb = int(lib.glm53f_kda_prefill_workspace_bytes(HEADS, batch, 256))
+            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda")
+            try:
+                ms, _g = graph_ms(torch, lambda st: [f.prefill(lib, l, st, ws, wsb, lane_rows, 2) for l in range(pl)], max(2, steps // 5), warm=2)
+                res["prefill_layer"][("bf16state" if bf16 else "f32state") + f"_batch{batch}"] = {
+                    "ms_per_lane": ms / pl / batch, "rows_per_s": batch * lane_rows * pl / (ms * 1e-3), "workspace_bytes": wsb, "value_blocks": 2}
+                del _g
+            finally:
+                del f, ws
+                torch.cuda.empty_cache()
+    return res
 
 
 def cpu_decode_gbs(seconds: float, layers_sample: int = 2):
@@ -206,10 +369,14 @@ def run_verify(torch, lib, rank, layers, steps):
         commit()
     ms_v, ms_c = timed(verify), timed(commit)
     state_bytes = layers * slots * per * 2
+    v_bytes = state_bytes + layers * rows * (TOKEN_IN_BYTES + TOKEN_OUT_BYTES + HEADS * 1284)
     hbm, kind = peaks()
     res = {"workload": f"config 4: {slots} slots x {window} draft rows x {layers} layers, bf16 states, accepted prefixes drawn from 0..{window}",
            "verify": {"ms_per_step": ms_v, "rows_per_s": rows * layers / (ms_v * 1e-3), "state_gbs": state_bytes / (ms_v * 1e-3) / 1e9,
-                      "algorithmic_bytes": state_bytes + layers * rows * (TOKEN_IN_BYTES + TOKEN_OUT_BYTES + HEADS * 1284), "gpu_launches": layers},
+                      "algorithmic_bytes": v_bytes, "gpu_launches": layers,
+                      "roofline": {"bound": "hbm", "achieved": v_bytes / (ms_v * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                                   "frac": v_bytes / (ms_v * 1e-3) / 1e9 / hbm, "peak_source": kind,
+                                   "counts": "each bf16 state read once, the rows' inputs and outputs, the replay saves written"}},
            "commit": {"ms_per_step": ms_c, "state_gbs": 2 * state_bytes / (ms_c * 1e-3) / 1e9, "frac_of_hbm": 2 * state_bytes / (ms_c * 1e-3) / 1e9 / hbm,
                       "peak_source": kind, "mean_kept_rows": float(keeps.mean()), "gpu_launches": 1}}
     del arena, ks, gs_, vs, bs
@@ -570,6 +737,7 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, 
     res = {
         "workload": f"config 3: one sequence of {tokens} tokens, H=64 ({hl} heads per GPU), d=128, chunk 64, FP32 state",
         "value": tokens / (ms_total * 1e-3), "unit": "tokens/s per layer", "ms_per_layer": ms_total,
+        "heads_per_gpu": hl, "n_gpus": world, "scaling": "strong (the same sequence, heads split over the GPUs)",
         "compute_only": {"value": tokens / (ms_compute * 1e-3), "ms_per_layer": ms_compute},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": hbm_kind,
                      "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
@@ -619,11 +787,130 @@ def check_prefill(torch, tokens, hl, n_heads, q, k, v, g, beta, out, state):
             "limits": {"state_rel_l2": 1e-3, "out_max_abs": 2e-2, "out_rel_l2": 5e-3}, "cpu_seconds": cpu_s}
 
 
+def run_decode_strong(torch, dist, lib, rank, world, layers, steps):
+    """The benchmark's own sharding of configurations 1 and 4: a fixed number of slots (16, 48) split by slot over the
+    ranks (no collective), every rank's 34 layer launches replayed from one CUDA graph; whole-job state GB/s from the
+    slowest rank.  With 8 GPUs a rank holds 2 (6) slots: the launches are short and the figure shows what that costs."""
+    par = importlib.import_module("glm53f-afd_b200.parallel")
+    res = []
+    for total in (SLOTS, VERIFY_SLOTS):
+        lo, hi = par.slot_range(total, rank, world)
+        n = hi - lo
+        gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 41 + rank)
+        rows = n * HEADS
+
+        def unit(scale):
+            x = torch.randn(rows, DK, device="cuda", generator=gen)
+            return (x * (scale / torch.sqrt((x * x).sum(1, keepdim=True) + 1e-6))).to(torch.bfloat16).reshape(-1)
+
+        q, k = unit(DK ** -0.5), unit(1.0)
+        v = torch.randn(rows * DK, device="cuda", generator=gen).to(torch.bfloat16)
+        g = torch.nn.functional.logsigmoid(torch.randn(rows * DK, device="cuda", generator=gen) + 3.0)
+        beta = torch.sigmoid(torch.randn(rows, device="cuda", generator=gen))
+        arena = (torch.randn(layers * n * STATE_ELEMS, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+        out = torch.empty(rows * DK, dtype=torch.bfloat16, device="cuda")
+        cu = torch.arange(n + 1, dtype=torch.int32, device="cuda")
+        offs = torch.arange(n, dtype=torch.int64, device="cuda") * STATE_ELEMS
+        P = lambda t: C.c_void_p(t.data_ptr())
+
+        def step(stream):
+            for l in range(layers):
+                st = C.c_void_p(arena.data_ptr() + 2 * l * n * STATE_ELEMS)
+                rc = lib.glm53f_kda_core_decode_batch(HEADS, n, P(cu), P(q), P(k), P(v), P(g), P(beta), st, st, P(offs), 1, 0, None, None, 1e-5, P(out), stream)
+                if rc != 0:
+                    raise RuntimeError(f"decode launch failed: {rc}")
+
+        _ms, graph = graph_ms(torch, step, 3)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        gbs = layers * total * STATE_ELEMS * 4 / (ms * 1e-3) / 1e9
+        res.append({"slots_total": total, "slots_per_gpu": n, "ms_per_step": ms, "state_gbs": gbs, "us_per_launch": ms * 1e3 / layers,
+                    "gpu_launches": steps * layers})
+        del arena, graph, q, k, v, g, beta, out
+        torch.cuda.empty_cache()
+    return res
+
+
 def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
-def run_reference(args):
+def headline_config(layers):
+    return {"workload": "config 1: batched single-token decode, 16 slots per GPU, H=64, d=128, 34 layers, bf16-stored states",
+            "layers": layers, "l2": "inputs larger than L2: 1.06 GiB of states stream per step", "sharding": "by slot, no collective",
+            "launch": "one CUDA graph of the step's 34 launches, replayed"}
+
+
+METRIC = "KDA decode state GB/s (16 slots x 34 layers, bf16 states)"
+
+
+def bind_to_gpu_numa(torch, index):
+    """Best effort: run this process on the CPUs of the GPU's NUMA node, so that pinned staging buffers are local to the
+    GPU's PCIe root (first touch).  Returns the node, or None when the topology files say nothing."""
+    try:
+        bus = torch.cuda.get_device_properties(index).pci_bus_id
+        dom = torch.cuda.get_device_properties(index).pci_domain_id
+        dev = torch.cuda.get_device_properties(index).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
+def e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer, group=9):
+    """One end-to-end step: the step's inputs go from one pinned host block to the device in a few large copies, one
+    per group of layers on a copy stream, so that the transfer of the next group runs beside the launches of the
+    current one; the outputs come back the same way; the step ends when its outputs are on the host."""
+    groups = [(a, min(a + group, layers)) for a in range(0, layers, group)]
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def step():
+        main = torch.cuda.current_stream()
+        copy_in.wait_stream(main)   # the previous step's launches have read the staging block
+        copy_out.wait_stream(main)
+        for a, b in groups:
+            with torch.cuda.stream(copy_in):
+                dev_in[a * layer_in:b * layer_in].copy_(host_in[a * layer_in:b * layer_in], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record()
+            main.wait_event(arrived)
+            for l in range(a, b):
+                launch_layer(l)
+            done = torch.cuda.Event()
+            done.record()
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                host_out[a * out_bytes:b * out_bytes].copy_(dev_out[a * out_bytes:b * out_bytes], non_blocking=True)
+        main.wait_stream(copy_out)
+
+    return step
+
+
+def run_reference_cpu(args):
+    """No reference kernels and no GPU needed: the reference's CPU formulation (the oracle port) on the host cores."""
     rank, _, world = dist_env()
     if rank != 0:
         return
@@ -637,15 +924,120 @@ def run_reference(args):
     value = sum(vals) / len(vals)
     ms = STATE_BYTES_PER_LAUNCH * LAYERS / (value * 1e9) * 1e3
     line = {
-        "impl": "reference", "metric": "KDA decode state GB/s (16 slots x 34 layers, bf16 states)", "value": value, "unit": "GB/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 1: batched single-token decode, 16 slots per GPU, H=64, d=128, 34 layers, bf16-stored states",
-                   "layers": LAYERS, "sample": "the same step on the host cores, a bounded number of repetitions of 2 of the 34 layers"},
+        "config": headline_config(LAYERS),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "the reference's CPU path is Rust (no toolchain here): this is the C++ port in oracle/, all host threads",
+        "note": "oracle/_ref (the reference's own kernels) is absent: this is the reference's CPU formulation, the C++ port in oracle/ "
+                "(its own CPU code is Rust, no toolchain here), all host threads, a bounded number of repetitions of 2 of the 34 layers",
     }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference(args):
+    """The reference arm: the reference's own CUDA kernels (oracle/_ref, compiled unmodified from the reference tree) on
+    this GPU, entered through the symbol its forward calls for a decode step (glm53f_kda_chain_batch_bf16state,
+    crates/glm53f-forward/src/forward.rs:3672-3735) with the forward's argument values; same slots, heads, layers,
+    distinct states per layer, CUDA graph of the step's launches, event timing, and the same end-to-end loop (the
+    step's projection rows and gate rows from pinned host memory, the outputs back).  Every rank runs its own 16
+    slots, as in the product arm."""
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = False
+    pkg = importlib.import_module("glm53f-afd_b200")
+    ref = reference_library(pkg) if has_gpu else None
+    if ref is None:
+        return run_reference_cpu(args)
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    numa = bind_to_gpu_numa(torch, local_rank)
+    layers = args.layers
+    d = LayerAbi(torch, rank, SLOTS, 1, layers)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    _ms, graph = graph_ms(torch, lambda st: [d.chain(ref, l, st) for l in range(layers)], max(3, args.warmup))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(graph.replay, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    per_rank_bytes = layers * STATE_BYTES_PER_LAUNCH
+    value = world * per_rank_bytes / (ms_per_step * 1e-3) / 1e9
+    peak, peak_kind = peaks()
+    achieved = STATE_BYTES_PER_LAUNCH / (ms * 1e-3 / (args.steps * layers)) / 1e9
+    # end to end
+    layer_in, out_bytes = SLOTS * LAYER_IN_BYTES, SLOTS * OUT_STRIDE * 2
+    host_in = torch.empty(layers * layer_in, dtype=torch.uint8).pin_memory()
+    host_in.random_(0, 64)
+    dev_in = torch.empty(layers * layer_in, dtype=torch.uint8, device="cuda")
+    dev_in.copy_(host_in)
+    dev_out = torch.empty(layers * out_bytes, dtype=torch.uint8, device="cuda")
+    host_out = torch.empty(layers * out_bytes, dtype=torch.uint8).pin_memory()
+    in16, out16 = dev_in.view(torch.bfloat16), dev_out.view(torch.bfloat16)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    le = layer_in // 2
+
+    def launch_layer(l):
+        d.chain(ref, l, stream, p=d.at(in16, l * le), ag=(in16, l * le + SLOTS * P_STRIDE), out=d.at(out16, l * out_bytes // 2))
+
+    e2e_step = e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer)
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_value = world * per_rank_bytes / (e2e_ms * 1e-3) / 1e9
+    del d, graph, dev_in, dev_out
+    torch.cuda.empty_cache()
+    shapes = run_layer_abi(torch, ref, rank, layers, args.steps) if (rank == 0 and not args.no_verify) else None
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": headline_config(layers),
+        "reference_kind": "the reference's own CUDA kernels (crates/glm53f-kda/kernels/kda.cu, kda_prefill.cu) compiled unmodified for sm_100a, on this GPU",
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_kind, "kernel": "the reference's chain_kernel<bf16>"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": layers * SLOTS * LAYER_IN_BYTES,
+                "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES, "numa_node": numa},
+        "gpu_launches": args.steps * layers, "clocks": clocks, "layer_abi": shapes,
+    }
+    if not args.no_cpu:
+        v, cores, sample = cpu_decode_gbs(args.cpu_seconds)
+        line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
 
 
@@ -663,7 +1055,7 @@ def main():
     ap.add_argument("--no-proj", action="store_true", help="skip the projection GEMM leg")
     ap.add_argument("--no-marks", action="store_true", help="skip the state snapshot / restore leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4) and the packed-prefill leg (config 2)")
-    ap.add_argument("--prefill-check-heads", type=int, default=0, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens)")
+    ap.add_argument("--prefill-check-heads", type=int, default=-1, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens); default: 4 on one GPU, 0 under torchrun")
     ap.add_argument("--prefill-ws-chunks", type=int, default=256, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -679,11 +1071,14 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    numa = bind_to_gpu_numa(torch, local_rank)  # before any pinned allocation: staging is first touched on the GPU's node
     pkg = importlib.import_module("glm53f-afd_b200")
     core = importlib.import_module("glm53f-afd_b200.core")
     ffi = pkg.ffi
     lib = ffi.load()  # raises when the CUDA library is missing: there is no fallback
     layers = args.layers
+    if args.prefill_check_heads < 0:
+        args.prefill_check_heads = 4 if world == 1 else 0
 
     # ---- inputs: host-generated tokens (seeded, exact distributions), device-generated carried states N(0, 0.05)
     gen = torch.Generator(device="cuda").manual_seed(0x53454544 + 1 + rank)
@@ -784,33 +1179,15 @@ def main():
             at += nb
         staged.append(views)
     e2e_outs = [dev_out[l * out_bytes:(l + 1) * out_bytes].view(torch.int16) for l in range(layers)]
-    groups = [(a, min(a + 9, layers)) for a in range(0, layers, 9)]
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    def launch_layer(l):
+        q, k, v, g, bb = staged[l]
+        st = C.c_void_p(arena.data_ptr() + 2 * l * SLOTS * STATE_ELEMS)
+        rc = lib.glm53f_kda_core_decode_batch(HEADS, SLOTS, P(cu), P(q), P(k), P(v), P(g), P(bb), st, st, P(offs), 1, 0, None,
+                                              None, 1e-5, P(e2e_outs[l]), stream)
+        if rc != 0:
+            raise RuntimeError(f"decode launch failed: {rc}")
 
-    def e2e_step():
-        main = torch.cuda.current_stream()
-        copy_in.wait_stream(main)   # the previous step's launches have read the staging block
-        copy_out.wait_stream(main)
-        for a, b in groups:
-            with torch.cuda.stream(copy_in):
-                dev_in[a * layer_in:b * layer_in].copy_(host_in[a * layer_in:b * layer_in], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record()
-            main.wait_event(arrived)
-            for l in range(a, b):
-                q, k, v, g, bb = staged[l]
-                st = C.c_void_p(arena.data_ptr() + 2 * l * SLOTS * STATE_ELEMS)
-                rc = lib.glm53f_kda_core_decode_batch(HEADS, SLOTS, P(cu), P(q), P(k), P(v), P(g), P(bb), st, st, P(offs), 1, 0, None,
-                                                      None, 1e-5, P(e2e_outs[l]), stream)
-                if rc != 0:
-                    raise RuntimeError(f"decode launch failed: {rc}")
-            done = torch.cuda.Event()
-            done.record()
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(done)
-                host_out[a * out_bytes:b * out_bytes].copy_(dev_out[a * out_bytes:b * out_bytes], non_blocking=True)
-        main.wait_stream(copy_out)  # the step ends when its outputs are on the host
-
+    e2e_step = e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer)
     for _ in range(3):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps) / args.steps
@@ -824,6 +1201,9 @@ def main():
     packed = run_packed_prefill(torch, pkg, core, rank) if not args.no_verify else None
     marks = run_marks(torch, pkg, rank) if not args.no_marks else None
     projections = run_projections(torch, pkg, rank) if not args.no_proj else None
+    strong = run_decode_strong(torch, dist if world > 1 else None, lib, rank, world, layers, args.steps) if not args.no_verify else None
+    layer_abi = run_layer_abi(torch, lib, rank, layers, args.steps) if (rank == 0 and not args.no_verify) else None
+    assert core.device_status() == 0
     prefill = None
     if args.prefill_tokens > 0:
         prefill = run_prefill(torch, dist if world > 1 else None, pkg, core, rank, world, args.prefill_tokens, args.prefill_passes, args.prefill_ws_chunks, args.prefill_check_heads)
@@ -833,21 +1213,22 @@ def main():
             dist.destroy_process_group()
         return
     line = {
-        "metric": "KDA decode state GB/s (16 slots x 34 layers, bf16 states)",
+        "metric": METRIC,
         "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 1: batched single-token decode, 16 slots per GPU, H=64, d=128, 34 layers, bf16-stored states",
-                   "layers": layers, "l2": "inputs larger than L2: 1.06 GiB of states stream per step", "sharding": "by slot, no collective",
-                   "launch": "one CUDA graph of the step's 34 launches, replayed"},
+        "config": headline_config(layers),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": peak_kind, "frac_of_nominal_8tbs": achieved / 8000.0,
                      "algorithmic_bytes_per_launch": STATE_BYTES_PER_LAUNCH, "kernel": "recurrent_kernel<bf16, core>"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": layers * SLOTS * TOKEN_IN_BYTES,
-                "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES},
+                "d2h_bytes_per_step": layers * SLOTS * TOKEN_OUT_BYTES, "numa_node": numa,
+                "h2d_plus_d2h_gbs_per_rank": layers * SLOTS * (TOKEN_IN_BYTES + TOKEN_OUT_BYTES) / (e2e_ms * 1e-3) / 1e9},
         "gpu_launches": timed_launches,
         "clocks": clocks,
         "verify": verify,
+        "decode_strong": strong,
+        "layer_abi": layer_abi,
         "prefill_packed": packed,
         "marks": marks,
         "projections": projections,

@@ -84,6 +84,7 @@ struct WaitCtx {
     volatile uint32_t* progress;  // bumped by every role whenever it finishes a job
     volatile uint32_t* abort;     // set once by the first wait that gives up
     int* status;                  // the library's device status word (global memory)
+    uint64_t limit_ns = kWaitLimitNs;  // how long a wait goes without progress before it gives up
 };
 
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int code) {
@@ -99,7 +100,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
         if (now_p != seen) {
             seen = now_p;
             t0 = now;
-        } else if (now - t0 > kWaitLimitNs) {
+        } else if (now - t0 > ctx.limit_ns) {
             atomicCAS(ctx.status, 0, code);
             *ctx.abort = 1u;
             return false;
@@ -153,6 +154,21 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// The same barrier carrying a vote: true when `ok` holds on every one of the `threads` threads.  A role whose threads
+// may individually give up on a wait decides at such a barrier whether it goes on, so that either all of its threads
+// reach the role's next barrier or none does.
+__device__ __forceinline__ bool named_bar_all(int id, int threads, bool ok) {
+    uint32_t all;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %3, 0;\n\t"
+        "bar.red.and.pred q, %1, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(all)
+        : "r"(id), "r"(threads), "r"((uint32_t)ok)
+        : "memory");
+    return all != 0;
 }
 
 }  // namespace kda

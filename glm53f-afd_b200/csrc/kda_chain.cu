@@ -35,6 +35,10 @@
 namespace kda {
 
 __device__ int g_status = 0;
+// Host-side settings of the diagnostic hook glm53f_kda_debug_wait_test: the bound of the recurrent kernels' waits, and
+// a one-shot request that the next launch's block 0 leaves its first unit's state unfetched.
+static unsigned long long g_wait_limit_ns = kWaitLimitNs;
+static int g_skip_first_state = 0;
 
 int sm_count() {
     static int n = 0;
@@ -99,6 +103,8 @@ struct Params {
     float* b_save;
     long long kv_stride, b_stride;
     unsigned long long neg_zero2;  // two -0.0f: see mul2
+    unsigned long long wait_limit_ns;  // bound of every device-side wait (no progress for this long: give up)
+    int skip_first_state;  // diagnostic (glm53f_kda_debug_wait_test): block 0 does not fetch its first unit's state
 };
 
 // Raw-row slot layouts, byte offsets.
@@ -508,12 +514,15 @@ __device__ void mover_role(const Params& p, unsigned char* smem, uint64_t* bars,
     Ring st, raw;
     const bool copy0 = copies_state(p);
     UnitIter<MODE> units(p);
-    while (units.valid()) {
+    bool first = true;
+    for (; units.valid(); first = false) {
         const Unit un = units.take(p);
         if (un.rows == 0 && !copy0) continue;
         // The unit's state.
         if (!mbar_wait(&st_empty[st.idx], st.phase ^ 1u, ctx, kStatusWaitStateEmpty)) return;
-        {
+        if (p.skip_first_state && blockIdx.x == 0 && first) {
+            // Diagnostic launch: nothing is copied and nobody is told, so the recurrence's wait for this state runs out.
+        } else {
             unsigned char* dst = smem + L::oState + st.idx * L::kStateBytes;
             const unsigned char* src = reinterpret_cast<const unsigned char*>(p.state_in) + un.s_elem * (long long)sizeof(S);
             if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
@@ -597,6 +606,8 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
     const int warp = t >> 5, lane = t & 31;
     Ring raw, row;
     const bool copy0 = copies_state(p);
+    // Whether the role's threads meet at barriers in every row (the L2 norms go through shared scratch).
+    const bool syncs = MODE == kLayer || (MODE == kCore && (p.flags & GLM53F_KDA_CORE_L2NORM) != 0);
     UnitIter<MODE> units(p);
     while (units.valid()) {
         const Unit un = units.take(p);
@@ -604,13 +615,18 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
         float decay_rate = 0.0f;
         if constexpr (MODE == kLayer) decay_rate = expf(un.a_log);
         for (int r = 0; r < un.rows; ++r) {
-            if (!mbar_wait(&raw_full[raw.idx], raw.phase, ctx, kStatusWaitRawFull)) return;
-            if (!mbar_wait(&row_empty[row.idx], row.phase ^ 1u, ctx, kStatusWaitRowEmpty)) return;
+            // A thread that gave up on a wait may not simply leave when the role synchronises below: the threads that got
+            // through would wait for it at the role's barrier for ever.  There the decision is taken by all at that barrier.
+            bool ready = mbar_wait(&raw_full[raw.idx], raw.phase, ctx, kStatusWaitRawFull);
+            if (ready) ready = mbar_wait(&row_empty[row.idx], row.phase ^ 1u, ctx, kStatusWaitRowEmpty);
+            if (!syncs && !ready) return;
             const unsigned char* in = smem + L::oRaw + raw.idx * L::kRawBytes;
             Cooked& ck = *reinterpret_cast<Cooked*>(smem + L::oCooked + row.idx * sizeof(Cooked));
             const long long gr = un.row0 + r;
             bool normalise = true;
-            if constexpr (MODE == kLayer) {
+            if (!ready) {
+                // nothing to read: go to the vote
+            } else if constexpr (MODE == kLayer) {
                 // Short conv + SiLU, one bf16 rounding (kda.cu:129-142): channel c of q, k and v.
                 const uint16_t* x = reinterpret_cast<const uint16_t*>(in + RawLayer::X);
                 const uint16_t* w = reinterpret_cast<const uint16_t*>(in + RawLayer::W);
@@ -669,8 +685,8 @@ __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* ba
                     ck.beta = *reinterpret_cast<const float*>(in + RawReplay::B + (addr & 15));
                 }
             }
-            if (MODE != kReplay && normalise) {
-                named_bar_sync(1, kProThreads);
+            if (syncs) {
+                if (!named_bar_all(1, kProThreads, ready)) return;
                 if (warp == 0) l2norm_warp(scratch, ck.q, lane, true);
                 else if (warp == 1) l2norm_warp(scratch + DK, ck.k, lane, false);
                 named_bar_sync(2, kProThreads);  // scratch may be overwritten by the next row
@@ -839,7 +855,7 @@ __global__ void __launch_bounds__(kThreads, 1) recurrent_kernel(const __grid_con
     // grid of the stream has completed and flushed.  Both are no-ops for a launch without the attribute.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const WaitCtx ctx{ctl, ctl + 1, &g_status};
+    const WaitCtx ctx{ctl, ctl + 1, &g_status, p.wait_limit_ns};
     if (warp < kRecWarps) {
         recurrence_role<S, MODE>(p, smem, bars, ctx, warp, lane);
     } else if (warp < kRecWarps + kProWarps) {
@@ -877,6 +893,9 @@ int launch(const Params& p, cudaStream_t stream) {
     const unsigned grid = (unsigned)(p.units < sms ? p.units : sms);
     Params q = p;
     q.neg_zero2 = 0x8000000080000000ull;
+    q.wait_limit_ns = g_wait_limit_ns;
+    q.skip_first_state = g_skip_first_state;
+    g_skip_first_state = 0;
     // Launched with programmatic stream serialization: the kernel itself waits for its predecessors before its first
     // global access, so ordering is what a plain launch gives.  GLM53F_KDA_PDL=0 selects a plain launch.
     static const bool pdl = [] {
@@ -1160,4 +1179,11 @@ extern "C" int glm53f_kda_device_status(void) {
     if (e != cudaSuccess) return (int)e;
     if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof zero);
     return v;
+}
+
+extern "C" int glm53f_kda_debug_wait_test(uint64_t wait_limit_ns, int32_t skip_first_state) {
+    if (wait_limit_ns != 0 && (wait_limit_ns < 100000ull || wait_limit_ns > 60000000000ull)) return kda::kInvalid;  // 0.1 ms .. 60 s
+    kda::g_wait_limit_ns = wait_limit_ns == 0 ? kda::kWaitLimitNs : wait_limit_ns;
+    kda::g_skip_first_state = skip_first_state != 0 ? 1 : 0;
+    return 0;
 }

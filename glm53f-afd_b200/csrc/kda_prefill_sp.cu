@@ -918,9 +918,10 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
 // whose planner has handed every byte of HBM to weights, KV pages and state arenas, or a component called from a
 // region of its host where allocation is forbidden (an allocator lock held, a latency-critical loop), where cudaMalloc
 // would fail, fragment the plan or stall.  Such a caller cannot produce the workspace
-// glm53f_kda_core_prefill_varlen_ws asks for.  For them the library carries its own scratch: a fixed array in device
-// memory that exists as soon as the library is loaded on a GPU (and is held by every GPU that loads it until the
-// process exits), big enough for 64 workspace slots and the item counters.  Nothing in it has to start at zero: the
+// glm53f_kda_core_prefill_varlen_ws asks for.  For them the library carries its own scratch: a fixed array in the
+// library's device image (held by every GPU that has loaded the image until the process exits; with the runtime's
+// default lazy loading the image is placed in device memory at the first call below, which is why a host makes one
+// small set-up call per device before its memory plan is final), big enough for 64 workspace slots and the item counters.  Nothing in it has to start at zero: the
 // intra role writes every byte of a slot that the state role reads, and each call clears the counters itself.  All calls share the one array, so two calls in flight at once (two
 // streams, two threads) overwrite each other's slots; the caller serialises them.
 constexpr int kStaticSlots = 64;

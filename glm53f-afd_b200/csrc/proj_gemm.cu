@@ -337,8 +337,9 @@ bool matrix_map(CUtensorMap* tm, int* swapped, const void* base, long long k, lo
 }
 
 // K splits for a launch of few tiles (little n, deep k: o_proj at decode): the largest of 8, 4, 2 that divides the
-// k blocks into runs of at least four and still leaves every block of the launch resident at once.  Up to 128 rows
-// (one row tile) it is a function of (n, k, groups) alone, so a row's bits do not depend on `rows`.  Measured for
+// k blocks into runs of at least four and still leaves every block of a one-row-tile launch resident at once.  It is
+// a function of (n, k, groups) alone for every launch on row tiles of up to 128 rows (all launches of up to 512 rows), so
+// a row's bits do not depend on `rows` there.  Measured for
 // o_proj at 16 rows (32 tiles): no split 40.7 us, 2 splits 27.1, 4 splits 20.9, 8 splits (two waves of clusters) 24.7.
 int pick_ksplit(long long tiles, int kblocks, long long resident) {
     for (int s = 8; s >= 2; s >>= 1)
@@ -379,7 +380,9 @@ int launch_gemm(GemmParams& p, const void* x, long long ldx, long long x_gstride
     p.tiles = (long long)groups * p.n_tiles * p.r_tiles;
     const long long cap = (long long)sm_count() * Cfg<NR, false>::kBlocksPerSm;
     if constexpr (NR <= 128) {
-        const int ks = pick_ksplit(p.tiles, p.kblocks, sm_count());  // clusters were measured at one block per SM
+        // The split is chosen for ONE row tile, whatever the launch's row count: a row's bits then depend on
+        // (groups, n, k) only.  More row tiles than fit at once are walked by the same clusters.
+        const int ks = pick_ksplit((long long)groups * p.n_tiles, p.kblocks, sm_count());  // clusters were measured at one block per SM
         const long long fit = cap / ks;
         const long long clusters = p.tiles < fit ? p.tiles : fit;
         if (ks == 8) return launch_one<NR, 8>(p, clusters, stream);

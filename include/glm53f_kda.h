@@ -326,13 +326,17 @@ int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const
  * engine whose memory planner has already given every byte of HBM away before the first request, or code that runs
  * where an allocation would fail or stall its host (under an allocator lock, in a latency-critical loop).  It takes
  * no workspace: it runs on a fixed array of 6,848,768 bytes (64 workspace slots and the item counters) that lives in
- * the library's device image, so every GPU on which the library is loaded holds that much until the process exits.
+ * the library's device image, so every GPU that has loaded that image holds that much until the process exits.
  *   - Limit: heads * batch <= 64 (at least one chunk per chain must fit); more is rejected with status 1
  *     (cudaErrorInvalidValue) before anything is enqueued.  A launch covers at most 64 / (heads * batch) chunks of
  *     every sequence, so the entry point suits few chains: one sequence on one GPU's shard of heads.
- *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with that device
- *     current) and remembers it; make that first call outside any stream capture.
- *   - The call allocates and frees nothing.
+ *   - The first call on each device is a set-up call: it looks the array's device address up (cudaGetSymbolAddress,
+ *     with that device current) and remembers it.  Under the CUDA runtime's default lazy module loading this is also
+ *     the moment the library's device image -- the array included -- is placed in device memory, so that one call can
+ *     fail with cudaErrorMemoryAllocation on a GPU that is already full.  Make it once per device, early: on any small
+ *     shape (one chain of one row will do), before the host's memory plan takes the rest of HBM and outside any
+ *     stream capture (or run the process with CUDA_MODULE_LOADING=EAGER, which loads the image when the library is).
+ *   - After that set-up call a call allocates and frees nothing.
  *   - All calls on a device share the one array.  Its contents are scratch (every slot is written before it is read,
  *     nothing needs clearing, nothing survives a call), so calls that overlap on the GPU -- different streams,
  *     or different processes' threads on one context -- race; keep calls on one device in stream order.
@@ -349,6 +353,17 @@ int glm53f_kda_core_prefill_varlen_static(int32_t heads, int32_t batch, const in
  * bounded wait ran out (the kernel then returned early instead of spinning).  Reads and clears it;
  * synchronises the device.  Not in the reference (its kernels have no device-side waits). */
 int glm53f_kda_device_status(void);
+
+/* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The decode / verify / commit
+ * kernels bound every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
+ * status code (101-108, which wait), makes its other waits return, and the kernel ends; the context stays usable and
+ * glm53f_kda_device_status reports the code.
+ *   wait_limit_ns     the limit for the launches that follow, 100,000 .. 60,000,000,000 ns; 0 restores the default
+ *   skip_first_state  != 0: in the NEXT decode / verify / commit launch only, block 0 does not fetch its first unit's
+ *                     state and tells nobody, so that this unit's wait runs out.  Nothing is in flight and nothing
+ *                     faults; the launch's other units complete, that unit's state and outputs are not written.
+ * Host-side settings, not thread safe; returns 0, or 1 for a limit outside the range. */
+int glm53f_kda_debug_wait_test(uint64_t wait_limit_ns, int32_t skip_first_state);
 
 #ifdef __cplusplus
 }

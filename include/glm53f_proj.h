@@ -27,7 +27,9 @@ typedef struct CUstream_st* glm53f_stream_t; /* cudaStream_t; NULL = the legacy 
 /* out[g][m][o] = sum_k x[g][m][k] * w[g][o][k] for groups g < groups, rows m < rows, outputs o < n:
  * x at x + g * x_gstride + m * ldx, w row o at w + g * w_gstride + o * ldw, out at out + g * o_gstride + m * ldo
  * (strides in elements; x and w bf16; out bf16, or f32 when out_f32 != 0).  Products are exact, sums accumulate in
- * f32 in k order; a row's result depends on that row and on (n, k) only, never on `rows`.
+ * f32 in k order; in launches of up to 512 rows a row's result depends on that row and on (groups, n, k) only, never on
+ * `rows` (bit for bit: the tile shape's accumulation and the K split are chosen from (groups, n, k)); larger launches
+ * use wider tiles without a K split and agree with them to the order of the f32 sums.
  *
  * n % 8 == 0; k % 64 == 0; ldx, ldw, x_gstride, w_gstride % 8 == 0; ldx, ldw >= k; ldo >= n; x and w 16-byte
  * aligned.  The group strides are read only when groups > 1.  rows == 0 launches nothing.  Returns 0, 1

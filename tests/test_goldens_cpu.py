@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-REFERENCE_GOLDENS = os.path.join(os.environ.get("GLM53F_REFERENCE", "/root/reference"), "oracle", "goldens")
+REFERENCE_GOLDENS = os.path.join(os.environ.get("GLM53F_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"), "oracle", "goldens")
 
 
 @pytest.fixture(scope="module")

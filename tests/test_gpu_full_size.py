@@ -1,5 +1,9 @@
 """The benchmark configurations at their full sizes, through properties that need no CPU pass over the whole input.
 
+  configuration 0   one sequence of 2,048 tokens, 64 heads, from a zero state (the host generator's bytes): the
+                    single-pass kernel and the workspace form, every head, against the oracle's FP32 recurrence
+                    (which must itself agree with the oracle's chunk-64 form within the reference's own 2e-5), with
+                    the task's tolerances (the reference's analogue: crates/glm53f-kda/tests/gpu_prefill.rs:250-279).
   configuration 2   8,192 rows of packed variable-length sequences, 64 heads: one call equals two calls that cut every
                     sequence at a chunk boundary and carry the state (bit for bit); the workspace form equals itself
                     for two workspace sizes (bit for bit) and the single-pass kernel to rounding; two heads of one
@@ -45,6 +49,40 @@ def tokens(rows, heads, seed):
     lg = torch.nn.functional.logsigmoid(torch.randn(n * DK, device="cuda", generator=g) + 3.0)
     beta = torch.sigmoid(torch.randn(n, device="cuda", generator=g))
     return q, k, v, lg, beta
+
+
+def test_config0_every_head_against_the_oracle(env, oracle):
+    pkg, core = env
+    o = oracle
+    t, per = 2048, H * DV * DK
+    q, k, v, g, beta = pkg.synth.tokens(0, 0, t, H)
+    s0 = np.zeros(per, np.float32)
+    y, s_ref = o.core_forward(H, q, k, v, g, beta, s0, form="recurrent", threads=16)
+    # the reference's two formulations agree on a sample of heads (its own bound), so either is the oracle
+    hs = [0, 21, 42, 63]
+    sub = lambda a, w: np.ascontiguousarray(a.reshape(t, H, w)[:, hs]).reshape(-1)
+    args = (len(hs), sub(q, DK), sub(k, DK), sub(v, DV), sub(g, DK), sub(beta, 1), np.zeros(len(hs) * DV * DK, np.float32))
+    y_r, s_r = o.core_forward(*args, form="recurrent", threads=4)
+    y_c, s_c = o.core_forward(*args, form="chunked", chunk=64, threads=4)
+    assert np.max(np.abs(y_c - y_r)) / np.max(np.abs(y_r)) < 2e-5 and np.max(np.abs(s_c - s_r)) / np.max(np.abs(s_r)) < 2e-5
+    assert np.array_equal(y_r, sub(y, DV))
+    up16 = lambda b: torch.from_numpy(np.ascontiguousarray(b).view(np.int16).copy()).cuda()
+    dq, dk, dv, dg, db = up16(q), up16(k), up16(v), torch.from_numpy(g).cuda(), torch.from_numpy(beta).cuda()
+    cu, off = torch.tensor([0, t], dtype=torch.int32, device="cuda"), torch.zeros(1, dtype=torch.int64, device="cuda")
+    for ws_chunks in (None, 8):
+        st, out = torch.zeros(per, device="cuda"), torch.zeros(t * H * DV, dtype=torch.bfloat16, device="cuda")
+        ws = None if ws_chunks is None else torch.empty(core.prefill_workspace_bytes(H, 1, ws_chunks), dtype=torch.uint8, device="cuda")
+        core.prefill_varlen(H, t, cu, t, dq, dk, dv, dg, db, st, off, out=out, workspace=ws)
+        torch.cuda.synchronize()
+        assert core.device_status() == 0
+        got, s_got = out.float().cpu().numpy(), st.cpu().numpy()
+        assert np.max(np.abs(got - y)) <= 2e-2, ws_chunks
+        assert np.linalg.norm(got - y) / np.linalg.norm(y) <= 5e-3, ws_chunks
+        assert np.linalg.norm(s_got - s_ref) / np.linalg.norm(s_ref) <= 1e-3, ws_chunks
+        # per head as well: no head may hide behind the others
+        for h in range(H):
+            e = np.linalg.norm(s_got.reshape(H, -1)[h] - s_ref.reshape(H, -1)[h]) / np.linalg.norm(s_ref.reshape(H, -1)[h])
+            assert e <= 1e-3, (ws_chunks, h, e)
 
 
 def test_config2_packed_prefill_properties(env, oracle):

@@ -167,3 +167,18 @@ def test_wide_weight_mid_range_rows(proj):
         got = run(proj, x, w, rows, True, ldo=n + 8, pad=16)
         check(got, x, w, True)
         assert (got[:, :64].view(np.uint32) == small.view(np.uint32)).all(), rows
+
+
+def test_split_k_shape_is_row_count_independent(proj):
+    """o_proj's shape (32 feature tiles, 128 k blocks: the K range of a tile is split over a cluster) at 129..512
+    rows: the split is chosen from (groups, n, k) alone, so the rows a 64-row launch also computes keep its bits."""
+    rng = go.Rng(29)
+    n, k, R = 4096, 8192, 512
+    w = rng.bf16s(n * k, 0.02).reshape(1, n, k)
+    x = rng.bf16s(R * k, 1.0).reshape(1, R, k)
+    small = run(proj, x, w, 64, True)
+    check(small, x, w, True)
+    for rows in (129, 256, 384, 512):
+        got = run(proj, x, w, rows, True, ldo=n + 8, pad=16)
+        assert (got[:, :64].view(np.uint32) == small.view(np.uint32)).all(), rows
+    check(got, x, w, True)

@@ -40,9 +40,10 @@ STATE_ELEMS = HEADS * DK * DK                        # one slot, one layer
 STATE_BYTES_PER_LAUNCH = 2 * SLOTS * STATE_ELEMS * 2  # bf16 read + write = 64 MiB
 TOKEN_IN_BYTES = HEADS * DK * (2 + 2 + 2 + 4) + HEADS * 4  # q, k, v bf16 + g f32 + beta f32 per token
 TOKEN_OUT_BYTES = HEADS * DK * 2
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised
-# under profiles/ (a single captured launch: the 32 MiB it writes stay in the 126 MB L2, so this is mostly the reads).
-NCU_DRAM_BYTES_PER_LAUNCH = 34_925_824 + 117_504
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel: the mean over 16 consecutive launches
+# of an 8-layer step (256 MiB of distinct states, caches left as they are between launches, so that one launch's
+# writes are evicted during the next ones as in the timed run); summarised under profiles/.
+NCU_DRAM_BYTES_PER_LAUNCH = 34_876_112 + 32_331_792
 # The same for the prefill kernel: 601 MB per captured launch of 2,048 (chain, chunk) items = 32 chunks of all 64 heads.
 NCU_PREFILL_DRAM_BYTES_PER_TOKEN = (393_953_280 + 207_395_072) // (32 * 64)
 
@@ -180,6 +181,7 @@ class LayerAbi:
 
 def graph_ms(torch, fn, reps, warm=3):
     """`fn(stream)` captured once in a CUDA graph on a side stream, replayed `reps` times between events."""
+    torch.cuda.synchronize()  # the inputs (metadata arrays included) were written on the current stream
     side = torch.cuda.Stream()
     st = C.c_void_p(side.cuda_stream)
     with torch.cuda.stream(side):

@@ -101,12 +101,28 @@ static_assert(kSmemSp <= 232448, "shared memory budget");
 // E_last, M, W, U), in the un-swizzled cell layout the state role reads, so no result tile lives in shared memory.
 // =====================================================================================================================
 constexpr int kGroupThreads = 256, kGroups = 2;
-constexpr int gQ = 0, gK = kTile, gV = 2 * kTile, gG = 3 * kTile, gKi = gG + 4 * kBox;  // Q/Qg | K/Kg | V | g/E | Kinv
-constexpr int gT = gG, gL = gG + CH * LS * 4, gP = gL + CH * LS * 4, gTp = gL;            // inverse scratch over E | Kinv; T' (hi | lo box) over L
-static_assert(gTp % 1024 == 0, "swizzled tiles are 1024-byte aligned");
-constexpr int gBeta = gKi + kTile, gEgl = gBeta + CH * 4, gScan = gEgl + 128 * 4, gBars = gScan + 2 * 128 * 4, gItem = gBars + 32;
-constexpr int kGroupBytes = 101376;
-static_assert(gP + 32 * 32 * 4 <= gKi + kTile && gTp + kTile <= gP && gItem + 16 <= kGroupBytes && kGroupBytes % 1024 == 0, "group map");
+// Decay range.  L and M hold exp(G_i - G_j) for every pair of rows j <= i of a chunk, and a tensor-core product can
+// only form it as (row factor) x (column factor).  With the model's gate bound (log decay down to -5.8 per row, -371
+// per chunk) neither exp(G) nor exp(-G) is representable, so the pair is split at a reference row r between j and i:
+// exp(G_i - G_r) exp(G_r - G_j).  Rows are grouped in blocks of 16 and the reference of row block I is its middle row
+// (16 I + 8).  The row side k_i exp(G_i - Gm_I) then stays within e^+-47; the column side for row block I is
+// k_j exp(Gm_I - G_j) for every j below the end of block I: at most e^47 inside the block and at most 1 (vanishing
+// harmlessly where the true product vanishes) in earlier blocks.  It depends on I, so there are four column-side
+// tiles of 16, 32, 48 and 64 rows, and L^T, M^T are formed block column by block column (N = 16) with the column side
+// as the M operand: rows past a tile's end produce entries above the diagonal, which are discarded.
+constexpr int kKcBytes = 2 * 128 * (16 + 32 + 48 + 64);  // the four column-side tiles, boxes of R x 128 bytes
+// Tile I starts at pf::kc_tile(I).  Byte offset inside tile I (R = 16 (I + 1) rows per box) of the 16-byte piece `piece` (0..15) of row r.
+__device__ __forceinline__ int kc_piece(int I, int r, int piece) {
+    return kc_tile(I) + (piece >> 3) * (I + 1) * 2048 + r * 128 + (((piece & 7) ^ (r & 7)) << 4);
+}
+constexpr int gQ = 0, gK = kTile, gV = 2 * kTile, gKb = 3 * kTile, gG = 4 * kTile, gKc = gG;  // Q/Qgb | K/Kg | V | Kgb | g/G, then the column-side tiles
+constexpr int gT = gKc, gL = gT + CH * LS * 4, gP = gL + CH * LS * 4, gTp = gL;              // inverse scratch over the column-side tiles; T' (hi | lo box) over L
+static_assert(gTp % 1024 == 0 && gKc % 1024 == 0, "swizzled tiles are 1024-byte aligned");
+// Per-block decay factors, 128 channels each: E0[J] = exp(Gm_J), EL[J] = exp(G_last - Gm_J), F[I(I-1)/2 + J] =
+// exp(Gm_I - Gm_J) for I > J.  The scan's totals use the first two rows before the tables are written.
+constexpr int gTab = gKc + kKcBytes, gBeta = gTab + kTabs * 512, gBars = gBeta + CH * 4, gItem = gBars + 32;
+constexpr int kGroupBytes = 114688;
+static_assert(4 * kBox <= kKcBytes && gP + 32 * 32 * 4 <= gKc + kKcBytes && gTp + kTile <= gP && gItem + 16 <= kGroupBytes && kGroupBytes % 1024 == 0, "group map");
 static_assert(kGroups * kGroupBytes <= oCtl, "two groups must fit below the block's control words");
 constexpr uint32_t gcL = 0, gcM = 64, gcW = 0, gcU = 128, kGroupCols = 256;
 
@@ -117,11 +133,9 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
     const uint32_t tm = tm_block + G * kGroupCols;
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(gs + gBars);
     uint64_t* bar_mma = bar_raw + 1;
-    uint64_t* bar_mma2 = bar_raw + 2;
     uint64_t* bar_free = bar_raw + 3;
     volatile int* item_slot = reinterpret_cast<volatile int*>(gs + gItem);
     float* betas = reinterpret_cast<float*>(gs + gBeta);
-    float* egl = reinterpret_cast<float*>(gs + gEgl);
     const int gt = threadIdx.x - G * kGroupThreads, gw = gt >> 5, lane = gt & 31;
     const int quad = gw & 3, cg = gw >> 2;  // a warp reaches tensor-memory lanes 32 * (warp % 4)..; cg picks a half of the columns
     const int lane_row64 = quad * 16 + lane;
@@ -140,7 +154,7 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
             atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
         }
     };
-    uint32_t raw_phase = 0, mma_phase = 0, mma2_phase = 0;
+    uint32_t raw_phase = 0, mma_phase = 0;
     auto mma_wait = [&](uint64_t* bar, uint32_t& phase) -> bool {
         if (!mbar_wait(bar, phase, ctx, kStatusWaitPrefill)) return false;
         phase ^= 1u;
@@ -156,13 +170,13 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
         const int chain = item % chains, jj = item / chains;
         unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, jj);
 
-        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging boxes ----------------------------
+        // ---- 1. cumulative log decay G per key channel, left in the staging boxes in place of g ---------------------------
         {
             const int part = gt >> 7, d = gt & 127;
             // Row r of this thread's channel: box d / 32, piece (d % 32) / 4 swizzled by r & 7, float d % 4.
             unsigned char* col = gs + gG + (d >> 5) * kBox + part * 32 * 128 + (d & 3) * 4;
             const int pc = (d >> 2) & 7;
-            float* totals = reinterpret_cast<float*>(gs + gScan);
+            float* totals = reinterpret_cast<float*>(gs + gTab);
             float run[32], acc = 0.0f;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
@@ -172,114 +186,141 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
             totals[part * 128 + d] = acc;
             group_sync();
             const float base = part ? totals[d] : 0.0f;
-            float e = 1.0f;
 #pragma unroll
-            for (int r = 0; r < 32; ++r) {
-                e = __expf(base + run[r]);
-                *reinterpret_cast<float*>(col + r * 128 + ((pc ^ (r & 7)) << 4)) = e;
-            }
-            if (part == 1) {
-                egl[d] = e;
-                if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
-            }
+            for (int r = 0; r < 32; ++r) *reinterpret_cast<float*>(col + r * 128 + ((pc ^ (r & 7)) << 4)) = base + run[r];
         }
         group_sync();
 
-        // ---- 2a. from k: Kg = K E in place, Kinv = K / E, Kdec = K E_last / E as bf16 hi + lo out to the workspace -------
+        // ---- 2. a = exp(G - Gm) of this thread's row and 32 channels into registers; the per-block factor tables -----------
+        const int r = gt & 63, cq = gt >> 6, J = r >> 4;
+        float a[32];
         {
-            const int r = gt & 63, cq = gt >> 6;
+            const int rm = (r & 48) | 8;
+            float amax = 0.0f;
+#pragma unroll
+            for (int pp = 0; pp < 8; ++pp) {
+                const float4 x = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, cq * 8 + pp));
+                const float4 m = *reinterpret_cast<const float4*>(gs + gG + box_piece(rm, cq * 8 + pp));
+                a[pp * 4 + 0] = __expf(x.x - m.x);
+                a[pp * 4 + 1] = __expf(x.y - m.y);
+                a[pp * 4 + 2] = __expf(x.z - m.z);
+                a[pp * 4 + 3] = __expf(x.w - m.w);
+                amax = fmaxf(fmaxf(fmaxf(a[pp * 4], a[pp * 4 + 1]), fmaxf(a[pp * 4 + 2], a[pp * 4 + 3])), amax);
+            }
+            // Eight rows of decay must stay below e^85: per-row log decays below about -10.6 (or positive ones) do not.
+            if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            const int half = gt >> 7, d = gt & 127;
+            const unsigned char* colg = gs + gG + (d >> 5) * kBox + (d & 3) * 4;
+            const int pc = (d >> 2) & 7;
+            auto G_at = [&](int row) { return *reinterpret_cast<const float*>(colg + row * 128 + ((pc ^ (row & 7)) << 4)); };
+            const float gm0 = G_at(8), gm1 = G_at(24), gm2 = G_at(40), gm3 = G_at(56), gl = G_at(63);
+            float* tab = reinterpret_cast<float*>(gs + gTab) + d;
+            if (half == 0) {
+                tab[(tE0 + 0) * 128] = __expf(gm0); tab[(tE0 + 1) * 128] = __expf(gm1); tab[(tE0 + 2) * 128] = __expf(gm2); tab[(tE0 + 3) * 128] = __expf(gm3);
+                tab[(tEL + 0) * 128] = __expf(gl - gm0); tab[(tEL + 1) * 128] = __expf(gl - gm1);
+                tab[(tEL + 2) * 128] = __expf(gl - gm2); tab[(tEL + 3) * 128] = __expf(gl - gm3);
+            } else {
+                tab[(tF + 0) * 128] = __expf(gm1 - gm0);
+                tab[(tF + 1) * 128] = __expf(gm2 - gm0); tab[(tF + 2) * 128] = __expf(gm2 - gm1);
+                tab[(tF + 3) * 128] = __expf(gm3 - gm0); tab[(tF + 4) * 128] = __expf(gm3 - gm1); tab[(tF + 5) * 128] = __expf(gm3 - gm2);
+                reinterpret_cast<float*>(slot + wEgl)[d] = __expf(gl);
+            }
+        }
+        group_sync();  // the tables are complete; nobody reads the staged G any more, so the column-side tiles may go over it
+
+        // ---- 3. operand tiles.  Row sides Kgb = K a, Qgb = Q a (over Q); Kg = K exp(G) (over K) for W; Qg = Q exp(G), Kdec =
+        // K exp(G_last - G) as bf16 hi + lo out to the workspace; column sides K exp(Gm_I - G) into the tiles I >= J.
+        {
+            const float* tabs = reinterpret_cast<const float*>(gs + gTab);
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 const int c = cq * 4 + cc;
                 const uint4 k8 = *reinterpret_cast<const uint4*>(gs + gK + box_piece(r, c));
-                const float4 e0 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c));
-                const float4 e1 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c + 1));
-                const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
-                const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
-                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-                const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
-                uint32_t kg[4], ki[4], dh[4], dl[4];
+                const uint4 q8 = *reinterpret_cast<const uint4*>(gs + gQ + box_piece(r, c));
+                const float4 e0a = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8), e0b = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+                const float4 ela = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8), elb = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8 + 4);
+                const float E0[8] = {e0a.x, e0a.y, e0a.z, e0a.w, e0b.x, e0b.y, e0b.z, e0b.w};
+                const float EL[8] = {ela.x, ela.y, ela.z, ela.w, elb.x, elb.y, elb.z, elb.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
+                uint32_t kg[4], kgb[4], qg[4], qgb[4], kcd[4], dh[4], dl[4];
+                float kc[8];  // K exp(Gm_J - G): the column side inside the row's own block
 #pragma unroll
                 for (int u2 = 0; u2 < 4; ++u2) {
                     const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
-                    float a[2], ci[2], hi[2], lo[2];
+                    const float qf[2] = {__uint_as_float(qw[u2] << 16), __uint_as_float(qw[u2] & 0xffff0000u)};
+                    float v_kg[2], v_kgb[2], v_qg[2], v_qgb[2], hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const float e = E[2 * u2 + u], einv = __fdividef(1.0f, e);
-                        a[u] = kf[u] * e;
-                        ci[u] = kf[u] * einv;
-                        tc::split_bf16(kf[u] * (EL[2 * u2 + u] * einv), hi[u], lo[u]);
+                        const float av = a[cc * 8 + 2 * u2 + u], inva = __fdividef(1.0f, av), e = av * E0[2 * u2 + u];
+                        v_kgb[u] = kf[u] * av;
+                        v_qgb[u] = qf[u] * av;
+                        v_kg[u] = kf[u] * e;
+                        v_qg[u] = qf[u] * e;
+                        kc[2 * u2 + u] = kf[u] * inva;
+                        tc::split_bf16(kc[2 * u2 + u] * EL[2 * u2 + u], hi[u], lo[u]);
                     }
-                    kg[u2] = tc::bf16x2(a[0], a[1]);
-                    ki[u2] = tc::bf16x2(ci[0], ci[1]);
+                    kg[u2] = tc::bf16x2(v_kg[0], v_kg[1]);
+                    kgb[u2] = tc::bf16x2(v_kgb[0], v_kgb[1]);
+                    qg[u2] = tc::bf16x2(v_qg[0], v_qg[1]);
+                    qgb[u2] = tc::bf16x2(v_qgb[0], v_qgb[1]);
+                    kcd[u2] = tc::bf16x2(kc[2 * u2], kc[2 * u2 + 1]);
                     dh[u2] = tc::bf16x2(hi[0], hi[1]);
                     dl[u2] = tc::bf16x2(lo[0], lo[1]);
                 }
                 *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
-                *reinterpret_cast<uint4*>(gs + gKi + box_piece(r, c)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(gs + gKb + box_piece(r, c)) = make_uint4(kgb[0], kgb[1], kgb[2], kgb[3]);
+                *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
+                *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
                 *reinterpret_cast<uint4*>(cell(slot + wKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
                 *reinterpret_cast<uint4*>(cell(slot + wKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+                *reinterpret_cast<uint4*>(gs + gKc + kc_piece(J, r, c)) = make_uint4(kcd[0], kcd[1], kcd[2], kcd[3]);
+                for (int I = J + 1; I < 4; ++I) {  // the later row blocks see this row through exp(Gm_I - Gm_J) <= 1
+                    const float* f = tabs + (tF + I * (I - 1) / 2 + J) * 128 + c * 8;
+                    const float4 fa = *reinterpret_cast<const float4*>(f), fb = *reinterpret_cast<const float4*>(f + 4);
+                    *reinterpret_cast<uint4*>(gs + gKc + kc_piece(I, r, c)) =
+                        make_uint4(tc::bf16x2(kc[0] * fa.x, kc[1] * fa.y), tc::bf16x2(kc[2] * fa.z, kc[3] * fa.w),
+                                   tc::bf16x2(kc[4] * fb.x, kc[5] * fb.y), tc::bf16x2(kc[6] * fb.z, kc[7] * fb.w));
+                }
             }
         }
         publish();
-        // ---- 3a. L = Kg Kinv^T starts while Qg is built -----------------------------------------------------------------
+        // ---- 3b. L^T and M^T, one block column of 16 rows i at a time: [64 j x 16 i] = column side (tile I) x row side (block I)^T ----
         mma_issue(bar_mma, [&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + gcL, tc::desc_sw128_kmajor(gs + gK, CH, k0), tc::desc_sw128_kmajor(gs + gKi, CH, k0), id, k0 > 0);
-        });
-        // ---- 2b. Qg = Q E in place and out to the workspace; E_last out ----------------------------------------------------
-        {
-            const int r = gt & 63, cq = gt >> 6;
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const int c = cq * 4 + cc;
-                const uint4 q8 = *reinterpret_cast<const uint4*>(gs + gQ + box_piece(r, c));
-                const float4 e0 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c));
-                const float4 e1 = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, 2 * c + 1));
-                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-                const uint32_t qw[4] = {q8.x, q8.y, q8.z, q8.w};
-                uint32_t qg[4];
-#pragma unroll
-                for (int u2 = 0; u2 < 4; ++u2)
-                    qg[u2] = tc::bf16x2(__uint_as_float(qw[u2] << 16) * E[2 * u2], __uint_as_float(qw[u2] & 0xffff0000u) * E[2 * u2 + 1]);
-                const uint4 o = make_uint4(qg[0], qg[1], qg[2], qg[3]);
-                *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = o;
-                *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = o;
+            constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
+            for (int I = 0; I < 4; ++I) {
+                const unsigned char* kct = gs + gKc + kc_tile(I);
+                const int R = 16 * (I + 1);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + gcL + 16 * I, tc::desc_sw128_kmajor(kct, R, k0), tc::desc_sw128_kmajor(gs + gKb + I * 2048, CH, k0), id, k0 > 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + gcM + 16 * I, tc::desc_sw128_kmajor(kct, R, k0), tc::desc_sw128_kmajor(gs + gQ + I * 2048, CH, k0), id, k0 > 0);
             }
-            if (gt < 32) *reinterpret_cast<float4*>(slot + wEgl + gt * 16) = *reinterpret_cast<const float4*>(egl + gt * 4);
-        }
-        publish();
-        // ---- 3b. M = Qg Kinv^T -------------------------------------------------------------------------------------------
-        mma_issue(bar_mma2, [&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + gcM, tc::desc_sw128_kmajor(gs + gQ, CH, k0), tc::desc_sw128_kmajor(gs + gKi, CH, k0), id, k0 > 0);
         });
         if (!mma_wait(bar_mma, mma_phase)) break;
-        if (!mma_wait(bar_mma2, mma2_phase)) break;
 
-        // ---- 4. L (FP32, strictly lower, times beta_i) into the scratch; M (bf16 cells, lower with the diagonal) out -------
+        // ---- 4. from L^T and M^T (lane = column j, tensor-memory column = row i): L (FP32, strictly lower, times beta_i) into
+        // the scratch; M (lower with the diagonal) out as bf16 cells of eight consecutive rows i, [8 cells][64 columns j] ----------
         {
-            const int i = lane_row64;
+            const int j = lane_row64;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                uint32_t r[32];
-                tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg == 0 ? gcL : gcM) + half * 32), r);
+                uint32_t rr[32];
+                tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg == 0 ? gcL : gcM) + half * 32), rr);
                 tc::tmem_ld_wait();
                 if (lane < 16) {
                     if (cg == 0) {
-                        float* Lr = reinterpret_cast<float*>(gs + gL) + i * LS + half * 32;
-                        const float bi = betas[i];
+                        float* Lc = reinterpret_cast<float*>(gs + gL) + j;
 #pragma unroll
-                        for (int j2 = 0; j2 < 32; ++j2) Lr[j2] = half * 32 + j2 < i ? bi * __uint_as_float(r[j2]) : 0.0f;
+                        for (int i2 = 0; i2 < 32; ++i2) {
+                            const int i = half * 32 + i2;
+                            Lc[i * LS] = i > j ? betas[i] * __uint_as_float(rr[i2]) : 0.0f;
+                        }
                     } else {
 #pragma unroll
-                        for (int j2 = 0; j2 < 32; ++j2)
-                            if (half * 32 + j2 > i) r[j2] = 0u;
+                        for (int i2 = 0; i2 < 32; ++i2)
+                            if (half * 32 + i2 < j) rr[i2] = 0u;
 #pragma unroll
-                        for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(slot + wMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
+                        for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(slot + wMm, CH, half * 4 + cc, j)) = pack8(rr + cc * 8);
                     }
                 }
             }
@@ -446,7 +487,7 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
     if (tid == 0) {
         for (int g = 0; g < kGroups; ++g) {
             uint64_t* b = reinterpret_cast<uint64_t*>(smem + g * kGroupBytes + gBars);
-            for (int i = 0; i < 4; ++i) mbar_init(b + i, 1);  // raw, mma, mma2, free
+            for (int i = 0; i < 4; ++i) mbar_init(b + i, 1);  // raw, mma, (spare), free
         }
         mbar_init_fence();
     }
@@ -668,11 +709,11 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         // ---- O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------
         if (!mbar_wait(&full[2], par, ctx, kStatusWaitPrefill)) { alive = false; break; }
         mma_issue([&] {
-            constexpr uint32_t id = tc::idesc_bf16(64, NV, 0, 1, 0), ids = tc::idesc_bf16(128, NV, 1, 1, 0);
+            constexpr uint32_t idm = tc::idesc_bf16(64, NV, 1, 1, 0), ids = tc::idesc_bf16(128, NV, 1, 1, 0);  // M arrives with its rows contiguous
             const unsigned char* kdhi = smem + sSlot + wKdHi;
             const unsigned char* kdlo = smem + sSlot + wKdLo;
             for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), id, true);
+                tc::mma_bf16(tm + tO, tc::desc_mnmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), idm, true);
             for (int k0 = 0; k0 < CH; k0 += 16)
                 tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
             for (int k0 = 0; k0 < CH; k0 += 16)

@@ -171,13 +171,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
         raw_phase ^= 1u;
 
-        // ---- 1. cumulative log decay per key channel, E = exp(G) left in the staging buffer --------------------------
-        // Thread (part, d): rows 16*part .. 16*part+15 of channel d; the parts' totals are combined through shared
-        // memory, so the scan is 16 steps deep instead of 64.
+        // ---- 1. per key channel: the cumulative log decay G, a = exp(G - Gm) of every row relative to the middle row of
+        // its block of 16 (left in the staging buffer in place of g), and the per-block factor tables.
+        // Thread (part, d): rows 16*part .. 16*part+15 of channel d, which is exactly row block J = part.
         {
             const int part = tid >> 7, d = tid & 127;
             float* col = reinterpret_cast<float*>(smem + oRawG + (part * 16) * RS32) + d;
             float* totals = reinterpret_cast<float*>(smem + oScan);
+            float* tab = reinterpret_cast<float*>(smem + oTab) + d;
             float loc[16], G = 0.0f;
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
@@ -185,98 +186,152 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 loc[r] = G;
             }
             totals[part * 128 + d] = G;
-            compute_sync();
-            float base = 0.0f;
-            for (int q2 = 0; q2 < part; ++q2) base += totals[q2 * 128 + d];
-            float e = 1.0f;
+            tab[part * 128] = loc[8];  // the block's middle row, relative to the block's start, until the tables are written
+            float amax = 0.0f;
 #pragma unroll
             for (int r = 0; r < 16; ++r) {
-                e = __expf(base + loc[r]);
-                *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32) = e;
+                const float av = __expf(loc[r] - loc[8]);
+                amax = fmaxf(amax, av);
+                *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(col) + r * RS32) = av;
             }
-            if (part == 3) {
-                egl[d] = e;
-                if (!(e > 1e-34f)) atomicCAS(p.status, 0, kStatusPrefillRange);
-            }
+            // Eight rows of decay must stay below e^85: per-row log decays below about -10.6 (or positive ones) do not.
+            if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            compute_sync();
+            float start[5];  // G before each block's first row, and after the last row
+            start[0] = 0.0f;
+#pragma unroll
+            for (int q2 = 0; q2 < 4; ++q2) start[q2 + 1] = start[q2] + totals[q2 * 128 + d];
+            float gm[4];
+#pragma unroll
+            for (int q2 = 0; q2 < 4; ++q2) gm[q2] = start[q2] + tab[q2 * 128];
+            compute_sync();  // the relative middles have been read: the tables may be written over them
+            tab[(tE0 + part) * 128] = __expf(gm[part]);
+            tab[(tEL + part) * 128] = __expf(start[4] - gm[part]);
+#pragma unroll
+            for (int I = 1; I < 4; ++I)
+                if (I > part) tab[(tF + I * (I - 1) / 2 + part) * 128] = __expf(gm[I] - gm[part]);
+            if (part == 3) egl[d] = __expf(start[4]);
         }
         compute_sync();
 
-        // ---- 2. operand tiles: lane <-> row, one 16-byte cell (8 channels) at a time -------------------------------------
+        // ---- 2. operand tiles: lane <-> row, one 16-byte cell (8 channels) at a time.  Row sides Kgb = K a -> oKg, Qgb = Q a ->
+        // oQg; the column sides K exp(Gm_I - G) into the four tiles I >= J; Kdec = K exp(G_last - G) as bf16 hi + lo; V as it is.
         {
-            const int r = tid & 63, cgrp = tid >> 6;
+            const int r = tid & 63, cgrp = tid >> 6, J = r >> 4;
+            const float* tabs = reinterpret_cast<const float*>(smem + oTab);
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 const int c = cgrp * 2 + cc;
                 const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
                 const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
                 const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oRawV + r * RS16 + c * 16);
-                const float4 e0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
-                const float4 e1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
-                const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
-                const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
-                const float E[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+                const float4 a0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
+                const float4 a1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
+                const float4 l0 = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8);
+                const float4 l1 = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8 + 4);
+                const float A[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
                 const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
                 const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
-                uint32_t kg[4], qg[4], ki[4], dh[4], dl[4];
+                uint32_t kgb[4], qgb[4], kcd[4], dh[4], dl[4];
+                float kc[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float kf[2] = {__uint_as_float(kw[j] << 16), __uint_as_float(kw[j] & 0xffff0000u)};
                     const float qf[2] = {__uint_as_float(qw[j] << 16), __uint_as_float(qw[j] & 0xffff0000u)};
-                    float a[2], bq[2], ci[2], hi[2], lo[2];
+                    float hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const float e = E[2 * j + u], einv = __fdividef(1.0f, e);
-                        a[u] = kf[u] * e;
-                        bq[u] = qf[u] * e;
-                        ci[u] = kf[u] * einv;
-                        tc::split_bf16(kf[u] * (EL[2 * j + u] * einv), hi[u], lo[u]);
+                        kc[2 * j + u] = kf[u] * __fdividef(1.0f, A[2 * j + u]);
+                        tc::split_bf16(kc[2 * j + u] * EL[2 * j + u], hi[u], lo[u]);
                     }
-                    kg[j] = tc::bf16x2(a[0], a[1]);
-                    qg[j] = tc::bf16x2(bq[0], bq[1]);
-                    ki[j] = tc::bf16x2(ci[0], ci[1]);
+                    kgb[j] = tc::bf16x2(kf[0] * A[2 * j], kf[1] * A[2 * j + 1]);
+                    qgb[j] = tc::bf16x2(qf[0] * A[2 * j], qf[1] * A[2 * j + 1]);
+                    kcd[j] = tc::bf16x2(kc[2 * j], kc[2 * j + 1]);
                     dh[j] = tc::bf16x2(hi[0], hi[1]);
                     dl[j] = tc::bf16x2(lo[0], lo[1]);
                 }
-                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
-                *reinterpret_cast<uint4*>(cell(smem + oKinv, CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kgb[0], kgb[1], kgb[2], kgb[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
+                *reinterpret_cast<uint4*>(cell(smem + oKc + kc_tile(J), 16 * (J + 1), c, r)) = make_uint4(kcd[0], kcd[1], kcd[2], kcd[3]);
+                for (int I = J + 1; I < 4; ++I) {  // the later row blocks see this row through exp(Gm_I - Gm_J) <= 1
+                    const float* f = tabs + (tF + I * (I - 1) / 2 + J) * 128 + c * 8;
+                    const float4 fa = *reinterpret_cast<const float4*>(f), fb = *reinterpret_cast<const float4*>(f + 4);
+                    *reinterpret_cast<uint4*>(cell(smem + oKc + kc_tile(I), 16 * (I + 1), c, r)) =
+                        make_uint4(tc::bf16x2(kc[0] * fa.x, kc[1] * fa.y), tc::bf16x2(kc[2] * fa.z, kc[3] * fa.w),
+                                   tc::bf16x2(kc[4] * fb.x, kc[5] * fb.y), tc::bf16x2(kc[6] * fb.z, kc[7] * fb.w));
+                }
             }
         }
         publish_operands();
+
+        // ---- 3. L^T and M^T, one block column of 16 rows i at a time: [64 j x 16 i] = column side (tile I) x row side (block I)^T
+        if (!mma_round([&] {
+                constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
+                for (int I = 0; I < 4; ++I) {
+                    const unsigned char* kct = smem + oKc + kc_tile(I);
+                    const int R = 16 * (I + 1);
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + cL + 16 * I, tc::desc_kmajor_bf16(kct, R, 0, k0), tc::desc_kmajor_bf16(smem + oKg, CH, 16 * I, k0), id, k0 > 0);
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + cMm + 16 * I, tc::desc_kmajor_bf16(kct, R, 0, k0), tc::desc_kmajor_bf16(smem + oQg, CH, 16 * I, k0), id, k0 > 0);
+                }
+            })) { alive = false; break; }
+
+        // ---- 3b. the tiles that take the decay from the chunk's start, over the row sides (the tensor core is done with
+        // them): Kg = K exp(G) for W, Qg = Q exp(G) for Q S.  Then the staging area is free.
+        {
+            const int r = tid & 63, cgrp = tid >> 6, J = r >> 4;
+            const float* tabs = reinterpret_cast<const float*>(smem + oTab);
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cgrp * 2 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
+                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
+                const float4 a0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
+                const float4 a1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
+                const float4 e0 = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8);
+                const float4 e1 = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+                const float E[8] = {a0.x * e0.x, a0.y * e0.y, a0.z * e0.z, a0.w * e0.w, a1.x * e1.x, a1.y * e1.y, a1.z * e1.z, a1.w * e1.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
+                uint32_t kg[4], qg[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    kg[j] = tc::bf16x2(__uint_as_float(kw[j] << 16) * E[2 * j], __uint_as_float(kw[j] & 0xffff0000u) * E[2 * j + 1]);
+                    qg[j] = tc::bf16x2(__uint_as_float(qw[j] << 16) * E[2 * j], __uint_as_float(qw[j] & 0xffff0000u) * E[2 * j + 1]);
+                }
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+            }
+        }
+        compute_sync();  // every thread is done with the staging area and the tables (M goes over them next)
         // The staging area is free: the loader streams the next chunk's rows in behind this chunk's arithmetic.
         if (tid == 0 && s + CH < T) mbar_arrive(bar_free);
 
-        // ---- 3. L = Kg Kinv^T, M = Qg Kinv^T ----------------------------------------------------------------------------
-        if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKinv, CH, 0, k0), id, k0 > 0);
-            })) { alive = false; break; }
-
-        // ---- 4. L (FP32, strictly lower, times beta_i) and M (bf16 cells, lower with the diagonal) --------------------------
-        // Column groups 0, 1 take the two halves of L, groups 2, 3 the two halves of M; lanes 0..15 hold rows.
+        // ---- 4. from L^T and M^T (lane = column j, tensor-memory column = row i): L (FP32, strictly lower, times beta_i); M
+        // (lower with the diagonal) as bf16 cells of eight consecutive rows i, [8 cells][64 columns j].  Column groups 0, 1
+        // take the two halves (of i) of L, groups 2, 3 those of M; lanes 0..15 hold the columns.
         {
             uint32_t r[32];
-            const int half = cg & 1, i = lane_row64;
+            const int half = cg & 1, j = lane_row64;
             tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg < 2 ? cL : cMm) + half * 32), r);
             tc::tmem_ld_wait();
             if (lane < 16) {
                 if (cg < 2) {
-                    float* Lr = reinterpret_cast<float*>(smem + oL) + i * LS + half * 32;
-                    const float bi = betas[i];
+                    float* Lc = reinterpret_cast<float*>(smem + oL) + j;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) Lr[j] = half * 32 + j < i ? bi * __uint_as_float(r[j]) : 0.0f;
+                    for (int i2 = 0; i2 < 32; ++i2) {
+                        const int i = half * 32 + i2;
+                        Lc[i * LS] = i > j ? betas[i] * __uint_as_float(r[i2]) : 0.0f;
+                    }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (half * 32 + j > i) r[j] = 0u;
+                    for (int i2 = 0; i2 < 32; ++i2)
+                        if (half * 32 + i2 < j) r[i2] = 0u;
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oMm, CH, half * 4 + cc, i)) = pack8(r + cc * 8);
+                    for (int cc = 0; cc < 4; ++cc) *reinterpret_cast<uint4*>(cell(smem + oMm, CH, half * 4 + cc, j)) = pack8(r + cc * 8);
                 }
             }
         }
@@ -386,9 +441,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
 
         // ---- 11. O = QS + M D;  S += Kdec^T D (hi hi + hi lo + lo hi) ------------------------------------------------------------------
         if (!mma_round([&] {
-                constexpr uint32_t id = tc::idesc_bf16(64, 128, 0, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);
+                constexpr uint32_t idm = tc::idesc_bf16(64, 128, 1, 1, 0), ids = tc::idesc_bf16(128, 128, 1, 1, 0);  // M has its rows contiguous
                 for (int k0 = 0; k0 < CH; k0 += 16)
-                    tc::mma_bf16(tm + cQS, tc::desc_kmajor_bf16(smem + oMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), id, true);
+                    tc::mma_bf16(tm + cQS, tc::desc_mnmajor_bf16(smem + oMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), idm, true);
                 for (int k0 = 0; k0 < CH; k0 += 16)
                     tc::mma_bf16(tm + cS, tc::desc_mnmajor_bf16(smem + oKdHi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + oDhi, CH, 0, k0), ids, true);
                 for (int k0 = 0; k0 < CH; k0 += 16)

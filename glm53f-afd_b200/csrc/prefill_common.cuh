@@ -27,6 +27,11 @@ constexpr int oQg = oV + kTile;           // Qg                       (steps 2-9
 constexpr int oKdHi = oQg + kTile, oKdLo = oKdHi + kTile;  // Kdec hi, lo (steps 2-11)
 constexpr int oMm = oKdLo + kTile;        // M, 64 x 64 bf16          (steps 4-11)
 constexpr int oS16 = oKg, oDhi = oTp, oDlo = oV, oTpHi = oTp, oTpLo = oTp + kTile / 2;
+// The column sides of L and M, one tile per row block I (rows 0 .. 16 I + 15, 256 bytes a row), over Kinv | T' | W
+// (steps 2-3); the per-block decay factor tables (14 x 128 floats: E0[4], EL[4], F[6]) over M (steps 1-3).
+constexpr int oKc = oKinv, oTab = oMm, kTabs = 14, tE0 = 0, tEL = 4, tF = 8;
+__device__ __forceinline__ int kc_tile(int I) { return 2048 * I * (I + 1); }
+static_assert(2 * 128 * (16 + 32 + 48 + 64) <= 3 * kTile && kTabs * 512 <= kTile / 2, "column-side tiles and tables");
 // FP32 scratch of the inversion (steps 4-5) over Kinv | T' | W, all dead then: T, P, L.  Rows are padded to 68
 // floats so that one lane per row spreads over the banks while float4 loads stay aligned.
 constexpr int LS = 68;

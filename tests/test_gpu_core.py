@@ -308,13 +308,64 @@ def test_prefill_strong_gates_and_large_beta(G, core, oracle, pkg, ws_chunks):
     assert G.rel_l2(G.host_f32(d_state), s_ref) <= STATE_REL_L2
 
 
-# Gates beyond the range the chunk-64 kernels cover (a chunk's cumulative decay below ~e^-78) are not computed wrongly
-# in silence: every form records status 121, which the status call returns once and clears.  Nothing faults: the
-# arithmetic merely overflows.
+# The whole domain of the layer entry points (log decay down to -5.8 per row, -371 per chunk of 64): the gates of the
+# reference's own saturated and mixed cases (crates/glm53f-kda/tests/cpu_reference.rs:399-450: every channel at the
+# lower bound; strong and no decay alternating by row), the model's gate law exp(lower * sigmoid(x)) with lower = -5,
+# channels that differ by orders of magnitude, and a burst of strong decay at the start of every chunk.  Both kernels,
+# carried and zero states, the task's tolerances against the FP32 recurrence.
+def wide_gates(kind, t, heads, rng):
+    shape = (t, heads, DK)
+    if kind == "model":
+        g = -5.0 / (1.0 + np.exp(-rng.normal(0.0, 2.0, shape)))
+    elif kind == "strongest":
+        g = np.full(shape, -5.8)
+    elif kind == "by_row":
+        g = np.where((np.arange(t) % 3 == 0)[:, None, None], 0.0, -5.0) * np.ones(shape)
+    elif kind == "by_channel":
+        g = np.where((np.arange(DK) % 2 == 0)[None, None, :], -5.8, -0.01) * np.ones(shape)
+    elif kind == "bursts":
+        g = np.where((np.arange(t) % 64 < 8)[:, None, None], -5.8, 0.0) * np.ones(shape)
+    else:
+        raise ValueError(kind)
+    return g.astype(np.float32).reshape(-1)
+
+
+@pytest.mark.parametrize("ws_chunks", [None, 3])
+@pytest.mark.parametrize("kind", ["model", "strongest", "by_row", "by_channel", "bursts"])
+def test_prefill_gates_over_the_whole_domain(G, core, oracle, pkg, ws_chunks, kind):
+    o = oracle
+    heads, lens = 2, [333, 48, 64]
+    rows, per = sum(lens), heads * DV * DK
+    q, k, v, _, beta = pkg.synth.tokens(0, 9, rows, heads)
+    g = wide_gates(kind, rows, heads, np.random.default_rng(5))
+    states = np.concatenate([pkg.synth.state(0, 9, 0, heads), np.zeros(per, np.float32), pkg.synth.state(0, 9, 2, heads)])
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    dq, dk, dv, dg, db = upload_tokens(G, (q, k, v, g, beta))
+    d_state, d_out = G.dev_f32(states), torch.zeros(rows * heads * DV, dtype=torch.int16, device="cuda")
+    ws = None if ws_chunks is None else torch.empty(core.prefill_workspace_bytes(heads, len(lens), ws_chunks), dtype=torch.uint8, device="cuda")
+    core.prefill_varlen(heads, rows, G.dev_i32(cu), max(lens), dq, dk, dv, dg, db, d_state, G.dev_i64([i * per for i in range(len(lens))]),
+                        out=d_out, workspace=ws)
+    G.check_status()
+    got, st = G.host_bf16(d_out).reshape(rows, heads * DV), G.host_f32(d_state)
+    assert np.isfinite(got).all() and np.isfinite(st).all()
+    for i, n in enumerate(lens):
+        part = lambda a, w: a.reshape(rows, heads * w)[cu[i]:cu[i] + n].reshape(-1)
+        y, s_ref = o.core_forward(heads, part(q, DK), part(k, DK), part(v, DV), part(g, DK), beta.reshape(rows, heads)[cu[i]:cu[i] + n].reshape(-1),
+                                  states[i * per:(i + 1) * per], form="recurrent", threads=4)
+        out_i = got[cu[i]:cu[i] + n].reshape(-1)
+        assert G.max_abs(out_i, y) <= OUT_MAX_ABS, (kind, i)
+        assert G.rel_l2(out_i, y) <= OUT_REL_L2, (kind, i)
+        assert G.rel_l2(st[i * per:(i + 1) * per], s_ref) <= STATE_REL_L2, (kind, i)
+
+
+# The one limit that is left: a block of eight rows may not decay by more than about e^-85 per channel (per-row log
+# decays below -10.6, twice the model's bound), and a positive "decay" is not a decay.  Such inputs are not computed
+# wrongly in silence: every form records status 121, which the status call returns once and clears.  Nothing faults:
+# the arithmetic merely overflows.
 def test_prefill_reports_gates_outside_its_range(G, core, pkg):
     heads, t = 2, 130
     q, k, v, g, beta = pkg.synth.tokens(0, 8, t, heads)
-    g = np.full_like(g, -2.0)   # -128 per chunk
+    g = np.full_like(g, -12.0)
     dq, dk, dv, dg, db = upload_tokens(G, (q, k, v, g, beta))
     for workspace in (None, torch.empty(core.prefill_workspace_bytes(heads, 1, 2), dtype=torch.uint8, device="cuda"), "static"):
         d_state, d_out = torch.zeros(heads * DV * DK, device="cuda"), torch.zeros(t * heads * DV, dtype=torch.int16, device="cuda")
@@ -323,7 +374,7 @@ def test_prefill_reports_gates_outside_its_range(G, core, pkg):
         assert core.device_status() == 121
         assert core.device_status() == 0
     # and the same call with gates inside the range is clean afterwards
-    dg = G.dev_f32(np.full_like(g, -0.5))
+    dg = G.dev_f32(np.full_like(g, -5.8))
     d_state, d_out = torch.zeros(heads * DV * DK, device="cuda"), torch.zeros(t * heads * DV, dtype=torch.int16, device="cuda")
     core.prefill_varlen(heads, t, G.dev_i32([0, t]), t, dq, dk, dv, dg, db, d_state, G.dev_i64([0]), out=d_out)
     G.check_status()

@@ -252,19 +252,33 @@ def run_layer_abi(torch, lib, rank, layers, steps, prefill_lib_ok=True):
     lanes, lane_rows, pl = 4, 2048, min(layers, 2)
     res["prefill_layer"] = {"workload": f"{lanes} lanes x {lane_rows} rows, 64 heads, through glm53f_kda_prefill_batch[_bf16state]; ms per lane and layer",
                             "reference_published_ms_per_lane": {"value": 0.983, "where": "RTX 5090, docs/PERFORMANCE.md:374-378"}}
-    for bf16 in (False, True):
-        for batch in (lanes, 1):
-            f = LayerAbi(torch, rank, batch, lane_rows, pl, bf16_state=bf16, seed=5)
-            wsb = int(lib.glm53f_kda_prefill_workspace_bytes(HEADS, batch, 256))
-            ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda")
-            try:
-                ms, _g = graph_ms(torch, lambda st: [f.prefill(lib, l, st, ws, wsb, lane_rows, 2) for l in range(pl)], max(2, steps // 5), warm=2)
-                res["prefill_layer"][("bf16state" if bf16 else "f32state") + f"_batch{batch}"] = {
-                    "ms_per_lane": ms / pl / batch, "rows_per_s": batch * lane_rows * pl / (ms * 1e-3), "workspace_bytes": wsb, "value_blocks": 2}
-                del _g
-            finally:
-                del f, ws
-                torch.cuda.empty_cache()
+    try:
+        set_mode = lib.glm53f_kda_prefill_mode
+        set_mode.restype, set_mode.argtypes = C.c_int32, [C.c_int32]
+        modes = [("exact", 0), ("chunked", 1)]   # the product: the row-by-row form (default) and the tensor-core form
+    except AttributeError:
+        set_mode, modes = None, [("kernel", None)]  # the reference's kernels have one form
+    for mode_name, mode in modes:
+        if set_mode is not None:
+            set_mode(mode)
+        try:
+            for bf16 in (False, True):
+                for batch in (lanes, 1):
+                    f = LayerAbi(torch, rank, batch, lane_rows, pl, bf16_state=bf16, seed=5)
+                    wsb = int(lib.glm53f_kda_prefill_workspace_bytes(HEADS, batch, 256))
+                    ws = torch.empty(max(wsb, 16), dtype=torch.uint8, device="cuda")
+                    try:
+                        ms, _g = graph_ms(torch, lambda st: [f.prefill(lib, l, st, ws, wsb, lane_rows, 2) for l in range(pl)], max(2, steps // 5), warm=2)
+                        res["prefill_layer"][f"{mode_name}_" + ("bf16state" if bf16 else "f32state") + f"_batch{batch}"] = {
+                            "ms_per_lane": ms / pl / batch, "rows_per_s": batch * lane_rows * pl / (ms * 1e-3), "workspace_bytes": wsb,
+                            "rows_per_pass": 256, "value_blocks": 2}
+                        del _g
+                    finally:
+                        del f, ws
+                        torch.cuda.empty_cache()
+        finally:
+            if set_mode is not None:
+                set_mode(0)
     return res
 
 

@@ -16,6 +16,7 @@ SOURCES = {
     "kda_chain.cu": IEEE,
     "kda_conv.cu": IEEE,
     "kda_prefill.cu": IEEE,
+    "kda_prologue.cu": IEEE,  # the layer prologue in front of the chunked prefill: the chain's prologue arithmetic
     "kda_prefill_tc.cu": [],
     "kda_prefill_sp.cu": [],
     "proj_gemm.cu": [],      # the projections: tcgen05 GEMM

@@ -29,11 +29,30 @@ int conv_shift_launch(int32_t channels, int32_t layers, int32_t batch, const int
                       int32_t keep1, int32_t rows1, glm53f_bf16* conv, int64_t conv_stride, const int64_t* conv_off,
                       const glm53f_bf16* p, int64_t p_layer_stride, int64_t p_stride, cudaStream_t stream);
 
-// The chunk-64 tensor-core prefill (kda_prefill_tc.cu).  q, k, v, g, out (and gate, norm_w) must be 16-byte aligned.
+// One pass of a layer prefill through the core kernel: sequence b's inputs are rows b * pass_rows .. of q, k, v, g, beta
+// (its rows row_shift .. row_shift + pass_rows - 1, as many of them as it has); its outputs and gate rows are rows
+// cu[b] + row_shift .. of `out` and `gate`, gate rows gate_stride elements apart.
+struct PrefillWindow {
+    int pass_rows = 0, row_shift = 0;
+    long long gate_stride = 0;
+    bool qk_fp16 = false;  // q and k hold fp16 bits (the layer prologue's), not bf16
+};
+
+// The chunk-64 tensor-core prefill (kda_prefill_tc.cu).  q, k, v, g, out (and norm_w) must be 16-byte aligned.
 int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, const glm53f_bf16* q, const glm53f_bf16* k,
                            const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
                            const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate, const glm53f_bf16* norm_w,
-                           float eps, glm53f_bf16* out, cudaStream_t stream);
+                           float eps, glm53f_bf16* out, cudaStream_t stream, const PrefillWindow* win = nullptr);
+
+// The layer prologue of a prefill pass (kda_prologue.cu): for rows row_shift .. row_shift + pass_rows - 1 of every request,
+// the short convolution + SiLU, the L2 norms, the log decay and beta, with the chain's arithmetic, written as core inputs
+// (q, k as fp16 bits, v bf16, g f32 log decay [batch * pass_rows][H][128]; beta f32 [batch * pass_rows][H]).  p, a, conv must be
+// 8-byte aligned with strides that are multiples of 4 elements.
+int layer_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t pass_rows, int32_t row_shift,
+                          const glm53f_bf16* p, int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride,
+                          const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w, const float* a_log,
+                          const float* dt_bias, float lower, glm53f_bf16* q, glm53f_bf16* k, glm53f_bf16* v, float* g, float* beta,
+                          cudaStream_t stream);
 
 // The two-pass tensor-core prefill over a workspace (kda_prefill_sp.cu).
 int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunks_per_pass);

@@ -30,6 +30,8 @@
 // Raw inputs arrive by bulk asynchronous copies (one per row and tensor) into padded row-major staging buffers;
 // operands are written in the un-swizzled "cell" layout of tc.cuh.  All waits are bounded.
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "glm53f_kda.h"
 #include "kda_internal.h"
@@ -56,8 +58,29 @@ struct TcParams {
     float eps;
     uint16_t* out;
     int* status;
+    // A pass of a layer prefill (pass_rows > 0): sequence b's inputs are rows b * pass_rows .. of q, k, v, g, beta (its
+    // rows row_shift .. row_shift + pass_rows - 1, as many as it has), its outputs and gate rows are rows
+    // cu[b] + row_shift .. of `out` and `gate`.  Otherwise inputs and outputs are both rows cu[b] .. cu[b + 1] - 1.
+    int pass_rows, row_shift;
+    long long gate_stride;  // elements between consecutive gate rows
 };
 
+// Two 16-bit values of a q or k row to FP32: bf16 (the core entry points' inputs), or fp16 when the layer prologue
+// produced them (normalised q and k lie in [-1, 1]; eleven mantissa bits instead of eight keep the rounding of k, which
+// goes into the state through Kdec, below the state's error budget).
+template <bool QK16>
+__device__ __forceinline__ void widen2(uint32_t w, float& lo, float& hi) {
+    if constexpr (QK16) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo = f.x;
+        hi = f.y;
+    } else {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    }
+}
+
+template <bool QK16>
 __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_constant__ TcParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(smem + oBars);
@@ -72,8 +95,19 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
     const int lane_row128 = quad * 32 + lane;     // row of an M = 128 accumulator this thread reaches
     const int lane_row64 = quad * 16 + lane;      // row of an M = 64 accumulator (lanes 0..15 only)
     const int h = blockIdx.x, b = blockIdx.y, H = p.H;
-    const long long row0 = p.cu[b];
-    const int T = p.cu[b + 1] - p.cu[b];
+    long long in0, out0;
+    int T;
+    {
+        const int r0 = p.cu[b], len = p.cu[b + 1] - r0;
+        if (p.pass_rows > 0) {
+            T = min(max(len - p.row_shift, 0), p.pass_rows);
+            in0 = (long long)b * p.pass_rows;
+            out0 = (long long)r0 + p.row_shift;
+        } else {
+            T = len;
+            in0 = out0 = r0;
+        }
+    }
     const long long s_elem = p.state_off[b] + (long long)h * DV * DK;
 
     if (tid == 0) {
@@ -102,7 +136,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 free_phase ^= 1u;
             }
             const int n = min(CH, T - s);
-            const long long gr0 = row0 + s;
+            const long long gr0 = in0 + s;
             float* bt = betas2 + (it & 1) * CH;
             for (int r = lane; r < CH; r += 32) {
                 bt[r] = r < n ? p.beta[(gr0 + r) * H + h] : 0.0f;
@@ -166,7 +200,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
 
     for (int s = 0; s < T; s += CH) {
         const int n = min(CH, T - s);
-        const long long gr0 = row0 + s;
+        const long long gr0 = out0 + s;
         const float* betas = betas2 + ((s / CH) & 1) * CH;
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
         raw_phase ^= 1u;
@@ -236,8 +270,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 float kc[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float kf[2] = {__uint_as_float(kw[j] << 16), __uint_as_float(kw[j] & 0xffff0000u)};
-                    const float qf[2] = {__uint_as_float(qw[j] << 16), __uint_as_float(qw[j] & 0xffff0000u)};
+                    float kf[2], qf[2];
+                    widen2<QK16>(kw[j], kf[0], kf[1]);
+                    widen2<QK16>(qw[j], qf[0], qf[1]);
                     float hi[2], lo[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
@@ -299,8 +334,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                 uint32_t kg[4], qg[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    kg[j] = tc::bf16x2(__uint_as_float(kw[j] << 16) * E[2 * j], __uint_as_float(kw[j] & 0xffff0000u) * E[2 * j + 1]);
-                    qg[j] = tc::bf16x2(__uint_as_float(qw[j] << 16) * E[2 * j], __uint_as_float(qw[j] & 0xffff0000u) * E[2 * j + 1]);
+                    float kf[2], qf[2];
+                    widen2<QK16>(kw[j], kf[0], kf[1]);
+                    widen2<QK16>(qw[j], qf[0], qf[1]);
+                    kg[j] = tc::bf16x2(kf[0] * E[2 * j], kf[1] * E[2 * j + 1]);
+                    qg[j] = tc::bf16x2(qf[0] * E[2 * j], qf[1] * E[2 * j + 1]);
                 }
                 *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
                 *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
@@ -475,7 +513,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
                     const float rinv = 1.0f / sqrtf(tot / (float)DV + p.eps);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float gt = bf16_bits_to_f32(p.gate[at + j]), w = bf16_bits_to_f32(p.norm_w[cg * 32 + j]);
+                        const float gt = bf16_bits_to_f32(p.gate[(gr0 + i) * p.gate_stride + h * DV + cg * 32 + j]), w = bf16_bits_to_f32(p.norm_w[cg * 32 + j]);
                         y[j] = w * (y[j] * rinv) * (1.0f / (1.0f + __expf(-gt)));
                     }
                 }
@@ -514,12 +552,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
 int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, const glm53f_bf16* q, const glm53f_bf16* k,
                            const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, void* state_out,
                            const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate, const glm53f_bf16* norm_w,
-                           float eps, glm53f_bf16* out, cudaStream_t stream) {
+                           float eps, glm53f_bf16* out, cudaStream_t stream, const PrefillWindow* win) {
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
         if (e != cudaSuccess) return (int)e;
         configured_dev = dev;
     }
@@ -532,9 +571,16 @@ int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     p.state_bf16 = bf16_state ? 1 : 0;
     p.gate = gate; p.norm_w = norm_w; p.eps = eps;
     p.out = out;
+    p.gate_stride = (long long)heads * DV;
+    if (win != nullptr) {
+        p.pass_rows = win->pass_rows;
+        p.row_shift = win->row_shift;
+        p.gate_stride = win->gate_stride;
+    }
     p.status = status_word();
     if (p.status == nullptr) return (int)cudaErrorUnknown;
-    prefill_tc_kernel<<<dim3(heads, batch), kThreadsTc, kSmemTc, stream>>>(p);
+    if (win != nullptr && win->qk_fp16) prefill_tc_kernel<true><<<dim3(heads, batch), kThreadsTc, kSmemTc, stream>>>(p);
+    else prefill_tc_kernel<false><<<dim3(heads, batch), kThreadsTc, kSmemTc, stream>>>(p);
     return (int)cudaGetLastError();
 }
 

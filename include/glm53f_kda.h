@@ -354,6 +354,19 @@ int glm53f_kda_core_prefill_varlen_static(int32_t heads, int32_t batch, const in
  * synchronises the device.  Not in the reference (its kernels have no device-side waits). */
 int glm53f_kda_device_status(void);
 
+/* Which form the layer prefill entry points (glm53f_kda_prefill, _batch, _batch_bf16state) run; not in the reference's
+ * header, whose forward gates its own chunked kernel with a switch of its own (crates/glm53f-forward/src/forward.rs:210,
+ * 3580).
+ *   0  exact (the default): the row-by-row recurrence, the chain's results bit for bit
+ *   1  chunked: passes of (layer prologue, chunk-64 tensor-core kernel with the gated norm fused) over the caller's
+ *      workspace; results agree with the chain to the rounding of bf16 operands (the task's tolerances: bf16 outputs
+ *      within 2e-2 max-abs / 5e-3 rel-L2, state within 1e-3 rel-L2) and do not depend on the workspace size or the
+ *      batching; `value_blocks` is not used.  Calls the chunked kernels cannot take (output rows that are not dense,
+ *      rows not 8-byte aligned, a workspace below 64 rows a pass) run the exact form.
+ * Any other value only queries.  Returns the mode that was in force.  The environment variable
+ * GLM53F_KDA_PREFILL=chunked makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */
+int32_t glm53f_kda_prefill_mode(int32_t mode);
+
 /* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The decode / verify / commit
  * kernels bound every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
  * status code (101-108, which wait), makes its other waits return, and the kernel ends; the context stays usable and

@@ -21,6 +21,7 @@ SOURCES = {
     "kda_prefill_sp.cu": [],
     "proj_gemm.cu": [],      # the projections: tcgen05 GEMM
     "proj_gemm_pair.cu": [], # the same on SM pairs (cta_group::2) for many rows
+    "kda_gather.cu": [],     # host code only: CUDA IPC handles for the full output buffers of a head-sharded prefill
     "fwd_rows.cu": [],       # row gather / scatter and the mark copy: data movement only  # tensor-core prefill: agrees with the chain to rounding, so default FP flags
 }
 

@@ -354,6 +354,29 @@ int glm53f_kda_core_prefill_varlen_static(int32_t heads, int32_t batch, const in
  * synchronises the device.  Not in the reference (its kernels have no device-side waits). */
 int glm53f_kda_device_status(void);
 
+/* The multi-GPU boundary of glm53f_kda_core_prefill_varlen_ws_gather for any host, one process per GPU; no counterpart
+ * in the reference, which runs on one GPU.  Each rank allocates its full [rows][heads_total][128] bf16 output buffer
+ * (plain cudaMalloc memory, 16-byte aligned), exports a handle, gives the 128 opaque bytes to the other ranks by
+ * whatever channel the host has, and opens theirs; the addresses it gets are what `full[]` takes.  CUDA IPC underneath:
+ * no collective library, no multicast object.  The kernels only store to a peer's buffer, they never load from it.
+ *   glm53f_kda_gather_head_range  heads [head0, head0 + heads) of heads_total for `rank` of `ranks` (1..8; heads_total
+ *                                 divisible by ranks)
+ *   glm53f_kda_gather_export      handle for the `bytes` bytes at `full`, a buffer inside a device allocation of this
+ *                                 process (the handle names the allocation and the buffer's offset in it)
+ *   glm53f_kda_gather_open        maps a peer's buffer into this process (its GPU must be able to reach the peer's:
+ *                                 peer access is enabled on first use); *full is the address to put in `full[]`;
+ *                                 *bytes (may be NULL) the exported size.  Not for a handle exported by this process:
+ *                                 a rank lists its own buffer by its own address.
+ *   glm53f_kda_gather_close       unmaps what glm53f_kda_gather_open mapped; call it after the last launch that stores
+ *                                 into the buffer has completed, and before the exporter frees the allocation.
+ * All four return 0, 1 (cudaErrorInvalidValue) for a rejected argument, or another cudaError_t.  The caller still
+ * orders the ranks around a launch (a barrier on each side), as glm53f_kda_core_prefill_varlen_ws_gather asks. */
+typedef struct glm53f_kda_gather_handle { unsigned char opaque[128]; } glm53f_kda_gather_handle;
+int glm53f_kda_gather_head_range(int32_t heads_total, int32_t rank, int32_t ranks, int32_t* head0, int32_t* heads);
+int glm53f_kda_gather_export(const void* full, int64_t bytes, glm53f_kda_gather_handle* handle);
+int glm53f_kda_gather_open(const glm53f_kda_gather_handle* handle, void** full, int64_t* bytes);
+int glm53f_kda_gather_close(const glm53f_kda_gather_handle* handle, void* full);
+
 /* Which form the layer prefill entry points (glm53f_kda_prefill, _batch, _batch_bf16state) run; not in the reference's
  * header, whose forward gates its own chunked kernel with a switch of its own (crates/glm53f-forward/src/forward.rs:210,
  * 3580).

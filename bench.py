@@ -356,13 +356,16 @@ def run_verify(torch, lib, rank, layers, steps):
     P = lambda t, byte_off=0: C.c_void_p(t.data_ptr() + byte_off)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
-    def verify():
+    def verify(flags=0):
         for l in range(layers):
             rc = lib.glm53f_kda_core_verify_batch(HEADS, slots, P(cu), P(q), P(k), P(v), P(g), P(beta), P(arena, 2 * l * slots * per), None, P(off),
-                                                  1, 0, None, None, 1e-5, P(out), P(ks, 4 * l * nkv), P(vs, 2 * l * nkv), P(gs_, 4 * l * nkv),
+                                                  1, flags, None, None, 1e-5, P(out), P(ks, 4 * l * nkv), P(vs, 2 * l * nkv), P(gs_, 4 * l * nkv),
                                                   P(bs, 4 * l * nb), stream)
             if rc != 0:
                 raise RuntimeError(f"verify launch failed: {rc}")
+
+    def verify_tensor():
+        verify(2)  # GLM53F_KDA_CORE_TENSOR: the window as one 16-row chunk on the tensor cores
 
     def commit():
         rc = lib.glm53f_kda_core_commit_batch(HEADS, layers, slots, P(cu), P(keep), P(arena), P(arena), slots * per, P(off), 1, P(ks), P(vs),
@@ -383,7 +386,8 @@ def run_verify(torch, lib, rank, layers, steps):
     for _ in range(3):
         verify()
         commit()
-    ms_v, ms_c = timed(verify), timed(commit)
+    verify_tensor()
+    ms_v, ms_c, ms_t = timed(verify), timed(commit), timed(verify_tensor)
     state_bytes = layers * slots * per * 2
     v_bytes = state_bytes + layers * rows * (TOKEN_IN_BYTES + TOKEN_OUT_BYTES + HEADS * 1284)
     hbm, kind = peaks()
@@ -393,6 +397,11 @@ def run_verify(torch, lib, rank, layers, steps):
                       "roofline": {"bound": "hbm", "achieved": v_bytes / (ms_v * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
                                    "frac": v_bytes / (ms_v * 1e-3) / 1e9 / hbm, "peak_source": kind,
                                    "counts": "each bf16 state read once, the rows' inputs and outputs, the replay saves written"}},
+           "verify_tensor": {"entry": "glm53f_kda_core_verify_batch with GLM53F_KDA_CORE_TENSOR (outputs to bf16-operand rounding, saves and committed states exact)",
+                             "ms_per_step": ms_t, "rows_per_s": rows * layers / (ms_t * 1e-3), "state_gbs": state_bytes / (ms_t * 1e-3) / 1e9,
+                             "algorithmic_bytes": v_bytes, "gpu_launches": layers,
+                             "roofline": {"bound": "hbm", "achieved": v_bytes / (ms_t * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                                          "frac": v_bytes / (ms_t * 1e-3) / 1e9 / hbm, "peak_source": kind}},
            "commit": {"ms_per_step": ms_c, "state_gbs": 2 * state_bytes / (ms_c * 1e-3) / 1e9, "frac_of_hbm": 2 * state_bytes / (ms_c * 1e-3) / 1e9 / hbm,
                       "peak_source": kind, "mean_kept_rows": float(keeps.mean()), "gpu_launches": 1}}
     del arena, ks, gs_, vs, bs

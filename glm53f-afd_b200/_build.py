@@ -16,6 +16,7 @@ SOURCES = {
     "kda_chain.cu": IEEE,
     "kda_conv.cu": IEEE,
     "kda_prefill.cu": IEEE,
+    "kda_verify_tc.cu": IEEE,  # the chunked verify: its replay saves must carry the exact path's bits (the same expf)
     "kda_prologue.cu": IEEE,  # the layer prologue in front of the chunked prefill: the chain's prologue arithmetic
     "kda_prefill_tc.cu": [],
     "kda_prefill_sp.cu": [],

@@ -14,6 +14,7 @@ from . import ffi
 
 DK = DV = 128
 L2NORM = 1
+TENSOR = 2   # verify only: the window as one 16-row chunk on the tensor cores (outputs to bf16-operand rounding, saves exact)
 STATIC_SCRATCH_SLOTS = 64  # chains the library's own scratch array can serve (one chunk per pass each)
 
 

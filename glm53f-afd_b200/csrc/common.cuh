@@ -22,7 +22,8 @@ enum : int {
     kStatusWaitYFull = 107,
     kStatusWaitYEmpty = 108,
     kStatusWaitPrefill = 120,
-    kStatusPrefillRange = 121,  // a chunk's cumulative decay left the range the tensor-core prefill covers
+    kStatusPrefillRange = 121,  // eight rows of decay beyond what the tensor-core kernels can factor (or a positive log decay)
+    kStatusVerifyWindow = 122,  // the tensor-core verify met a window of more than 16 rows (it computed the first 16)
 };
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }

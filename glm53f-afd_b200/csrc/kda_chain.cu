@@ -992,8 +992,17 @@ int core_entry(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53
     if (heads < 1 || heads > 65535 || batch < 1 || batch > 65535) return kInvalid;
     if (!cu_rows || !q || !k || !v || !g || !beta || !state_in || !state_off || !out) return kInvalid;
     if (gate && !norm_w) return kInvalid;
-    if (flags & ~GLM53F_KDA_CORE_L2NORM) return kInvalid;
+    if (flags & ~(GLM53F_KDA_CORE_L2NORM | GLM53F_KDA_CORE_TENSOR)) return kInvalid;
     if (!saves_ok(k_save, v_save, g_save, b_save)) return kInvalid;
+    if (flags & GLM53F_KDA_CORE_TENSOR) {
+        // The chunked verify takes read-only bf16 states, inputs as given (no fused norms) and aligned rows; any other
+        // call runs the exact form, whose results are always valid.
+        auto al = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+        if (state_bf16 != 0 && state_out == nullptr && gate == nullptr && !(flags & GLM53F_KDA_CORE_L2NORM) && al(q) && al(k) && al(v) && al(g))
+            return core_verify_tc_launch(heads, batch, cu_rows, q, k, v, g, beta, state_in, state_off, out, k_save, v_save, g_save, b_save,
+                                         (cudaStream_t)stream);
+        flags &= ~GLM53F_KDA_CORE_TENSOR;
+    }
     Params x{};
     x.H = heads;
     x.layers = 1;

@@ -44,6 +44,12 @@ int core_prefill_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
                            const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate, const glm53f_bf16* norm_w,
                            float eps, glm53f_bf16* out, cudaStream_t stream, const PrefillWindow* win = nullptr);
 
+// Draft verification as one 16-row chunk on the tensor cores (kda_verify_tc.cu): bf16 states, read only; outputs to the
+// rounding of bf16 operands, replay saves as the exact path writes them.  q, k, v, g must be 16-byte aligned.
+int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+                          const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, const int64_t* state_off,
+                          glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream);
+
 // The layer prologue of a prefill pass (kda_prologue.cu): for rows row_shift .. row_shift + pass_rows - 1 of every request,
 // the short convolution + SiLU, the L2 norms, the log decay and beta, with the chain's arithmetic, written as core inputs
 // (q, k as fp16 bits, v bf16, g f32 log decay [batch * pass_rows][H][128]; beta f32 [batch * pass_rows][H]).  p, a, conv must be

@@ -1,0 +1,369 @@
+// Draft verification on the tensor cores: a verify window of up to 16 rows is one 16-row chunk.
+//
+// The exact verify (kda_chain.cu) walks a window's rows one after the other through the delta rule, each row a full
+// pass over the 128 x 128 state in registers: 16 serial passes, bound by instruction issue.  The chunked form reads the
+// state once and does the state-sized work as two small tensor-core products.  For the rows i = 0..15 of a window,
+// with G the cumulative log decay, Gm = G_8 (the middle row: every decay factor formed below stays within e^+-47 for
+// the model's gate bound of -5.8 per row) and S the window's incoming state [v][k]:
+//
+//   L = beta_i (k_i a_i).(k_j / a_j) for j < i,  M = (q_i a_i).(k_j / a_j) for j <= i,   a = exp(G - Gm)
+//                         as L^T, M^T = Kc x Kgb^T, Kc x Qgb^T (tcgen05, M = 128 of which 16 rows are real, N = 16)
+//   T = (I + L)^-1        16 x 16 forward substitution, FP32, one thread per column;  T' = T diag(beta)
+//   W = T' Kg,  U = T' V  FP32 on the CUDA cores (thread = channel: 136 multiply-adds each), Kg = k exp(G)
+//   (W S)^T, (Qg S)^T     = S x W^T, S x Qg^T: tcgen05, M = 128 value channels, N = 16 rows, K = 128 key channels; the
+//                         bf16 state tile is the A operand exactly as it lies in HBM (rows of 128 key channels)
+//   D = U - W S,  O = Qg S + M D   FP32, thread = value channel (its tensor-memory lane)
+//
+// The state is not written (a verify leaves it to the commit) and the replay saves are the exact path's, bit for bit
+// (k widened, v copied, exp(g) by the same expf, beta copied), so verify + commit still leaves the states of serial
+// decode steps; only the window's OUTPUTS differ from the serial steps', by the rounding of bf16 operands (within the
+// task's tolerance: max-abs 2e-2, rel-L2 5e-3).  Selected by GLM53F_KDA_CORE_TENSOR on glm53f_kda_core_verify_batch.
+//
+// One block of 128 threads per (request, head) unit, three blocks per SM, blocks walk the units persistently.  A unit's
+// rows and state arrive by asynchronous 16-byte copies issued one unit ahead (the state straight into the 128-byte
+// swizzle the tensor core reads), so one unit's arithmetic covers the next one's loads.  All waits are bounded.
+
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "glm53f_kda.h"
+#include "kda_internal.h"
+#include "tc.cuh"
+
+namespace kda {
+namespace {
+
+constexpr int WIN = 16, kVThreads = 128;
+// Shared memory map (bytes).  Tiles are boxes of R rows x 128 bytes in the 128-byte swizzle (16-byte piece p of row r at
+// piece p ^ (r & 7)), two boxes per tile (channels 0-63, 64-127).  The column-side tile Kc comes first: as the M = 128
+// operand of L^T and M^T its descriptor walks 128 rows although 16 are real, and what follows it is the state tile.
+constexpr int vKc = 0, vS = 4096, vKgb = vS + 32768, vQgb = vKgb + 4096, vQg = vQgb + 4096, vRaw = vQg + 4096;
+constexpr int vW = vKgb;                                                 // W replaces Kgb once L^T is done
+constexpr int rQ = 0, rK = 4096, rV = 8192, rG = 12288, rB = 20480;      // raw rows inside vRaw
+constexpr int vL = vRaw + 20608, vM = vL + WIN * 17 * 4, vTp = vM + WIN * WIN * 4, vBeta = vTp + WIN * WIN * 4;
+constexpr int vBar = vBeta + 64, vCtl = vBar + 16, kVSmem = vCtl + 16;
+static_assert(vL % 16 == 0 && vBar % 8 == 0 && kVSmem <= 75 * 1024, "verify kernel shared memory");
+constexpr uint32_t kVCols = 32;  // tensor memory: [0, 16) L^T then (W S)^T, [16, 32) M^T then (Qg S)^T
+
+struct VParams {
+    int H;
+    long long units;
+    const int32_t* cu;
+    const uint16_t *q, *k, *v;
+    const float* g;
+    const float* beta;
+    const uint16_t* state;
+    const long long* state_off;
+    uint16_t* out;
+    float* k_save;
+    uint16_t* v_save;
+    float* g_save;
+    float* b_save;
+    int* status;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Byte offset in a tile with R rows per box of the bf16 element (row r, channel c).
+__device__ __forceinline__ int sw_elem(int R, int r, int c) {
+    return (c >> 6) * R * 128 + r * 128 + (((((c & 63) >> 3) ^ (r & 7))) << 4) + (c & 7) * 2;
+}
+
+struct Unit {
+    int b, h, n;
+    long long row0, s_elem;
+};
+__device__ __forceinline__ Unit unit_of(const VParams& p, long long u) {
+    Unit x;
+    x.b = (int)(u / p.H);
+    x.h = (int)(u % p.H);
+    const int r0 = p.cu[x.b];
+    x.row0 = r0;
+    x.n = p.cu[x.b + 1] - r0;
+    x.s_elem = p.state_off[x.b] + (long long)x.h * DV * DK;
+    return x;
+}
+
+// The unit's raw rows: q, k, v (256 bytes a row), g (512), beta; rows past the window's end become zero.
+__device__ __forceinline__ void fetch_rows(const VParams& p, unsigned char* smem, const Unit& un, int t) {
+    const int n = min(max(un.n, 0), WIN);
+    unsigned char* raw = smem + vRaw;
+    for (int e = t; e < WIN * 16; e += kVThreads) {  // 16-byte pieces of the bf16 rows
+        const int r = e >> 4, pc = e & 15;
+        const long long at = ((un.row0 + r) * p.H + un.h) * DK + pc * 8;
+        if (r < n) {
+            cp_async16(raw + rQ + e * 16, p.q + at);
+            cp_async16(raw + rK + e * 16, p.k + at);
+            cp_async16(raw + rV + e * 16, p.v + at);
+        } else {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(raw + rQ + e * 16) = z;
+            *reinterpret_cast<uint4*>(raw + rK + e * 16) = z;
+            *reinterpret_cast<uint4*>(raw + rV + e * 16) = z;
+        }
+    }
+    for (int e = t; e < WIN * 32; e += kVThreads) {
+        const int r = e >> 5, pc = e & 31;
+        if (r < n) cp_async16(raw + rG + e * 16, p.g + ((un.row0 + r) * p.H + un.h) * DK + pc * 4);
+        else *reinterpret_cast<uint4*>(raw + rG + e * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if (t < WIN) reinterpret_cast<float*>(raw + rB)[t] = t < n ? p.beta[(un.row0 + t) * p.H + un.h] : 0.0f;
+    cp_async_commit();
+}
+// The unit's state, 2,048 pieces of 16 bytes, into the swizzled tile.
+__device__ __forceinline__ void fetch_state(const VParams& p, unsigned char* smem, const Unit& un, int t) {
+    const uint16_t* src = p.state + un.s_elem;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int e = t + i * kVThreads, v = e >> 4, pk = e & 15;
+            cp_async16(smem + vS + (pk >> 3) * 16384 + v * 128 + (((pk & 7) ^ (v & 7)) << 4), src + (long long)e * 8);
+        }
+    } else {  // a state that is not 16-byte aligned: element by element
+        for (int e = t; e < DV * DK; e += kVThreads) *reinterpret_cast<uint16_t*>(smem + vS + sw_elem(DV, e >> 7, e & 127)) = src[e];
+    }
+    cp_async_commit();
+}
+
+__global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_constant__ VParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + vBar);
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + vCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    if (t == 0) {
+        mbar_init(bar, 1);
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, kVCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+    uint32_t phase = 0;
+    float* Lf = reinterpret_cast<float*>(smem + vL);
+    float* Mf = reinterpret_cast<float*>(smem + vM);
+    float* Tp = reinterpret_cast<float*>(smem + vTp);
+    float* betas = reinterpret_cast<float*>(smem + vBeta);
+
+    long long u = blockIdx.x;
+    if (u < p.units) {
+        const Unit first = unit_of(p, u);
+        fetch_rows(p, smem, first, t);
+        fetch_state(p, smem, first, t);
+    }
+    for (; u < p.units; u += gridDim.x) {
+        const Unit un = unit_of(p, u);
+        const long long u_next = u + gridDim.x;
+        const bool more = u_next < p.units;
+        Unit nxt = un;
+        if (more) nxt = unit_of(p, u_next);
+        if (un.n > WIN && t == 0) atomicCAS(p.status, 0, kStatusVerifyWindow);
+        const int n = min(max(un.n, 0), WIN);
+
+        cp_async_wait<1>();  // this unit's rows have landed (its state may still be on the way)
+        __syncthreads();
+
+        // ---- A. thread = channel c: the decay scan, the operand tiles, the replay saves ----------------------------------
+        float kg[WIN], vv[WIN];
+        {
+            const int c = t;
+            const unsigned char* raw = smem + vRaw;
+            float G[WIN], acc = 0.0f;
+#pragma unroll
+            for (int r = 0; r < WIN; ++r) {
+                acc += reinterpret_cast<const float*>(raw + rG)[r * DK + c];
+                G[r] = acc;
+            }
+            const float gm = G[WIN / 2];
+            float amax = 0.0f;
+#pragma unroll
+            for (int r = 0; r < WIN; ++r) {
+                const float kf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + rK)[r * DK + c]);
+                const float qf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + rQ)[r * DK + c]);
+                const uint16_t vb = reinterpret_cast<const uint16_t*>(raw + rV)[r * DK + c];
+                const float a = __expf(G[r] - gm), e = __expf(G[r]);
+                amax = fmaxf(amax, a);
+                kg[r] = kf * e;
+                vv[r] = bf16_bits_to_f32(vb);
+                *reinterpret_cast<uint16_t*>(smem + vKgb + sw_elem(WIN, r, c)) = f32_to_bf16_bits(kf * a);
+                *reinterpret_cast<uint16_t*>(smem + vQgb + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * a);
+                *reinterpret_cast<uint16_t*>(smem + vKc + sw_elem(WIN, r, c)) = f32_to_bf16_bits(kf * __fdividef(1.0f, a));
+                *reinterpret_cast<uint16_t*>(smem + vQg + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * e);
+                if (r < n && p.k_save != nullptr) {
+                    const long long at = ((un.row0 + r) * p.H + un.h) * DK + c;
+                    p.k_save[at] = kf;
+                    p.v_save[at] = vb;
+                    p.g_save[at] = expf(reinterpret_cast<const float*>(raw + rG)[r * DK + c]);
+                }
+            }
+            if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+            if (t < WIN) {
+                const float bt = reinterpret_cast<const float*>(raw + rB)[t];
+                betas[t] = bt;
+                if (t < n && p.b_save != nullptr) p.b_save[(un.row0 + t) * p.H + un.h] = bt;
+            }
+        }
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        tc::fence_after_sync();
+        // The raw rows are consumed: the next unit's may come in.
+        if (more) fetch_rows(p, smem, nxt, t);
+        else cp_async_commit();
+
+        // ---- B. L^T and M^T -------------------------------------------------------------------------------------------------
+        if (t == 0) {
+            constexpr uint32_t id = tc::idesc_bf16(128, WIN, 0, 0, 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm, tc::desc_sw128_kmajor(smem + vKc, WIN, k0), tc::desc_sw128_kmajor(smem + vKgb, WIN, k0), id, k0 > 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + 16, tc::desc_sw128_kmajor(smem + vKc, WIN, k0), tc::desc_sw128_kmajor(smem + vQgb, WIN, k0), id, k0 > 0);
+            tc::mma_commit(bar);
+            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+        }
+        bool ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
+        phase ^= 1u;
+        if (!__syncthreads_and(ok)) break;
+        tc::fence_after_sync();
+        if (warp == 0) {  // lanes 0..15 hold column j of L and of M; tensor-memory column = row i
+            uint32_t l16[16], m16[16];
+            tc::tmem_ld16(tc::tmem_addr(tm, 0, 0), l16);
+            tc::tmem_ld16(tc::tmem_addr(tm, 0, 16), m16);
+            tc::tmem_ld_wait();
+            if (lane < WIN) {
+                const int j = lane;
+#pragma unroll
+                for (int i = 0; i < WIN; ++i) {
+                    Lf[i * 17 + j] = i > j ? betas[i] * __uint_as_float(l16[i]) : 0.0f;
+                    Mf[i * WIN + j] = i >= j ? __uint_as_float(m16[i]) : 0.0f;
+                }
+            }
+            __syncwarp();
+            // T = (I + L)^-1, one thread per column (a column needs only its own earlier rows); T' = T diag(beta).
+            if (lane < WIN) {
+                const int j = lane;
+                float tcol[WIN];
+                const float bj = betas[j];
+#pragma unroll
+                for (int i = 0; i < WIN; ++i) {
+                    float a0 = i == j ? 1.0f : 0.0f, a1 = 0.0f;
+#pragma unroll
+                    for (int m = 0; m < i; ++m) {
+                        if (m & 1) a1 = fmaf(-Lf[i * 17 + m], tcol[m], a1);
+                        else a0 = fmaf(-Lf[i * 17 + m], tcol[m], a0);
+                    }
+                    tcol[i] = a0 + a1;
+                    Tp[i * WIN + j] = tcol[i] * bj;
+                }
+            }
+        }
+        tc::fence_before_sync();
+        __syncthreads();
+        tc::fence_after_sync();
+
+        // ---- C. W = T' Kg into its tile (thread = channel), U = T' V in registers (thread = value channel) ------------------------
+        float U[WIN];
+        {
+#pragma unroll
+            for (int i = 0; i < WIN; ++i) {
+                float w = 0.0f, uu = 0.0f;
+#pragma unroll
+                for (int j = 0; j <= i; ++j) {
+                    const float tp = Tp[i * WIN + j];
+                    w = fmaf(tp, kg[j], w);
+                    uu = fmaf(tp, vv[j], uu);
+                }
+                U[i] = uu;
+                *reinterpret_cast<uint16_t*>(smem + vW + sw_elem(WIN, i, t)) = f32_to_bf16_bits(w);
+            }
+        }
+        cp_async_wait<1>();  // this unit's state has landed (the next unit's rows may still be on the way)
+        fence_proxy_async_smem();
+        tc::fence_before_sync();
+        __syncthreads();
+        tc::fence_after_sync();
+
+        // ---- D. (W S)^T and (Qg S)^T: the state tile as it lies in memory is the M operand ---------------------------------------
+        if (t == 0) {
+            constexpr uint32_t id = tc::idesc_bf16(128, WIN, 0, 0, 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm, tc::desc_sw128_kmajor(smem + vS, DV, k0), tc::desc_sw128_kmajor(smem + vW, WIN, k0), id, k0 > 0);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + 16, tc::desc_sw128_kmajor(smem + vS, DV, k0), tc::desc_sw128_kmajor(smem + vQg, WIN, k0), id, k0 > 0);
+            tc::mma_commit(bar);
+            atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+        }
+        ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
+        phase ^= 1u;
+        if (!__syncthreads_and(ok)) break;
+        tc::fence_after_sync();
+        // The state tile is consumed: the next unit's may come in.
+        if (more) fetch_state(p, smem, nxt, t);
+        else cp_async_commit();
+
+        // ---- E. D = U - W S,  O = Qg S + M D; thread = value channel = its tensor-memory lane -----------------------------------------
+        {
+            uint32_t ws[16], qs[16];
+            tc::tmem_ld16(tc::tmem_addr(tm, warp, 0), ws);
+            tc::tmem_ld16(tc::tmem_addr(tm, warp, 16), qs);
+            tc::tmem_ld_wait();
+            float D[WIN];
+#pragma unroll
+            for (int j = 0; j < WIN; ++j) D[j] = U[j] - __uint_as_float(ws[j]);
+#pragma unroll
+            for (int i = 0; i < WIN; ++i) {
+                float o = __uint_as_float(qs[i]);
+#pragma unroll
+                for (int j = 0; j <= i; ++j) o = fmaf(Mf[i * WIN + j], D[j], o);
+                if (i < n) p.out[((un.row0 + i) * p.H + un.h) * DV + t] = f32_to_bf16_bits(o);
+            }
+        }
+        tc::fence_before_sync();  // the next unit's products overwrite these tensor-memory columns
+    }
+    cp_async_wait<0>();
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tm, kVCols);
+}
+
+}  // namespace
+
+// Whether the chunked verify can take this call: bf16 states, no state written, no fused norm, 16-byte aligned rows.
+int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+                          const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, const int64_t* state_off,
+                          glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(verify_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured_dev = dev;
+    }
+    VParams p{};
+    p.H = heads;
+    p.units = (long long)heads * batch;
+    p.cu = cu_rows;
+    p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta;
+    p.state = reinterpret_cast<const uint16_t*>(state_in);
+    p.state_off = reinterpret_cast<const long long*>(state_off);
+    p.out = out;
+    p.k_save = k_save; p.v_save = v_save; p.g_save = g_save; p.b_save = b_save;
+    p.status = status_word();
+    if (p.status == nullptr) return (int)cudaErrorUnknown;
+    const long long cap = 3LL * sm_count();
+    verify_tc_kernel<<<(unsigned)(p.units < cap ? p.units : cap), kVThreads, kVSmem, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace kda

@@ -222,6 +222,13 @@ int glm53f_kda_prefill_batch_bf16state(int32_t heads, int32_t batch, const int32
  * =================================================================================================== */
 
 #define GLM53F_KDA_CORE_L2NORM 1
+/* glm53f_kda_core_verify_batch only: compute a verify window's outputs as one 16-row chunk on the tensor cores.  The
+ * state is read once instead of being walked row by row; the outputs then agree with the serial steps' to the rounding
+ * of bf16 operands (max-abs 2e-2, rel-L2 5e-3) instead of bit for bit, while the replay saves are written exactly as
+ * without the flag, so a commit still leaves the states of serial decode steps.  Takes windows of up to 16 rows
+ * (a longer one records status 122 and only its first 16 rows are computed), bf16 states, state_out == NULL, no gate and
+ * no GLM53F_KDA_CORE_L2NORM; any other call ignores the flag and runs the exact form. */
+#define GLM53F_KDA_CORE_TENSOR 2
 
 /* One recurrent step per row, rows of request b run in order from its state (decode: one row per request). */
 int glm53f_kda_core_decode_batch(int32_t heads, int32_t batch, const int32_t* cu_rows,

@@ -703,7 +703,11 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, 
     full = torch.empty((tokens, HEADS, DK), dtype=torch.bfloat16, device="cuda") if world > 1 else None
     # Every rank's full output buffer mapped into every rank: the prefill kernel stores its heads' rows into all of them.
     fused = par.GatheredOutput(tokens, HEADS) if world > 1 else None
-    # Few chains (one sequence x this rank's heads): the two-pass form over a workspace keeps every SM busy.
+    # Few chains (one sequence x this rank's heads): the two-pass form over a workspace keeps every SM busy.  With 32 or
+    # fewer chains a workspace that holds every chunk of the sequence lets the kernel cut each chain into segments that
+    # are walked at the same time (the scan over segments), which is what shortens the serial walk when heads are sharded.
+    if ws_chunks > 0 and world > 1:
+        ws_chunks = (tokens + 63) // 64 + 64
     ws = torch.empty(core.prefill_workspace_bytes(hl, 1, ws_chunks), dtype=torch.uint8, device="cuda") if ws_chunks > 0 else None
 
     def one_pass(gather):
@@ -755,7 +759,9 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, 
     gbs = tokens * PREFILL_BYTES_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e9      # per GPU
     tflops = tokens * PREFILL_FLOP_PER_TOKEN * (hl / HEADS) / (ms_compute * 1e-3) / 1e12  # per GPU
     chunks = (tokens + 63) // 64
-    if ws_chunks >= 2:    # workspace halves: one launch per segment of ws_chunks // 2 chunks, plus the last state role
+    if world > 1 and ws_chunks > chunks:  # the scan over segments: intra role, two passes of walks, the composition
+        kernels_per_pass = 4
+    elif ws_chunks >= 2:  # workspace halves: one launch per segment of ws_chunks // 2 chunks, plus the last state role
         kernels_per_pass = (chunks + ws_chunks // 2 - 1) // (ws_chunks // 2) + 1
     else:                 # one chunk per launch pair, or the single-pass kernel
         kernels_per_pass = 2 * chunks if ws_chunks == 1 else 1

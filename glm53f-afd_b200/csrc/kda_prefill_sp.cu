@@ -20,6 +20,8 @@
 // the 2,176 the reference's prefill workspace formula provides (kernels/kda_prefill.cu:40-43, 695-698).  The last
 // 256 bytes of the workspace hold the two item counters.
 
+#include <cstdlib>
+
 #include <cuda.h>
 
 #include "common.cuh"
@@ -74,6 +76,16 @@ struct SpParams {
     unsigned int* counters;  // [2] item counters: this launch hands items out of counters[ctr], and zeroes the other
     int ctr;
     int* status;
+    // The scan over segments of the sequence (scan_pass != 0; FP32 states; the workspace holds every chunk).  Segment s of
+    // a chain covers chunks [s * scan_chunks, (s + 1) * scan_chunks).
+    //   pass 1  blocks (chain, s < K - 1, kind): the walk of segment s without outputs, from the zero state (kind 0: its
+    //           end state is the segment's offset B_s) and from the identity with U = 0 (kind 1: its end state is the
+    //           segment's transition A_s), written to scan_ab
+    //   pass 2  blocks (chain, s): the walk of segment s with outputs from its true incoming state scan_start (composed
+    //           from the A_s, B_s between the two passes); the last segment writes the final state
+    int scan_pass, scan_k, scan_chunks;
+    float* scan_ab;     // [chain][K - 1][2][128 x 128]: B_s, A_s in the state's layout
+    float* scan_start;  // [chain][K][128 x 128]: the state before each segment (segment 0: unused, the caller's state)
 };
 
 __device__ __forceinline__ unsigned char* slot_of(unsigned char* ws, int seg_chunks, int chain, int jj) {
@@ -515,8 +527,19 @@ constexpr uint32_t tS = 0, tQS = 128, tD = 256, tQS1 = 384;  // QS/O accumulator
 // NV = the value channels this block owns (all 128, or 64: a chain's value columns never interact, so two blocks can
 // share a chain when chains are few and the serial walk over the chunks is what takes the time); value channels
 // [vpart * NV, vpart * NV + NV).  A warp then covers C = NV / 4 accumulator columns.
+// What one walk of the state role covers: chunks [ja, jb) of its chain, where the state comes from and goes to, whether
+// U takes part (not in the walk that yields a segment's transition) and whether outputs are produced.
+struct Walk {
+    int ja, jb;
+    int init;          // 0: the state buffer (state_in for the first chunk of a sequence, else state_out); 1: zero; 2: identity; 3: FP32 `from`
+    const float* from;
+    int fin;           // where the end state goes: 0 state_out, 1 the FP32 buffer `to`, 2 nowhere
+    float* to;
+    bool use_u, emit;
+};
+
 template <int NV>
-__device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain, const int vpart) {
+__device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_t tm, const int chain, const int vpart, const Walk wk) {
     constexpr int C = NV / 4, CELLS = C / 8;
     const int v0 = vpart * NV;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + oBarsState);  // [3]
@@ -532,12 +555,18 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
     const long long row0 = p.cu[b];
     const int T = p.cu[b + 1] - p.cu[b];
     const int nch = (T + CH - 1) / CH;
-    const int j0 = p.state_chunk0, j1 = min(nch, p.state_chunk0 + p.seg_chunks);
+    const int j0 = min(wk.ja, nch), j1 = min(nch, wk.jb);
     const long long s_elem = p.state_off[b] + (long long)h * DV * DK;
-    // A chain with no chunk in this segment: only the first segment has anything to do (an empty sequence copies its state).
-    if (j0 >= j1 && !(j0 == 0 && p.state_out != p.state_in)) return;
+    // A chain with no chunk in this range: only the first segment has anything to do (an empty sequence copies its state);
+    // a scan walk always delivers its end state.
+    if (p.scan_pass == 0 && j0 >= j1 && !(j0 == 0 && p.state_out != p.state_in)) return;
     const WaitCtx ctx{ctl, ctl + 1, p.status};
 
+    if (warp == kOutWarp && !wk.emit) {
+        tc::fence_before_sync();
+        __syncthreads();
+        return;
+    }
     if (warp == kOutWarp) {
         // The output warp: each finished tile of rows goes to the shard-local `out` and, for a head-sharded launch, into
         // every rank's full buffer -- the all-gather, done here: a peer's buffer is reached over NVLink.  A full chunk
@@ -578,7 +607,7 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         if (lane == 0) {
             uint32_t ph = 1;  // the empty barriers start released
             for (int j = j0; j < j1; ++j) {
-                const unsigned char* slot = slot_of(p.ws_state, p.seg_chunks, chain, j - j0);
+                const unsigned char* slot = slot_of(p.ws_state, p.seg_chunks, chain, j - p.state_chunk0);
                 if (!mbar_wait(&empty[0], ph, ctx, kStatusWaitPrefill)) break;
                 mbar_arrive_expect_tx(&full[0], 2 * kTile + 512);
                 bulk_load(smem + sSlot + wQg, slot + wQg, 2 * kTile, &full[0]);
@@ -643,8 +672,9 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         const uint32_t tO = (c & 1) ? tQS1 : tQS;
         mma_issue([&] {
             constexpr uint32_t id = tc::idesc_bf16(64, NV, 0, 1, 0), idn = tc::idesc_bf16(64, NV, 0, 1, 1);
-            for (int k0 = 0; k0 < DK; k0 += 16)
-                tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
+            if (wk.emit)
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm + tO, tc::desc_kmajor_bf16(smem + sSlot + wQg, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), id, k0 > 0);
             for (int k0 = 0; k0 < DK; k0 += 16)
                 tc::mma_bf16(tm + tD, tc::desc_kmajor_bf16(smem + sSlot + wW, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sS16, 128, 0, k0), idn, k0 > 0);
         });
@@ -657,8 +687,13 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         uint32_t r[C];
 #pragma unroll
         for (int j = 0; j < C; ++j) {
-            const long long at = s_elem + (long long)(v0 + cg * C + j) * DK + lane_row128;
-            const float x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
+            const int vch = v0 + cg * C + j;
+            const long long at = s_elem + (long long)vch * DK + lane_row128;
+            float x;
+            if (wk.init == 1) x = 0.0f;
+            else if (wk.init == 2) x = vch == lane_row128 ? 1.0f : 0.0f;
+            else if (wk.init == 3) x = wk.from[vch * DK + lane_row128];
+            else x = p.state_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[at]) : reinterpret_cast<const float*>(src)[at];
             r[j] = __float_as_uint(x);
         }
         tc::tmem_st<C>(tc::tmem_addr(tm, quad, tS + cg * C), r);
@@ -693,8 +728,8 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj) {
                         float h0, l0, h1, l1;
-                        tc::split_bf16(uu[2 * jj] + __uint_as_float(r[cc * 8 + 2 * jj]), h0, l0);
-                        tc::split_bf16(uu[2 * jj + 1] + __uint_as_float(r[cc * 8 + 2 * jj + 1]), h1, l1);
+                        tc::split_bf16((wk.use_u ? uu[2 * jj] : 0.0f) + __uint_as_float(r[cc * 8 + 2 * jj]), h0, l0);
+                        tc::split_bf16((wk.use_u ? uu[2 * jj + 1] : 0.0f) + __uint_as_float(r[cc * 8 + 2 * jj + 1]), h1, l1);
                         wh[jj] = tc::bf16x2(h0, h1);
                         wl[jj] = tc::bf16x2(l0, l1);
                     }
@@ -712,8 +747,9 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
             constexpr uint32_t idm = tc::idesc_bf16(64, NV, 1, 1, 0), ids = tc::idesc_bf16(128, NV, 1, 1, 0);  // M arrives with its rows contiguous
             const unsigned char* kdhi = smem + sSlot + wKdHi;
             const unsigned char* kdlo = smem + sSlot + wKdLo;
-            for (int k0 = 0; k0 < CH; k0 += 16)
-                tc::mma_bf16(tm + tO, tc::desc_mnmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), idm, true);
+            if (wk.emit)
+                for (int k0 = 0; k0 < CH; k0 += 16)
+                    tc::mma_bf16(tm + tO, tc::desc_mnmajor_bf16(smem + sSlot + wMm, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), idm, true);
             for (int k0 = 0; k0 < CH; k0 += 16)
                 tc::mma_bf16(tm + tS, tc::desc_mnmajor_bf16(kdhi, CH, 0, k0), tc::desc_mnmajor_bf16(smem + sDhi, CH, 0, k0), ids, true);
             for (int k0 = 0; k0 < CH; k0 += 16)
@@ -728,7 +764,7 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
         if (j + 1 < j1 && !begin_chunk(c + 1)) { alive = false; break; }
 
         // ---- outputs: bf16(y), or the gated RMSNorm of bf16(y) ------------------------------------------------------------------
-        {
+        if (wk.emit) {
             uint32_t r[C];
             tc::tmem_ld<C>(tc::tmem_addr(tm, quad, tO + cg * C), r);
             tc::tmem_ld_wait();
@@ -779,7 +815,9 @@ __device__ void state_role(const SpParams& p, unsigned char* smem, const uint32_
 #pragma unroll
         for (int j = 0; j < C; ++j) {
             const long long at = s_elem + (long long)(v0 + cg * C + j) * DK + lane_row128;
-            if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
+            if (wk.fin == 2) continue;
+            if (wk.fin == 1) wk.to[(v0 + cg * C + j) * DK + lane_row128] = __uint_as_float(r[j]);
+            else if (p.state_bf16) reinterpret_cast<uint16_t*>(p.state_out)[at] = f32_to_bf16_bits(__uint_as_float(r[j]));
             else reinterpret_cast<float*>(p.state_out)[at] = __uint_as_float(r[j]);
         }
     }
@@ -808,15 +846,67 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tm = *tmem_slot;
-    if (p.has_state && blockIdx.x < (unsigned)(p.batch * p.H * p.parts)) {
-        if (p.parts == 2) state_role<64>(p, smem, tm, (int)(blockIdx.x >> 1), (int)(blockIdx.x & 1));
-        else state_role<DV>(p, smem, tm, (int)blockIdx.x, 0);
+    const int chains = p.batch * p.H;
+    if (p.scan_pass == 1) {  // (chain, segment s < K - 1, kind): the segment's offset and transition
+        const int kind = blockIdx.x & 1, sg = (blockIdx.x >> 1) % (p.scan_k - 1), chain = (blockIdx.x >> 1) / (p.scan_k - 1);
+        if (chain < chains) {
+            const Walk wk{sg * p.scan_chunks, (sg + 1) * p.scan_chunks, kind ? 2 : 1, nullptr, 1,
+                          p.scan_ab + (((size_t)chain * (p.scan_k - 1) + sg) * 2 + kind) * DV * DK, kind == 0, false};
+            state_role<DV>(p, smem, tm, chain, 0, wk);
+        }
+    } else if (p.scan_pass == 2) {  // (chain, segment): the walk with outputs from the segment's true incoming state
+        const int sg = blockIdx.x % p.scan_k, chain = blockIdx.x / p.scan_k;
+        if (chain < chains) {
+            // Only the last segment delivers the sequence's final state; the others end where the next one starts.
+            const bool last = sg == p.scan_k - 1;
+            const Walk wk{sg * p.scan_chunks, last ? 0x7fffffff : (sg + 1) * p.scan_chunks, sg == 0 ? 0 : 3,
+                          p.scan_start + ((size_t)chain * p.scan_k + sg) * DV * DK, last ? 0 : 2, nullptr, true, true};
+            state_role<DV>(p, smem, tm, chain, 0, wk);
+        }
+    } else if (p.has_state && blockIdx.x < (unsigned)(chains * p.parts)) {
+        const Walk wk{p.state_chunk0, p.state_chunk0 + p.seg_chunks, 0, nullptr, 0, nullptr, true, true};
+        if (p.parts == 2) state_role<64>(p, smem, tm, (int)(blockIdx.x >> 1), (int)(blockIdx.x & 1), wk);
+        else state_role<DV>(p, smem, tm, (int)blockIdx.x, 0, wk);
         tc::fence_after_sync();
     }
     if (p.has_intra && ctl[1] == 0u) intra_role(p, smem, tm);
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc::tmem_dealloc(tm, kTmemCols);
+}
+
+// Between the two scan passes: the state before every segment, S_start[s + 1] = A_s S_start[s] + B_s in FP32, from the
+// caller's state.  A state's value columns never mix, so a block owns eight of them (held in shared memory across the
+// segments) and a thread one key channel: acc[v] += A_s[k][k'] S[k'][v] with A_s read along k (coalesced; A_s lies in
+// the state's layout, entry [k'][k]).
+__global__ void __launch_bounds__(128) scan_compose_kernel(const __grid_constant__ SpParams p) {
+    __shared__ float S[8][DK];
+    const int chain = blockIdx.x >> 4, v0 = (blockIdx.x & 15) * 8, k = threadIdx.x;
+    const int b = chain / p.H, h = chain % p.H;
+    const float* s0 = reinterpret_cast<const float*>(p.state_in) + p.state_off[b] + (long long)h * DV * DK;
+#pragma unroll
+    for (int vi = 0; vi < 8; ++vi) S[vi][k] = s0[(v0 + vi) * DK + k];
+    __syncthreads();
+    for (int sg = 0; sg + 1 < p.scan_k; ++sg) {
+        const float* B = p.scan_ab + ((size_t)chain * (p.scan_k - 1) + sg) * 2 * DV * DK;
+        const float* A = B + DV * DK;
+        float acc[8];
+#pragma unroll
+        for (int vi = 0; vi < 8; ++vi) acc[vi] = B[(v0 + vi) * DK + k];
+        for (int kp = 0; kp < DK; ++kp) {
+            const float a = A[kp * DK + k];
+#pragma unroll
+            for (int vi = 0; vi < 8; ++vi) acc[vi] = fmaf(a, S[vi][kp], acc[vi]);
+        }
+        __syncthreads();
+        float* out = p.scan_start + ((size_t)chain * p.scan_k + sg + 1) * DV * DK;
+#pragma unroll
+        for (int vi = 0; vi < 8; ++vi) {
+            S[vi][k] = acc[vi];
+            out[(v0 + vi) * DK + k] = acc[vi];
+        }
+        __syncthreads();
+    }
 }
 
 }  // namespace
@@ -918,6 +1008,48 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
     cudaError_t e = cudaMemsetAsync(p.counters, 0, 2 * sizeof(unsigned int), stream);
     if (e != cudaSuccess) return (int)e;
     const long long sms = sm_count();
+    // Few chains and a long sequence: the serial walk over a chain's chunks is the critical path whatever the number of
+    // idle SMs.  The recurrence is affine in the state (S_end = A S_start + B over any run of chunks), so the sequence is
+    // cut into K segments that are walked at the same time: once from the zero state and once from the identity without
+    // U (their end states are B and A), then, after the K - 1 compositions, once more from the true incoming states with
+    // the outputs.  Needs FP32 states (a bf16 state is rounded every chunk, which is not affine) and a workspace that
+    // holds every chunk of the call plus (3K - 2) states per chain.  K follows from the number of chains, the SM count and
+    // the length (or GLM53F_KDA_PREFILL_SEGMENTS); the results depend on K, not otherwise on the workspace size.
+    {
+        long long K = 1;
+        if (const char* env = getenv("GLM53F_KDA_PREFILL_SEGMENTS")) K = atoll(env);
+        else if (chains <= 16) {  // measured, 2^20 tokens: 8 chains 41.0 -> 17.0 ms, 16 chains 42.1 -> 33.8 ms, 32 chains 55.3 -> 61.9 ms
+            const long long ka = sms / (2 * chains) + 1, kc = sms / chains;
+            K = ka < kc ? ka : kc;
+            if (K > 16) K = 16;
+            if (K > need / 32) K = need / 32;  // a segment of fewer than 32 chunks is not worth three walks
+        }
+        if (K > need) K = need;
+        const long long scratch = chains * (3 * K - 2) * (long long)(DV * DK * sizeof(float));
+        if (K >= 2 && !bf16_state && chains * need * kSlotBytes + scratch <= usable) {
+            p.seg_chunks = (int)need;
+            p.parts = 1;
+            p.ws_intra = p.ws_state = base;
+            p.intra_chunk0 = p.state_chunk0 = 0;
+            p.ctr = 0;
+            p.scan_k = (int)K;
+            p.scan_chunks = (int)((need + K - 1) / K);
+            p.scan_ab = reinterpret_cast<float*>(base + chains * need * kSlotBytes);
+            p.scan_start = p.scan_ab + chains * (K - 1) * 2 * DV * DK;
+            p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
+            const long long items = chains * need;
+            prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, stream>>>(p);
+            if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+            p.has_intra = 0; p.has_state = 1; p.scan_pass = 1;
+            prefill_sp_kernel<<<(unsigned)(2 * (K - 1) * chains), kThreadsSp, kSmemSp, stream>>>(p);
+            if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+            scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, stream>>>(p);
+            if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+            p.scan_pass = 2;
+            prefill_sp_kernel<<<(unsigned)(K * chains), kThreadsSp, kSmemSp, stream>>>(p);
+            return (int)cudaGetLastError();
+        }
+    }
     const long long segs = need > 0 ? (need + seg - 1) / seg : 0;
     int launch_no = 0;
     auto launch = [&](long long intra_seg, long long state_seg) -> int {

@@ -401,3 +401,26 @@ def test_core_rejections(G, core, pkg):
     with pytest.raises(core.Invalid):
         core.prefill_varlen(heads, 1, cu, 1, z16, z16, z16, zf, zf, st, off, out=z16, state_out=None)
     assert core.device_status() == 0
+
+
+# The scan over segments of the sequence (few chains, long sequences: each chain is cut into K segments that are walked
+# at the same time, composed, and walked again with the outputs).  K is forced here; the results must stay within the
+# task's tolerances of the FP32 recurrence for every K, agree closely with the unsegmented run, and cover sequences
+# shorter than a segment, empty ones, carried states and the fused all-gather stores.
+@pytest.mark.parametrize("segments", [2, 4, 5, 32])
+def test_prefill_scan_over_segments(G, core, oracle, pkg, segments, monkeypatch):
+    heads, lens = 2, [1100, 300, 0, 64, 2000]
+    carried = [True, False, True, True, False]
+    need = (max(lens) + 63) // 64
+    monkeypatch.setenv("GLM53F_KDA_PREFILL_SEGMENTS", "1")
+    base_out, base_st = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=need + 12)
+    monkeypatch.setenv("GLM53F_KDA_PREFILL_SEGMENTS", str(segments))
+    out, st = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=need + 12)   # against the oracle, inside
+    assert G.max_abs(out, base_out) / G.max_abs(base_out) <= 1.0 / 128.0
+    assert G.rel_l2(st, base_st) <= 3e-4
+    # a workspace that cannot hold every chunk: no scan, the unsegmented run's bits
+    out2, st2 = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=8)
+    small_out, small_st = out2, st2
+    monkeypatch.setenv("GLM53F_KDA_PREFILL_SEGMENTS", "1")
+    out3, st3 = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=8)
+    assert np.array_equal(G.bits(small_out), G.bits(out3)) and np.array_equal(G.bits(small_st), G.bits(st3))

@@ -138,13 +138,14 @@ static_assert(4 * kBox <= kKcBytes && gP + 32 * 32 * 4 <= gKc + kKcBytes && gTp 
 static_assert(kGroups * kGroupBytes <= oCtl, "two groups must fit below the block's control words");
 constexpr uint32_t gcL = 0, gcM = 64, gcW = 0, gcU = 128, kGroupCols = 256;
 
-template <int G>
-__device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* smem, const uint32_t tm_block, const WaitCtx& ctx) {
-    constexpr int BAR = 2 + G;
+// G = 0 or 1, a runtime value: both groups run the same instructions (one copy of this code in the instruction cache).
+__device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* smem, const uint32_t tm_block, const WaitCtx& ctx, const int G) {
+    const int BAR = 2 + G;
     unsigned char* gs = smem + G * kGroupBytes;
     const uint32_t tm = tm_block + G * kGroupCols;
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(gs + gBars);
     uint64_t* bar_mma = bar_raw + 1;
+    uint64_t* bar_lm = bar_raw + 2;  // the eight products of L^T and M^T: eight issuing threads arrive
     uint64_t* bar_free = bar_raw + 3;
     volatile int* item_slot = reinterpret_cast<volatile int*>(gs + gItem);
     float* betas = reinterpret_cast<float*>(gs + gBeta);
@@ -166,7 +167,7 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
             atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
         }
     };
-    uint32_t raw_phase = 0, mma_phase = 0;
+    uint32_t raw_phase = 0, mma_phase = 0, lm_phase = 0;
     auto mma_wait = [&](uint64_t* bar, uint32_t& phase) -> bool {
         if (!mbar_wait(bar, phase, ctx, kStatusWaitPrefill)) return false;
         phase ^= 1u;
@@ -182,52 +183,39 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
         const int chain = item % chains, jj = item / chains;
         unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, jj);
 
-        // ---- 1. cumulative log decay G per key channel, left in the staging boxes in place of g ---------------------------
+        // ---- 1. per key channel: the cumulative log decay; a = exp(G - Gm), every row relative to the middle row of its block of
+        // 16, left in the staging boxes in place of g; then the per-block factor tables.  Thread (part, d): rows 32 part ..
+        // 32 part + 31 of channel d, i.e. row blocks 2 part and 2 part + 1 (a needs nothing from the other half).
         {
             const int part = gt >> 7, d = gt & 127;
             // Row r of this thread's channel: box d / 32, piece (d % 32) / 4 swizzled by r & 7, float d % 4.
             unsigned char* col = gs + gG + (d >> 5) * kBox + part * 32 * 128 + (d & 3) * 4;
             const int pc = (d >> 2) & 7;
-            float* totals = reinterpret_cast<float*>(gs + gTab);
+            float* tmp = reinterpret_cast<float*>(gs + gKb);  // totals [2][128], middles [4][128]: the Kgb tile is not in use yet
             float run[32], acc = 0.0f;
 #pragma unroll
             for (int r = 0; r < 32; ++r) {
                 acc += *reinterpret_cast<const float*>(col + r * 128 + ((pc ^ (r & 7)) << 4));
                 run[r] = acc;
             }
-            totals[part * 128 + d] = acc;
-            group_sync();
-            const float base = part ? totals[d] : 0.0f;
-#pragma unroll
-            for (int r = 0; r < 32; ++r) *reinterpret_cast<float*>(col + r * 128 + ((pc ^ (r & 7)) << 4)) = base + run[r];
-        }
-        group_sync();
-
-        // ---- 2. a = exp(G - Gm) of this thread's row and 32 channels into registers; the per-block factor tables -----------
-        const int r = gt & 63, cq = gt >> 6, J = r >> 4;
-        float a[32];
-        {
-            const int rm = (r & 48) | 8;
+            tmp[part * 128 + d] = acc;
+            tmp[(2 + 2 * part) * 128 + d] = run[8];
+            tmp[(3 + 2 * part) * 128 + d] = run[24];
             float amax = 0.0f;
 #pragma unroll
-            for (int pp = 0; pp < 8; ++pp) {
-                const float4 x = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, cq * 8 + pp));
-                const float4 m = *reinterpret_cast<const float4*>(gs + gG + box_piece(rm, cq * 8 + pp));
-                a[pp * 4 + 0] = __expf(x.x - m.x);
-                a[pp * 4 + 1] = __expf(x.y - m.y);
-                a[pp * 4 + 2] = __expf(x.z - m.z);
-                a[pp * 4 + 3] = __expf(x.w - m.w);
-                amax = fmaxf(fmaxf(fmaxf(a[pp * 4], a[pp * 4 + 1]), fmaxf(a[pp * 4 + 2], a[pp * 4 + 3])), amax);
+            for (int r = 0; r < 32; ++r) {
+                const float av = __expf(run[r] - run[(r & 16) | 8]);
+                amax = fmaxf(amax, av);
+                *reinterpret_cast<float*>(col + r * 128 + ((pc ^ (r & 7)) << 4)) = av;
             }
             // Eight rows of decay must stay below e^85: per-row log decays below about -10.6 (or positive ones) do not.
             if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
-            const int half = gt >> 7, d = gt & 127;
-            const unsigned char* colg = gs + gG + (d >> 5) * kBox + (d & 3) * 4;
-            const int pc = (d >> 2) & 7;
-            auto G_at = [&](int row) { return *reinterpret_cast<const float*>(colg + row * 128 + ((pc ^ (row & 7)) << 4)); };
-            const float gm0 = G_at(8), gm1 = G_at(24), gm2 = G_at(40), gm3 = G_at(56), gl = G_at(63);
+            group_sync();
+            const float base1 = tmp[d];
+            const float gm0 = tmp[2 * 128 + d], gm1 = tmp[3 * 128 + d], gm2 = base1 + tmp[4 * 128 + d], gm3 = base1 + tmp[5 * 128 + d];
+            const float gl = base1 + tmp[128 + d];
             float* tab = reinterpret_cast<float*>(gs + gTab) + d;
-            if (half == 0) {
+            if (part == 0) {
                 tab[(tE0 + 0) * 128] = __expf(gm0); tab[(tE0 + 1) * 128] = __expf(gm1); tab[(tE0 + 2) * 128] = __expf(gm2); tab[(tE0 + 3) * 128] = __expf(gm3);
                 tab[(tEL + 0) * 128] = __expf(gl - gm0); tab[(tEL + 1) * 128] = __expf(gl - gm1);
                 tab[(tEL + 2) * 128] = __expf(gl - gm2); tab[(tEL + 3) * 128] = __expf(gl - gm3);
@@ -238,77 +226,107 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
                 reinterpret_cast<float*>(slot + wEgl)[d] = __expf(gl);
             }
         }
-        group_sync();  // the tables are complete; nobody reads the staged G any more, so the column-side tiles may go over it
+        group_sync();
 
-        // ---- 3. operand tiles.  Row sides Kgb = K a, Qgb = Q a (over Q); Kg = K exp(G) (over K) for W; Qg = Q exp(G), Kdec =
+        // ---- 2. a of this thread's row and 32 channels into registers -----------------------------------------------------------
+        const int r = gt & 63, cq = gt >> 6, J = r >> 4;
+        float a[32];
+#pragma unroll
+        for (int pp = 0; pp < 8; ++pp) {
+            const float4 x = *reinterpret_cast<const float4*>(gs + gG + box_piece(r, cq * 8 + pp));
+            a[pp * 4 + 0] = x.x; a[pp * 4 + 1] = x.y; a[pp * 4 + 2] = x.z; a[pp * 4 + 3] = x.w;
+        }
+        group_sync();  // nobody reads the staged a (or the scan's scratch) any more: the tiles may go over them
+
+        // ---- 3. operand tiles, first those made from k.  Row side Kgb = K a; Kg = K exp(G) (over K) for W; Kdec =
         // K exp(G_last - G) as bf16 hi + lo out to the workspace; column sides K exp(Gm_I - G) into the tiles I >= J.
-        {
-            const float* tabs = reinterpret_cast<const float*>(gs + gTab);
+        const float* tabs = reinterpret_cast<const float*>(gs + gTab);
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const int c = cq * 4 + cc;
-                const uint4 k8 = *reinterpret_cast<const uint4*>(gs + gK + box_piece(r, c));
-                const uint4 q8 = *reinterpret_cast<const uint4*>(gs + gQ + box_piece(r, c));
-                const float4 e0a = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8), e0b = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
-                const float4 ela = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8), elb = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8 + 4);
-                const float E0[8] = {e0a.x, e0a.y, e0a.z, e0a.w, e0b.x, e0b.y, e0b.z, e0b.w};
-                const float EL[8] = {ela.x, ela.y, ela.z, ela.w, elb.x, elb.y, elb.z, elb.w};
-                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
-                uint32_t kg[4], kgb[4], qg[4], qgb[4], kcd[4], dh[4], dl[4];
-                float kc[8];  // K exp(Gm_J - G): the column side inside the row's own block
+        for (int cc = 0; cc < 4; ++cc) {
+            const int c = cq * 4 + cc;
+            const uint4 k8 = *reinterpret_cast<const uint4*>(gs + gK + box_piece(r, c));
+            const float4 e0a = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8), e0b = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+            const float4 ela = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8), elb = *reinterpret_cast<const float4*>(tabs + (tEL + J) * 128 + c * 8 + 4);
+            const float E0[8] = {e0a.x, e0a.y, e0a.z, e0a.w, e0b.x, e0b.y, e0b.z, e0b.w};
+            const float EL[8] = {ela.x, ela.y, ela.z, ela.w, elb.x, elb.y, elb.z, elb.w};
+            const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
+            uint32_t kg[4], kgb[4], kcd[4], dh[4], dl[4];
+            float kc[8];  // K exp(Gm_J - G): the column side inside the row's own block
 #pragma unroll
-                for (int u2 = 0; u2 < 4; ++u2) {
-                    const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
-                    const float qf[2] = {__uint_as_float(qw[u2] << 16), __uint_as_float(qw[u2] & 0xffff0000u)};
-                    float v_kg[2], v_kgb[2], v_qg[2], v_qgb[2], hi[2], lo[2];
+            for (int u2 = 0; u2 < 4; ++u2) {
+                const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
+                float v_kg[2], v_kgb[2], hi[2], lo[2];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const float av = a[cc * 8 + 2 * u2 + u], inva = __fdividef(1.0f, av), e = av * E0[2 * u2 + u];
-                        v_kgb[u] = kf[u] * av;
-                        v_qgb[u] = qf[u] * av;
-                        v_kg[u] = kf[u] * e;
-                        v_qg[u] = qf[u] * e;
-                        kc[2 * u2 + u] = kf[u] * inva;
-                        tc::split_bf16(kc[2 * u2 + u] * EL[2 * u2 + u], hi[u], lo[u]);
-                    }
-                    kg[u2] = tc::bf16x2(v_kg[0], v_kg[1]);
-                    kgb[u2] = tc::bf16x2(v_kgb[0], v_kgb[1]);
-                    qg[u2] = tc::bf16x2(v_qg[0], v_qg[1]);
-                    qgb[u2] = tc::bf16x2(v_qgb[0], v_qgb[1]);
-                    kcd[u2] = tc::bf16x2(kc[2 * u2], kc[2 * u2 + 1]);
-                    dh[u2] = tc::bf16x2(hi[0], hi[1]);
-                    dl[u2] = tc::bf16x2(lo[0], lo[1]);
+                for (int u = 0; u < 2; ++u) {
+                    const float av = a[cc * 8 + 2 * u2 + u], inva = __fdividef(1.0f, av);
+                    v_kgb[u] = kf[u] * av;
+                    v_kg[u] = kf[u] * (av * E0[2 * u2 + u]);
+                    kc[2 * u2 + u] = kf[u] * inva;
+                    tc::split_bf16(kc[2 * u2 + u] * EL[2 * u2 + u], hi[u], lo[u]);
                 }
-                *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
-                *reinterpret_cast<uint4*>(gs + gKb + box_piece(r, c)) = make_uint4(kgb[0], kgb[1], kgb[2], kgb[3]);
-                *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
-                *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
-                *reinterpret_cast<uint4*>(cell(slot + wKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
-                *reinterpret_cast<uint4*>(cell(slot + wKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
-                *reinterpret_cast<uint4*>(gs + gKc + kc_piece(J, r, c)) = make_uint4(kcd[0], kcd[1], kcd[2], kcd[3]);
-                for (int I = J + 1; I < 4; ++I) {  // the later row blocks see this row through exp(Gm_I - Gm_J) <= 1
-                    const float* f = tabs + (tF + I * (I - 1) / 2 + J) * 128 + c * 8;
-                    const float4 fa = *reinterpret_cast<const float4*>(f), fb = *reinterpret_cast<const float4*>(f + 4);
-                    *reinterpret_cast<uint4*>(gs + gKc + kc_piece(I, r, c)) =
-                        make_uint4(tc::bf16x2(kc[0] * fa.x, kc[1] * fa.y), tc::bf16x2(kc[2] * fa.z, kc[3] * fa.w),
-                                   tc::bf16x2(kc[4] * fb.x, kc[5] * fb.y), tc::bf16x2(kc[6] * fb.z, kc[7] * fb.w));
-                }
+                kg[u2] = tc::bf16x2(v_kg[0], v_kg[1]);
+                kgb[u2] = tc::bf16x2(v_kgb[0], v_kgb[1]);
+                kcd[u2] = tc::bf16x2(kc[2 * u2], kc[2 * u2 + 1]);
+                dh[u2] = tc::bf16x2(hi[0], hi[1]);
+                dl[u2] = tc::bf16x2(lo[0], lo[1]);
+            }
+            *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+            *reinterpret_cast<uint4*>(gs + gKb + box_piece(r, c)) = make_uint4(kgb[0], kgb[1], kgb[2], kgb[3]);
+            *reinterpret_cast<uint4*>(cell(slot + wKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+            *reinterpret_cast<uint4*>(cell(slot + wKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+            *reinterpret_cast<uint4*>(gs + gKc + kc_piece(J, r, c)) = make_uint4(kcd[0], kcd[1], kcd[2], kcd[3]);
+            for (int I = J + 1; I < 4; ++I) {  // the later row blocks see this row through exp(Gm_I - Gm_J) <= 1
+                const float* f = tabs + (tF + I * (I - 1) / 2 + J) * 128 + c * 8;
+                const float4 fa = *reinterpret_cast<const float4*>(f), fb = *reinterpret_cast<const float4*>(f + 4);
+                *reinterpret_cast<uint4*>(gs + gKc + kc_piece(I, r, c)) =
+                    make_uint4(tc::bf16x2(kc[0] * fa.x, kc[1] * fa.y), tc::bf16x2(kc[2] * fa.z, kc[3] * fa.w),
+                               tc::bf16x2(kc[4] * fb.x, kc[5] * fb.y), tc::bf16x2(kc[6] * fb.z, kc[7] * fb.w));
             }
         }
         publish();
-        // ---- 3b. L^T and M^T, one block column of 16 rows i at a time: [64 j x 16 i] = column side (tile I) x row side (block I)^T ----
-        mma_issue(bar_mma, [&] {
+        // ---- 3a. L^T, one block column of 16 rows i a warp: [64 j x 16 i] = column side (tile I) x row side (block I)^T.  Eight
+        // threads (lane 0 of every warp) issue the eight small products of L^T and M^T, so none of them issues for long; each
+        // commits to the same barrier, which completes when all eight have.
+        if (lane == 0 && gw < 4) {
             constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
-            for (int I = 0; I < 4; ++I) {
-                const unsigned char* kct = gs + gKc + kc_tile(I);
-                const int R = 16 * (I + 1);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + gcL + 16 * I, tc::desc_sw128_kmajor(kct, R, k0), tc::desc_sw128_kmajor(gs + gKb + I * 2048, CH, k0), id, k0 > 0);
-                for (int k0 = 0; k0 < DK; k0 += 16)
-                    tc::mma_bf16(tm + gcM + 16 * I, tc::desc_sw128_kmajor(kct, R, k0), tc::desc_sw128_kmajor(gs + gQ + I * 2048, CH, k0), id, k0 > 0);
+            const int I = gw;
+            const unsigned char* kct = gs + gKc + kc_tile(I);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + gcL + 16 * I, tc::desc_sw128_kmajor(kct, 16 * (I + 1), k0), tc::desc_sw128_kmajor(gs + gKb + I * 2048, CH, k0), id, k0 > 0);
+            tc::mma_commit(bar_lm);
+            atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
+        }
+        // ---- 3b. the tiles made from q, while L^T runs: row side Qgb = Q a (over Q); Qg = Q exp(G) out to the workspace -------
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            const int c = cq * 4 + cc;
+            const uint4 q8 = *reinterpret_cast<const uint4*>(gs + gQ + box_piece(r, c));
+            const float4 e0a = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8), e0b = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+            const float E0[8] = {e0a.x, e0a.y, e0a.z, e0a.w, e0b.x, e0b.y, e0b.z, e0b.w};
+            const uint32_t qw[4] = {q8.x, q8.y, q8.z, q8.w};
+            uint32_t qg[4], qgb[4];
+#pragma unroll
+            for (int u2 = 0; u2 < 4; ++u2) {
+                const float q0 = __uint_as_float(qw[u2] << 16), q1 = __uint_as_float(qw[u2] & 0xffff0000u);
+                const float a0 = a[cc * 8 + 2 * u2], a1 = a[cc * 8 + 2 * u2 + 1];
+                qgb[u2] = tc::bf16x2(q0 * a0, q1 * a1);
+                qg[u2] = tc::bf16x2(q0 * (a0 * E0[2 * u2]), q1 * (a1 * E0[2 * u2 + 1]));
             }
-        });
-        if (!mma_wait(bar_mma, mma_phase)) break;
+            *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
+            *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+        }
+        publish();
+        // ---- 3c. M^T the same way, by the other four warps ------------------------------------------------------------------------
+        if (lane == 0 && gw >= 4) {
+            constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
+            const int I = gw - 4;
+            const unsigned char* kct = gs + gKc + kc_tile(I);
+            for (int k0 = 0; k0 < DK; k0 += 16)
+                tc::mma_bf16(tm + gcM + 16 * I, tc::desc_sw128_kmajor(kct, 16 * (I + 1), k0), tc::desc_sw128_kmajor(gs + gQ + I * 2048, CH, k0), id, k0 > 0);
+            tc::mma_commit(bar_lm);
+            atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
+        }
+        if (!mma_wait(bar_lm, lm_phase)) break;
 
         // ---- 4. from L^T and M^T (lane = column j, tensor-memory column = row i): L (FP32, strictly lower, times beta_i) into
         // the scratch; M (lower with the diagonal) out as bf16 cells of eight consecutive rows i, [8 cells][64 columns j] ----------
@@ -345,9 +363,9 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
             const float* Lm = reinterpret_cast<const float*>(gs + gL);
             float* Tm = reinterpret_cast<float*>(gs + gT);
             float* Pm = reinterpret_cast<float*>(gs + gP);
-            invert_diag16<kGroupThreads, BAR>(Lm, Tm, gt);
-            invert_level<4, kGroupThreads, BAR>(Lm, Tm, Pm, gt);
-            invert_level<5, kGroupThreads, BAR>(Lm, Tm, Pm, gt);
+            invert_diag16<kGroupThreads>(Lm, Tm, gt, BAR);
+            invert_level<4, kGroupThreads>(Lm, Tm, Pm, gt, BAR);
+            invert_level<5, kGroupThreads>(Lm, Tm, Pm, gt, BAR);
             const int i = gt & 63, cq = gt >> 6;
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
@@ -415,8 +433,7 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
 // chunk arrives by ten tiled tensor copies issued by one lane; a sequence's last, partial chunk is copied by the
 // warp's own loads and stores (rows past the sequence's end are not read, they become zero), so no copy ever reaches
 // past the rows the caller's metadata names.
-template <int G>
-__device__ __forceinline__ void intra_loader(const SpParams& p, unsigned char* smem, const WaitCtx& ctx) {
+__device__ __forceinline__ void intra_loader(const SpParams& p, unsigned char* smem, const WaitCtx& ctx, const int G) {
     unsigned char* gs = smem + G * kGroupBytes;
     uint64_t* bar_raw = reinterpret_cast<uint64_t*>(gs + gBars);
     uint64_t* bar_free = bar_raw + 3;
@@ -499,15 +516,13 @@ __device__ void intra_role(const SpParams& p, unsigned char* smem, const uint32_
     if (tid == 0) {
         for (int g = 0; g < kGroups; ++g) {
             uint64_t* b = reinterpret_cast<uint64_t*>(smem + g * kGroupBytes + gBars);
-            for (int i = 0; i < 4; ++i) mbar_init(b + i, 1);  // raw, mma, (spare), free
+            for (int i = 0; i < 4; ++i) mbar_init(b + i, i == 2 ? 8 : 1);  // raw, mma, L^T/M^T (eight issuers), free
         }
         mbar_init_fence();
     }
     __syncthreads();
-    if (warp == kLoaderWarp) intra_loader<0>(p, smem, ctx);
-    else if (warp == kOutWarp) intra_loader<1>(p, smem, ctx);
-    else if (warp < kGroupThreads / 32) intra_group<0>(p, smem, tm, ctx);
-    else intra_group<1>(p, smem, tm, ctx);
+    if (warp == kLoaderWarp || warp == kOutWarp) intra_loader(p, smem, ctx, warp == kLoaderWarp ? 0 : 1);
+    else intra_group(p, smem, tm, ctx, warp < kGroupThreads / 32 ? 0 : 1);
     tc::fence_before_sync();
     __syncthreads();
 }

@@ -59,9 +59,9 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r) {
 // every sz x sz diagonal block, fills the lower-left sz x sz block of every 2sz x 2sz diagonal block with
 // -T22 (L21 T11).  A thread computes VJ consecutive columns of one row; the loops run over the full block (the
 // triangular halves that are zero cost a few multiply-adds and keep the trip counts fixed and unrolled).
-// NT threads (numbered tid = 0..NT-1) take part and meet at named barrier BAR.
-template <int LG, int NT = kCompute, int BAR = 1>
-__device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* Pm, int tid) {
+// NT threads (numbered tid = 0..NT-1) take part and meet at named barrier `bar`.
+template <int LG, int NT = kCompute>
+__device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* Pm, int tid, int bar = 1) {
     constexpr int sz = 1 << LG, nblk = 32 >> LG, VJ = sz >= 4 ? 4 : sz, cols = sz / VJ, per = sz * cols, total = nblk * per;
     for (int e = tid; e < total; e += NT) {
         const int blk = e / per, rem = e % per, i = rem / cols, j0 = (rem % cols) * VJ;
@@ -85,7 +85,7 @@ __device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* 
 #pragma unroll
         for (int v = 0; v < VJ; ++v) Pm[blk * sz * sz + i * sz + j0 + v] = acc[v];
     }
-    named_bar_sync(BAR, NT);
+    named_bar_sync(bar, NT);
     for (int e = tid; e < total; e += NT) {
         const int blk = e / per, rem = e % per, i = rem / cols, j0 = (rem % cols) * VJ;
         const int c0 = blk * 2 * sz, r0 = c0 + sz;
@@ -108,14 +108,14 @@ __device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* 
 #pragma unroll
         for (int v = 0; v < VJ; ++v) Tm[(r0 + i) * LS + c0 + j0 + v] = -acc[v];
     }
-    named_bar_sync(BAR, NT);
+    named_bar_sync(bar, NT);
 }
 
 // The start of the inverse: the four 16 x 16 diagonal blocks of (I + L)^-1 by forward substitution, one thread per
 // column (a column needs only its own earlier rows, so the 64 threads never talk to each other), while the other
 // threads clear every entry outside those blocks.  Ends with a barrier; levels 4 and 5 of invert_level follow.
-template <int NT = kCompute, int BAR = 1>
-__device__ __forceinline__ void invert_diag16(const float* Lm, float* Tm, int tid) {
+template <int NT = kCompute>
+__device__ __forceinline__ void invert_diag16(const float* Lm, float* Tm, int tid, int bar = 1) {
     if (tid < 64) {
         const int o = (tid >> 4) * 16, j = tid & 15;
         float t[16];
@@ -137,7 +137,7 @@ __device__ __forceinline__ void invert_diag16(const float* Lm, float* Tm, int ti
             if ((i >> 4) != (j >> 4)) Tm[i * LS + j] = 0.0f;
         }
     }
-    named_bar_sync(BAR, NT);
+    named_bar_sync(bar, NT);
 }
 
 }  // namespace pf

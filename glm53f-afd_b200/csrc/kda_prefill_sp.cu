@@ -132,9 +132,9 @@ constexpr int gT = gKc, gL = gT + CH * LS * 4, gP = gL + CH * LS * 4, gTp = gL; 
 static_assert(gTp % 1024 == 0 && gKc % 1024 == 0, "swizzled tiles are 1024-byte aligned");
 // Per-block decay factors, 128 channels each: E0[J] = exp(Gm_J), EL[J] = exp(G_last - Gm_J), F[I(I-1)/2 + J] =
 // exp(Gm_I - Gm_J) for I > J.  The scan's totals use the first two rows before the tables are written.
-constexpr int gTab = gKc + kKcBytes, gBeta = gTab + kTabs * 512, gBars = gBeta + CH * 4, gItem = gBars + 32;
+constexpr int gTab = gKc + kKcBytes, gBeta = gTab + kTabs * 512, gBars = gBeta + CH * 4, gItem = gBars + 32, gGl = gItem + 16;  // gGl: exp(G_last) [128]
 constexpr int kGroupBytes = 114688;
-static_assert(4 * kBox <= kKcBytes && gP + 32 * 32 * 4 <= gKc + kKcBytes && gTp + kTile <= gP && gItem + 16 <= kGroupBytes && kGroupBytes % 1024 == 0, "group map");
+static_assert(4 * kBox <= kKcBytes && gP + 32 * 32 * 4 <= gKc + kKcBytes && gTp + kTile <= gP && gGl + 512 <= kGroupBytes && kGroupBytes % 1024 == 0, "group map");
 static_assert(kGroups * kGroupBytes <= oCtl, "two groups must fit below the block's control words");
 constexpr uint32_t gcL = 0, gcM = 64, gcW = 0, gcU = 128, kGroupCols = 256;
 
@@ -183,6 +183,7 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
         const int chain = item % chains, jj = item / chains;
         unsigned char* slot = slot_of(p.ws_intra, p.seg_chunks, chain, jj);
 
+        bool mild;
         // ---- 1. per key channel: the cumulative log decay; a = exp(G - Gm), every row relative to the middle row of its block of
         // 16, left in the staging boxes in place of g; then the per-block factor tables.  Thread (part, d): rows 32 part ..
         // 32 part + 31 of channel d, i.e. row blocks 2 part and 2 part + 1 (a needs nothing from the other half).
@@ -223,10 +224,17 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
                 tab[(tF + 0) * 128] = __expf(gm1 - gm0);
                 tab[(tF + 1) * 128] = __expf(gm2 - gm0); tab[(tF + 2) * 128] = __expf(gm2 - gm1);
                 tab[(tF + 3) * 128] = __expf(gm3 - gm0); tab[(tF + 4) * 128] = __expf(gm3 - gm1); tab[(tF + 5) * 128] = __expf(gm3 - gm2);
-                reinterpret_cast<float*>(slot + wEgl)[d] = __expf(gl);
+                const float egl = __expf(gl);
+                reinterpret_cast<float*>(slot + wEgl)[d] = egl;
+                reinterpret_cast<float*>(gs + gGl)[d] = egl;
             }
+            mild = gl > -60.0f;
         }
-        group_sync();
+        // A chunk whose whole decay stays above e^-60 in every channel needs no block-wise references: exp(G) and exp(-G) from
+        // the chunk's start are both representable with room for small q and k, one column-side tile serves every row, and L^T,
+        // M^T are one product each.  The group decides together (the barrier carries the vote); the choice depends on the chunk's
+        // own gates only, so it is the same however the call is batched or cut into passes.
+        const bool narrow = named_bar_all(BAR, kGroupThreads, mild);
 
         // ---- 2. a of this thread's row and 32 channels into registers -----------------------------------------------------------
         const int r = gt & 63, cq = gt >> 6, J = r >> 4;
@@ -241,6 +249,41 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
         // ---- 3. operand tiles, first those made from k.  Row side Kgb = K a; Kg = K exp(G) (over K) for W; Kdec =
         // K exp(G_last - G) as bf16 hi + lo out to the workspace; column sides K exp(Gm_I - G) into the tiles I >= J.
         const float* tabs = reinterpret_cast<const float*>(gs + gTab);
+        if (narrow) {
+            // One reference (the chunk's start): Kg = K exp(G) (over K) is the row side of L and the operand of W, Kinv = K exp(-G)
+            // the one column-side tile (the 64-row tile), Kdec = Kinv exp(G_last).
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const int c = cq * 4 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(gs + gK + box_piece(r, c));
+                const float4 e0a = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8), e0b = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+                const float4 gla = *reinterpret_cast<const float4*>(gs + gGl + c * 32), glb = *reinterpret_cast<const float4*>(gs + gGl + c * 32 + 16);
+                const float E0[8] = {e0a.x, e0a.y, e0a.z, e0a.w, e0b.x, e0b.y, e0b.z, e0b.w};
+                const float GL[8] = {gla.x, gla.y, gla.z, gla.w, glb.x, glb.y, glb.z, glb.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
+                uint32_t kg[4], ki[4], dh[4], dl[4];
+#pragma unroll
+                for (int u2 = 0; u2 < 4; ++u2) {
+                    const float kf[2] = {__uint_as_float(kw[u2] << 16), __uint_as_float(kw[u2] & 0xffff0000u)};
+                    float v_kg[2], v_ki[2], hi[2], lo[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float e = a[cc * 8 + 2 * u2 + u] * E0[2 * u2 + u], einv = __fdividef(1.0f, e);
+                        v_kg[u] = kf[u] * e;
+                        v_ki[u] = kf[u] * einv;
+                        tc::split_bf16(kf[u] * (GL[2 * u2 + u] * einv), hi[u], lo[u]);
+                    }
+                    kg[u2] = tc::bf16x2(v_kg[0], v_kg[1]);
+                    ki[u2] = tc::bf16x2(v_ki[0], v_ki[1]);
+                    dh[u2] = tc::bf16x2(hi[0], hi[1]);
+                    dl[u2] = tc::bf16x2(lo[0], lo[1]);
+                }
+                *reinterpret_cast<uint4*>(gs + gK + box_piece(r, c)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(gs + gKc + kc_piece(3, r, c)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(cell(slot + wKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(cell(slot + wKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+            }
+        } else {
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
             const int c = cq * 4 + cc;
@@ -283,16 +326,24 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
                                tc::bf16x2(kc[4] * fb.x, kc[5] * fb.y), tc::bf16x2(kc[6] * fb.z, kc[7] * fb.w));
             }
         }
+        }
         publish();
         // ---- 3a. L^T, one block column of 16 rows i a warp: [64 j x 16 i] = column side (tile I) x row side (block I)^T.  Eight
         // threads (lane 0 of every warp) issue the eight small products of L^T and M^T, so none of them issues for long; each
         // commits to the same barrier, which completes when all eight have.
         if (lane == 0 && gw < 4) {
+            if (narrow) {  // one product, all 64 rows i at once, row side Kg (a commit with nothing pending arrives at once)
+                constexpr uint32_t id64 = tc::idesc_bf16(64, 64, 0, 0, 0);
+                if (gw == 0)
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + gcL, tc::desc_sw128_kmajor(gs + gKc + kc_tile(3), CH, k0), tc::desc_sw128_kmajor(gs + gK, CH, k0), id64, k0 > 0);
+            } else {
             constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
             const int I = gw;
             const unsigned char* kct = gs + gKc + kc_tile(I);
             for (int k0 = 0; k0 < DK; k0 += 16)
                 tc::mma_bf16(tm + gcL + 16 * I, tc::desc_sw128_kmajor(kct, 16 * (I + 1), k0), tc::desc_sw128_kmajor(gs + gKb + I * 2048, CH, k0), id, k0 > 0);
+            }
             tc::mma_commit(bar_lm);
             atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
         }
@@ -312,17 +363,25 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
                 qgb[u2] = tc::bf16x2(q0 * a0, q1 * a1);
                 qg[u2] = tc::bf16x2(q0 * (a0 * E0[2 * u2]), q1 * (a1 * E0[2 * u2 + 1]));
             }
-            *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
+            // narrow: Qg itself is M's row side
+            *reinterpret_cast<uint4*>(gs + gQ + box_piece(r, c)) = narrow ? make_uint4(qg[0], qg[1], qg[2], qg[3]) : make_uint4(qgb[0], qgb[1], qgb[2], qgb[3]);
             *reinterpret_cast<uint4*>(cell(slot + wQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
         }
         publish();
         // ---- 3c. M^T the same way, by the other four warps ------------------------------------------------------------------------
         if (lane == 0 && gw >= 4) {
+            if (narrow) {
+                constexpr uint32_t id64 = tc::idesc_bf16(64, 64, 0, 0, 0);
+                if (gw == 4)
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + gcM, tc::desc_sw128_kmajor(gs + gKc + kc_tile(3), CH, k0), tc::desc_sw128_kmajor(gs + gQ, CH, k0), id64, k0 > 0);
+            } else {
             constexpr uint32_t id = tc::idesc_bf16(64, 16, 0, 0, 0);
             const int I = gw - 4;
             const unsigned char* kct = gs + gKc + kc_tile(I);
             for (int k0 = 0; k0 < DK; k0 += 16)
                 tc::mma_bf16(tm + gcM + 16 * I, tc::desc_sw128_kmajor(kct, 16 * (I + 1), k0), tc::desc_sw128_kmajor(gs + gQ + I * 2048, CH, k0), id, k0 > 0);
+            }
             tc::mma_commit(bar_lm);
             atomicAdd(const_cast<uint32_t*>(ctx.progress), 1u);
         }
@@ -338,12 +397,14 @@ __device__ __forceinline__ void intra_group(const SpParams& p, unsigned char* sm
                 tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg == 0 ? gcL : gcM) + half * 32), rr);
                 tc::tmem_ld_wait();
                 if (lane < 16) {
-                    if (cg == 0) {
-                        float* Lc = reinterpret_cast<float*>(gs + gL) + j;
+                    if (cg == 0) {  // L stays transposed: this thread's column j, 32 consecutive rows i
+                        float* Lt = reinterpret_cast<float*>(gs + gL) + j * LS + half * 32;
 #pragma unroll
-                        for (int i2 = 0; i2 < 32; ++i2) {
-                            const int i = half * 32 + i2;
-                            Lc[i * LS] = i > j ? betas[i] * __uint_as_float(rr[i2]) : 0.0f;
+                        for (int i4 = 0; i4 < 8; ++i4) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(betas + half * 32 + i4 * 4);
+                            const int i = half * 32 + i4 * 4;
+                            *reinterpret_cast<float4*>(Lt + i4 * 4) = make_float4(i > j ? b4.x * __uint_as_float(rr[i4 * 4]) : 0.0f, i + 1 > j ? b4.y * __uint_as_float(rr[i4 * 4 + 1]) : 0.0f,
+                                                                                  i + 2 > j ? b4.z * __uint_as_float(rr[i4 * 4 + 2]) : 0.0f, i + 3 > j ? b4.w * __uint_as_float(rr[i4 * 4 + 3]) : 0.0f);
                         }
                     } else {
 #pragma unroll

@@ -357,12 +357,14 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
             tc::tmem_ld32(tc::tmem_addr(tm, quad, (cg < 2 ? cL : cMm) + half * 32), r);
             tc::tmem_ld_wait();
             if (lane < 16) {
-                if (cg < 2) {
-                    float* Lc = reinterpret_cast<float*>(smem + oL) + j;
+                if (cg < 2) {  // L stays transposed: this thread's column j, 32 consecutive rows i
+                    float* Lt = reinterpret_cast<float*>(smem + oL) + j * LS + half * 32;
 #pragma unroll
-                    for (int i2 = 0; i2 < 32; ++i2) {
-                        const int i = half * 32 + i2;
-                        Lc[i * LS] = i > j ? betas[i] * __uint_as_float(r[i2]) : 0.0f;
+                    for (int i4 = 0; i4 < 8; ++i4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(betas + half * 32 + i4 * 4);
+                        const int i = half * 32 + i4 * 4;
+                        *reinterpret_cast<float4*>(Lt + i4 * 4) = make_float4(i > j ? b4.x * __uint_as_float(r[i4 * 4]) : 0.0f, i + 1 > j ? b4.y * __uint_as_float(r[i4 * 4 + 1]) : 0.0f,
+                                                                              i + 2 > j ? b4.z * __uint_as_float(r[i4 * 4 + 2]) : 0.0f, i + 3 > j ? b4.w * __uint_as_float(r[i4 * 4 + 3]) : 0.0f);
                     }
                 } else {
 #pragma unroll

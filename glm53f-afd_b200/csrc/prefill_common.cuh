@@ -55,7 +55,8 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r) {
                       tc::bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])), tc::bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
 }
 
-// One level of the recursive-doubling inverse of I + L (L strictly lower, 64 x 64, row stride LS).  Given T correct on
+// One level of the recursive-doubling inverse of I + L (L strictly lower, 64 x 64).  L is held TRANSPOSED, as the
+// tensor core delivers it (Lm[j * LS + i] = L[i][j]); T is held row by row (row stride LS).  Given T correct on
 // every sz x sz diagonal block, fills the lower-left sz x sz block of every 2sz x 2sz diagonal block with
 // -T22 (L21 T11).  A thread computes VJ consecutive columns of one row; the loops run over the full block (the
 // triangular halves that are zero cost a few multiply-adds and keep the trip counts fixed and unrolled).
@@ -66,14 +67,14 @@ __device__ __forceinline__ void invert_level(const float* Lm, float* Tm, float* 
     for (int e = tid; e < total; e += NT) {
         const int blk = e / per, rem = e % per, i = rem / cols, j0 = (rem % cols) * VJ;
         const int c0 = blk * 2 * sz, r0 = c0 + sz;
-        const float* Lrow = Lm + (r0 + i) * LS + c0;
+        const float* Lrow = Lm + c0 * LS + r0 + i;  // L is held transposed: L[r0 + i][c0 + m] at (c0 + m) * LS + r0 + i
         const float* Tc = Tm + c0 * LS + c0 + j0;
         float acc[VJ];
 #pragma unroll
         for (int v = 0; v < VJ; ++v) acc[v] = 0.0f;
 #pragma unroll
         for (int m = 0; m < sz; ++m) {
-            const float l = Lrow[m];
+            const float l = Lrow[m * LS];
             if constexpr (VJ == 4) {
                 const float4 t = *reinterpret_cast<const float4*>(Tc + m * LS);
                 acc[0] = fmaf(l, t.x, acc[0]); acc[1] = fmaf(l, t.y, acc[1]); acc[2] = fmaf(l, t.z, acc[2]); acc[3] = fmaf(l, t.w, acc[3]);
@@ -121,12 +122,12 @@ __device__ __forceinline__ void invert_diag16(const float* Lm, float* Tm, int ti
         float t[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float* Lr = Lm + (o + i) * LS + o;
+            const float* Lr = Lm + o * LS + o + i;  // L[o + i][o + m] at (o + m) * LS + o + i
             float a0 = i == j ? 1.0f : 0.0f, a1 = 0.0f;
 #pragma unroll
             for (int m = 0; m < i; ++m) {
-                if (m & 1) a1 = fmaf(-Lr[m], t[m], a1);
-                else a0 = fmaf(-Lr[m], t[m], a0);
+                if (m & 1) a1 = fmaf(-Lr[m * LS], t[m], a1);
+                else a0 = fmaf(-Lr[m * LS], t[m], a0);
             }
             t[i] = a0 + a1;
             Tm[(o + i) * LS + o + j] = t[i];

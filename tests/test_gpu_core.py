@@ -243,7 +243,7 @@ def test_prefill_two_pass_over_a_workspace(G, core, oracle, pkg):
         assert np.array_equal(G.bits(out), G.bits(runs[0][0]))
         assert np.array_equal(G.bits(st), G.bits(runs[0][1]))
     assert G.max_abs(runs[0][0], ref_out) / G.max_abs(ref_out) <= 1.0 / 128.0
-    assert G.rel_l2(runs[0][1], ref_st) <= 1e-4
+    assert G.rel_l2(runs[0][1], ref_st) <= 6e-4   # mild chunks: one reference row here, block-wise references in the single-pass kernel
 
 
 # The gathering form on one GPU: two "ranks" (two head shards of one 4-head problem, run one after the other) store

@@ -57,9 +57,12 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    """nvidia-smi samples of SM clock and throttle reasons.  nvidia-smi needs a fraction of a second to start and samples
+    every 20 ms at best, while a timed region of 20 decode steps lasts 11 ms, so the sampler is started early, every
+    sample carries its timestamp, and the caller names the window to evaluate: the timed region followed by a short
+    untimed tail in which the same CUDA graph keeps replaying (the same load, so the same clocks)."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
@@ -68,35 +71,45 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t0=None, t1=None, t_timed_end=None):
+        """Samples taken in [t0, t1] (epoch seconds; all samples when None); `t_timed_end` splits the timed region from the tail."""
+        import datetime
+
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, in_timed = [], [], set(), 0
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clock, cmax = float(f[2]), float(f[3])
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+            if t0 is not None and not (t0 - 0.02 <= ts <= t1 + 0.02):
+                continue
+            sm.append(clock)
+            mx.append(cmax)
+            if t_timed_end is not None and ts <= t_timed_end + 0.02:
+                in_timed += 1
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[6:10]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_in_timed_region": in_timed,
+                "window": "the timed region and 0.4 s of the same graph replaying after it"}
 
 
 def oracle_module():
@@ -1016,12 +1029,17 @@ def run_reference(args):
         barrier()
         return ms
 
-    _ms, graph = graph_ms(torch, lambda st: [d.chain(ref, l, st) for l in range(layers)], max(3, args.warmup))
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    _ms, graph = graph_ms(torch, lambda st: [d.chain(ref, l, st) for l in range(layers)], max(3, args.warmup))
+    t_c0 = time.time()
     ms = timed(graph.replay, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    t_c1 = time.time()
+    while time.time() < t_c1 + 0.4:   # untimed: the same graph under the clock sampler
+        graph.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(t_c0, time.time(), t_c1) if rank == 0 else None
     ms_per_step = ms / args.steps
     per_rank_bytes = layers * STATE_BYTES_PER_LAUNCH
     value = world * per_rank_bytes / (ms_per_step * 1e-3) / 1e9
@@ -1103,6 +1121,9 @@ def main():
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     numa = bind_to_gpu_numa(torch, local_rank)  # before any pinned allocation: staging is first touched on the GPU's node
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # early: it is running long before the timed region
     pkg = importlib.import_module("glm53f-afd_b200")
     core = importlib.import_module("glm53f-afd_b200.core")
     ffi = pkg.ffi
@@ -1177,12 +1198,14 @@ def main():
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     for _ in range(3):
         graph.replay()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    t_c0 = time.time()
     ms = timed(graph.replay, args.steps)
     timed_launches = args.steps * layers
-    clocks = sampler.stop() if rank == 0 else None
+    t_c1 = time.time()
+    while time.time() < t_c1 + 0.4:   # untimed: the same graph under the clock sampler
+        graph.replay()
+        torch.cuda.synchronize()
+    clocks = sampler.stop(t_c0, time.time(), t_c1) if rank == 0 else None
     ms_per_step = ms / args.steps
     per_rank_bytes = layers * STATE_BYTES_PER_LAUNCH
     value = world * per_rank_bytes / (ms_per_step * 1e-3) / 1e9

@@ -782,6 +782,7 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, 
         "workload": f"config 3: one sequence of {tokens} tokens, H=64 ({hl} heads per GPU), d=128, chunk 64, FP32 state",
         "value": tokens / (ms_total * 1e-3), "unit": "tokens/s per layer", "ms_per_layer": ms_total,
         "heads_per_gpu": hl, "n_gpus": world, "scaling": "strong (the same sequence, heads split over the GPUs)",
+        "speedup_hint": HEADS // hl,  # the factor by which this rank's share of the work shrank
         "compute_only": {"value": tokens / (ms_compute * 1e-3), "ms_per_layer": ms_compute},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": hbm_kind,
                      "tensor": {"achieved": tflops, "peak": tf, "unit": "TFLOP/s", "frac": tflops / tf, "peak_source": tf_kind,
@@ -1105,6 +1106,7 @@ def main():
     ap.add_argument("--no-marks", action="store_true", help="skip the state snapshot / restore leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the draft-verification leg (config 4) and the packed-prefill leg (config 2)")
     ap.add_argument("--prefill-check-heads", type=int, default=-1, help="check this many heads of the prefill leg at full length against the CPU recurrence (about half a minute per head and core at 1M tokens); default: 4 on one GPU, 0 under torchrun")
+    ap.add_argument("--e2e-group", type=int, default=9, help="layers per host-to-device copy of the end-to-end step")
     ap.add_argument("--prefill-ws-chunks", type=int, default=256, help="chunks of 64 rows per pass of the two-pass prefill (0: single-pass kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -1241,7 +1243,7 @@ def main():
         if rc != 0:
             raise RuntimeError(f"decode launch failed: {rc}")
 
-    e2e_step = e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer)
+    e2e_step = e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer, group=args.e2e_group)
     for _ in range(3):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps) / args.steps

@@ -28,6 +28,7 @@
 // 290-460 (argument checks and entry points).
 
 #include <cstdlib>
+#include <cstring>
 #include "common.cuh"
 #include "glm53f_kda.h"
 #include "kda_internal.h"
@@ -876,6 +877,132 @@ __global__ void __launch_bounds__(kThreads, 1) recurrent_kernel(const __grid_con
     __syncthreads();
 }
 
+// ---- the core step on many small blocks ------------------------------------------------------------------------
+// The same arithmetic (delta_rule, rows_dot, round_rows: the bits are those of the kernel above and of the reference)
+// for the core entry points without fused norms, arranged for few units: a block of four warps owns a QUARTER of a
+// unit -- 32 of its 128 value rows, 8 a warp, which never interact with the others -- loads that part of the state
+// straight from global memory into registers (a lane's four consecutive key channels of a row are 8 or 16 contiguous
+// bytes, a warp's a whole row), cooks each row's inputs itself (128 threads, one channel each: widen q, k, v, exp of
+// the log decay, beta), steps through the request's rows and stores its rows of the state back.  No rings, no bulk
+// copies: with eight such blocks resident on an SM, and blocks handed out as SMs free up, the loads of some cover the
+// arithmetic and stores of others, a launch's last blocks end within one small block's time of each other, and the
+// next launch's blocks move in as room appears (programmatic dependent launch).  Used for the exact verify, whose 16
+// serial rows a unit want many warps; for single-row decode the persistent kernel above streams faster.
+constexpr int kSmallWarps = 4, kSmallThreads = kSmallWarps * 32, kSmallParts = kRecWarps / kSmallWarps;
+
+template <typename S>
+__device__ __forceinline__ void load_rows_global(const S* head, int warp, int lane, f32x2 (&s)[kPairs][4]) {
+    const bool vec = (reinterpret_cast<uintptr_t>(head) & (4 * sizeof(S) - 1)) == 0;
+#pragma unroll
+    for (int jp = 0; jp < kPairs; ++jp) {
+        float x[2][4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const S* src = head + (size_t)(warp * kRowsPerLane + 2 * jp + half) * DK + lane * 4;
+            if constexpr (sizeof(S) == 4) {
+                if (vec) {
+                    const float4 v = *reinterpret_cast<const float4*>(src);
+                    x[half][0] = v.x; x[half][1] = v.y; x[half][2] = v.z; x[half][3] = v.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) x[half][i] = src[i];
+                }
+            } else {
+                uint32_t lo, hi;
+                if (vec) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(src);
+                    lo = v.x; hi = v.y;
+                } else {
+                    const uint16_t* u = reinterpret_cast<const uint16_t*>(src);
+                    lo = (uint32_t)u[0] | ((uint32_t)u[1] << 16);
+                    hi = (uint32_t)u[2] | ((uint32_t)u[3] << 16);
+                }
+                x[half][0] = __uint_as_float(lo << 16);
+                x[half][1] = __uint_as_float(lo & 0xffff0000u);
+                x[half][2] = __uint_as_float(hi << 16);
+                x[half][3] = __uint_as_float(hi & 0xffff0000u);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[jp][i] = pack2(x[0][i], x[1][i]);
+    }
+}
+
+template <typename S>
+__global__ void __launch_bounds__(kSmallThreads, 8) core_small_kernel(const __grid_constant__ Params p) {
+    __shared__ __align__(16) float sq[DK], sk[DK], sg[DK], sv[DV];
+    __shared__ float sbeta;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const long long unit = blockIdx.x / kSmallParts;
+    const int part = blockIdx.x % kSmallParts, uw = part * kSmallWarps + warp;  // this warp's place among the unit's 16
+    const int b = (int)(unit / p.H), h = (int)(unit % p.H);
+    const int r0 = p.cu_rows[b], rows = max(p.cu_rows[b + 1] - r0, 0);
+    const bool writes = p.state_out != nullptr;
+    if (rows == 0 && !copies_state(p)) return;
+    const long long s_elem = p.state_off[b] + (long long)h * DV * DK;
+    f32x2 s[kPairs][4];
+    load_rows_global<S>(reinterpret_cast<const S*>(p.state_in) + s_elem, uw, lane, s);
+    for (int r = 0; r < rows; ++r) {
+        const long long gr = (long long)r0 + r, at = (gr * p.H + h) * DK + t;
+        // The row's inputs, one channel a thread (the prologue of the kernel above for the core entry points).
+        const float kf = bf16_bits_to_f32(p.k[at]), gf = expf(p.glog[at]);
+        const uint16_t vb = p.v[at];
+        sq[t] = bf16_bits_to_f32(p.q[at]);
+        sk[t] = kf;
+        sg[t] = gf;
+        sv[t] = bf16_bits_to_f32(vb);
+        float bt = 0.0f;
+        if (t == 0) sbeta = bt = p.beta[gr * p.H + h];
+        if (p.k_save != nullptr && part == 0) {
+            p.k_save[at] = kf;
+            p.g_save[at] = gf;
+            p.v_save[at] = vb;
+            if (t == 0) p.b_save[gr * p.H + h] = bt;
+        }
+        __syncthreads();
+        f32x2 kk[4], gg[4];
+        {
+            const float4 k4 = *reinterpret_cast<const float4*>(&sk[lane * 4]);
+            const float4 g4 = *reinterpret_cast<const float4*>(&sg[lane * 4]);
+            kk[0] = pack2(k4.x, k4.x); kk[1] = pack2(k4.y, k4.y); kk[2] = pack2(k4.z, k4.z); kk[3] = pack2(k4.w, k4.w);
+            gg[0] = pack2(g4.x, g4.x); gg[1] = pack2(g4.y, g4.y); gg[2] = pack2(g4.z, g4.z); gg[3] = pack2(g4.w, g4.w);
+        }
+        delta_rule(s, kk, gg, sv, uw, lane, sbeta, p.neg_zero2);
+        const float4 q4 = *reinterpret_cast<const float4*>(&sq[lane * 4]);
+        const f32x2 qq[4] = {pack2(q4.x, q4.x), pack2(q4.y, q4.y), pack2(q4.z, q4.z), pack2(q4.w, q4.w)};
+        const float o = rows_dot(s, qq, lane, p.neg_zero2);
+        if ((lane & 3) == 0) p.out[gr * p.out_stride + (long long)h * DV + uw * kRowsPerLane + (lane >> 2)] = f32_to_bf16_bits(o);
+        if constexpr (sizeof(S) == 2) {
+            if (r + 1 < rows || !writes) round_rows(s);
+        }
+        __syncthreads();  // the cooked row is overwritten by the next one
+    }
+    if (writes) store_rows_global<S>(reinterpret_cast<S*>(p.state_out) + s_elem, uw, lane, s);
+}
+
+template <typename S>
+int launch_small(const Params& p, cudaStream_t stream) {
+    Params q = p;
+    q.neg_zero2 = 0x8000000080000000ull;
+    static const bool pdl = [] {
+        const char* v = getenv("GLM53F_KDA_PDL");
+        return !(v && v[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.units * kSmallParts));
+    cfg.blockDim = dim3(kSmallThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, core_small_kernel<S>, q);
+}
+
 template <typename S, int MODE>
 int launch(const Params& p, cudaStream_t stream) {
     using L = Smem<S, MODE>;
@@ -1014,6 +1141,18 @@ int core_entry(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53
     x.state_off = reinterpret_cast<const long long*>(state_off);
     x.out = out; x.out_stride = (long long)heads * DV;
     x.k_save = k_save; x.v_save = v_save; x.g_save = g_save; x.b_save = b_save;
+    // The exact verify (saves requested, inputs used as given, no fused output norm) runs on the small-block kernel: 16
+    // serial rows a unit are bound by instruction issue, and 32 resident warps an SM issue more than the persistent
+    // kernel's 16 (11.1 against 12.3 ms per step of 48 slots x 16 rows x 34 layers).  Single-row decode stays on the
+    // persistent kernel, which streams faster (4,263 against 3,500 GB/s at 16 slots: small blocks keep too few bytes in
+    // flight).  GLM53F_KDA_DECODE=pipeline / small forces one or the other; the bits are the same either way.
+    static const int forced = [] {
+        const char* e = getenv("GLM53F_KDA_DECODE");
+        return e == nullptr ? 0 : (strcmp(e, "pipeline") == 0 ? 1 : (strcmp(e, "small") == 0 ? 2 : 0));
+    }();
+    const bool small = forced == 2 || (forced == 0 && k_save != nullptr);
+    if (small && flags == 0 && gate == nullptr && x.units * kSmallParts <= 0x7fffffffll)
+        return state_bf16 != 0 ? launch_small<__nv_bfloat16>(x, (cudaStream_t)stream) : launch_small<float>(x, (cudaStream_t)stream);
     return launch_typed<kCore>(x, state_bf16 != 0, (cudaStream_t)stream);
 }
 

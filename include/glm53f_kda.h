@@ -397,12 +397,12 @@ int glm53f_kda_gather_close(const glm53f_kda_gather_handle* handle, void* full);
  * GLM53F_KDA_PREFILL=chunked makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */
 int32_t glm53f_kda_prefill_mode(int32_t mode);
 
-/* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The decode / verify / commit
- * kernels bound every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
+/* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The persistent recurrent kernel
+ * (the layer entry points, the replays, and core calls with fused norms or an output gate) bounds every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
  * status code (101-108, which wait), makes its other waits return, and the kernel ends; the context stays usable and
  * glm53f_kda_device_status reports the code.
  *   wait_limit_ns     the limit for the launches that follow, 100,000 .. 60,000,000,000 ns; 0 restores the default
- *   skip_first_state  != 0: in the NEXT decode / verify / commit launch only, block 0 does not fetch its first unit's
+ *   skip_first_state  != 0: in the NEXT launch of that kernel only, block 0 does not fetch its first unit's
  *                     state and tells nobody, so that this unit's wait runs out.  Nothing is in flight and nothing
  *                     faults; the launch's other units complete, that unit's state and outputs are not written.
  * Host-side settings, not thread safe; returns 0, or 1 for a limit outside the range. */

@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
         if (!mbar_wait(bar_raw, raw_phase, ctx, kStatusWaitPrefill)) { alive = false; break; }
         raw_phase ^= 1u;
 
+        bool mild;
         // ---- 1. per key channel: the cumulative log decay G, a = exp(G - Gm) of every row relative to the middle row of
         // its block of 16 (left in the staging buffer in place of g), and the per-block factor tables.
         // Thread (part, d): rows 16*part .. 16*part+15 of channel d, which is exactly row block J = part.
@@ -245,9 +246,67 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
             for (int I = 1; I < 4; ++I)
                 if (I > part) tab[(tF + I * (I - 1) / 2 + part) * 128] = __expf(gm[I] - gm[part]);
             if (part == 3) egl[d] = __expf(start[4]);
+            mild = start[4] > -60.0f;
         }
-        compute_sync();
+        // A chunk whose whole decay stays above e^-60 in every channel takes one reference row (the chunk's start): one
+        // column-side tile, one product each for L^T and M^T, no second operand pass.  The block decides together (the
+        // barrier carries the vote) from the chunk's own gates.
+        const bool narrow = named_bar_all(1, kCompute, mild);
 
+        if (narrow) {
+            const int r = tid & 63, cgrp = tid >> 6, J = r >> 4;
+            const float* tabs = reinterpret_cast<const float*>(smem + oTab);
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = cgrp * 2 + cc;
+                const uint4 k8 = *reinterpret_cast<const uint4*>(smem + oRawK + r * RS16 + c * 16);
+                const uint4 q8 = *reinterpret_cast<const uint4*>(smem + oRawQ + r * RS16 + c * 16);
+                const uint4 v8 = *reinterpret_cast<const uint4*>(smem + oRawV + r * RS16 + c * 16);
+                const float4 a0 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32);
+                const float4 a1 = *reinterpret_cast<const float4*>(smem + oRawG + r * RS32 + c * 32 + 16);
+                const float4 e0 = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8);
+                const float4 e1 = *reinterpret_cast<const float4*>(tabs + (tE0 + J) * 128 + c * 8 + 4);
+                const float4 l0 = *reinterpret_cast<const float4*>(egl + c * 8);
+                const float4 l1 = *reinterpret_cast<const float4*>(egl + c * 8 + 4);
+                const float E[8] = {a0.x * e0.x, a0.y * e0.y, a0.z * e0.z, a0.w * e0.w, a1.x * e1.x, a1.y * e1.y, a1.z * e1.z, a1.w * e1.w};
+                const float EL[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w}, qw[4] = {q8.x, q8.y, q8.z, q8.w};
+                uint32_t kg[4], qg[4], ki[4], dh[4], dl[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float kf[2], qf[2], vi[2], hi[2], lo[2];
+                    widen2<QK16>(kw[j], kf[0], kf[1]);
+                    widen2<QK16>(qw[j], qf[0], qf[1]);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float einv = __fdividef(1.0f, E[2 * j + u]);
+                        vi[u] = kf[u] * einv;
+                        tc::split_bf16(kf[u] * (EL[2 * j + u] * einv), hi[u], lo[u]);
+                    }
+                    kg[j] = tc::bf16x2(kf[0] * E[2 * j], kf[1] * E[2 * j + 1]);
+                    qg[j] = tc::bf16x2(qf[0] * E[2 * j], qf[1] * E[2 * j + 1]);
+                    ki[j] = tc::bf16x2(vi[0], vi[1]);
+                    dh[j] = tc::bf16x2(hi[0], hi[1]);
+                    dl[j] = tc::bf16x2(lo[0], lo[1]);
+                }
+                *reinterpret_cast<uint4*>(cell(smem + oKg, CH, c, r)) = make_uint4(kg[0], kg[1], kg[2], kg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oQg, CH, c, r)) = make_uint4(qg[0], qg[1], qg[2], qg[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKc + kc_tile(3), CH, c, r)) = make_uint4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKdHi, CH, c, r)) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oKdLo, CH, c, r)) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+                *reinterpret_cast<uint4*>(cell(smem + oV, CH, c, r)) = v8;
+            }
+            publish_operands();
+            if (tid == 0 && s + CH < T) mbar_arrive(bar_free);  // the staging area is free for the next chunk's rows
+            if (!mma_round([&] {
+                    constexpr uint32_t id = tc::idesc_bf16(64, 64, 0, 0, 0);
+                    const unsigned char* kit = smem + oKc + kc_tile(3);
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + cL, tc::desc_kmajor_bf16(kit, CH, 0, k0), tc::desc_kmajor_bf16(smem + oKg, CH, 0, k0), id, k0 > 0);
+                    for (int k0 = 0; k0 < DK; k0 += 16)
+                        tc::mma_bf16(tm + cMm, tc::desc_kmajor_bf16(kit, CH, 0, k0), tc::desc_kmajor_bf16(smem + oQg, CH, 0, k0), id, k0 > 0);
+                })) { alive = false; break; }
+        } else {
         // ---- 2. operand tiles: lane <-> row, one 16-byte cell (8 channels) at a time.  Row sides Kgb = K a -> oKg, Qgb = Q a ->
         // oQg; the column sides K exp(Gm_I - G) into the four tiles I >= J; Kdec = K exp(G_last - G) as bf16 hi + lo; V as it is.
         {
@@ -347,6 +406,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) prefill_tc_kernel(const __grid_
         compute_sync();  // every thread is done with the staging area and the tables (M goes over them next)
         // The staging area is free: the loader streams the next chunk's rows in behind this chunk's arithmetic.
         if (tid == 0 && s + CH < T) mbar_arrive(bar_free);
+        }
 
         // ---- 4. from L^T and M^T (lane = column j, tensor-memory column = row i): L (FP32, strictly lower, times beta_i); M
         // (lower with the diagonal) as bf16 cells of eight consecutive rows i, [8 cells][64 columns j].  Column groups 0, 1

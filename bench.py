@@ -259,6 +259,22 @@ def run_layer_abi(torch, lib, rank, layers, steps, prefill_lib_ok=True):
                      "state_gbs": sb / (ms_v * 1e-3) / 1e9, "frac_of_hbm": sb / (ms_v * 1e-3) / 1e9 / hbm}
     res["commit"] = {"entry": "glm53f_kda_replay_batch_bf16state", "ms_per_step": ms_c, "state_gbs": 2 * sb / (ms_c * 1e-3) / 1e9,
                      "frac_of_hbm": 2 * sb / (ms_c * 1e-3) / 1e9 / hbm}
+    if hasattr(lib, "glm53f_kda_verify_mode"):  # the product's tensor-core form of the same call (two launches a layer)
+        set_v = lib.glm53f_kda_verify_mode
+        set_v.restype, set_v.argtypes = C.c_int32, [C.c_int32]
+        set_v(1)
+        try:
+            ms_t, _g3 = graph_ms(torch, verify, n, warm=2)
+        finally:
+            set_v(0)
+        # all the bytes the step must move: states read once, projection rows, gate rows in; outputs and saves out
+        vb = sb + layers * v.rows * ((P_STRIDE + AG_STRIDE) * 2 + OUT_STRIDE * 2 + HEADS * 1284)
+        res["verify_chunked"] = {"entry": "glm53f_kda_chain_batch_bf16state after glm53f_kda_verify_mode(1)", "ms_per_step": ms_t,
+                                 "rows_per_s": v.rows * layers / (ms_t * 1e-3), "state_gbs": sb / (ms_t * 1e-3) / 1e9, "gpu_launches": 2 * layers,
+                                 "algorithmic_bytes": vb,
+                                 "roofline": {"bound": "hbm", "achieved": vb / (ms_t * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                                              "frac": vb / (ms_t * 1e-3) / 1e9 / hbm, "peak_source": kind}}
+        del _g3
     del v, ks, gs_, vs, bs, _g1, _g2
     torch.cuda.empty_cache()
     # prefill lanes: 4 lanes x 2,048 rows in one call, and one lane per call; f32 and bf16 states

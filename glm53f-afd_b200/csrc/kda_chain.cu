@@ -27,6 +27,7 @@
 // Reference lines restated here: kernels/kda.cu:38-53 (update), 98-210 (chain_kernel), 214-253 (replay_kernel),
 // 290-460 (argument checks and entry points).
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include "common.cuh"
@@ -39,6 +40,12 @@ __device__ int g_status = 0;
 // Host-side settings of the diagnostic hook glm53f_kda_debug_wait_test: the bound of the recurrent kernels' waits, and
 // a one-shot request that the next launch's block 0 leaves its first unit's state unfetched.
 static unsigned long long g_wait_limit_ns = kWaitLimitNs;
+// How glm53f_kda_chain_batch_bf16state runs a verify call (read-only states, saves on): 0 = the exact row-by-row form,
+// 1 = the chunked tensor-core form; GLM53F_KDA_VERIFY=chunked makes 1 the default.
+static std::atomic<int> g_layer_verify_mode{[] {
+    const char* e = getenv("GLM53F_KDA_VERIFY");
+    return e != nullptr && strcmp(e, "chunked") == 0 ? 1 : 0;
+}()};
 static int g_skip_first_state = 0;
 
 int sm_count() {
@@ -1068,6 +1075,20 @@ int chain_entry(int32_t heads, int32_t batch, bool batched, const int32_t* cu_ro
     } else if (rows < 1) {
         return kInvalid;
     }
+    if (batched && bf16_state && state_out == nullptr && k_save != nullptr && keep == nullptr && g_layer_verify_mode.load() == 1) {
+        // The chunked form of a verify call: eligible when every row the two kernels touch by vector is aligned; any
+        // other call runs the exact form below.
+        auto al = [](const void* x, int bytes) { return (reinterpret_cast<uintptr_t>(x) & (bytes - 1)) == 0; };
+        if (al(p, 8) && al(a, 8) && al(g, 8) && al(conv, 8) && al(conv_w, 16) && al(dt_bias, 16) && al(out, 16) && al(k_save, 16) && al(v_save, 16) &&
+            al(g_save, 16) && al(state_in, 16) && p_stride % 4 == 0 && a_stride % 4 == 0 && g_stride % 4 == 0 && out_stride % 8 == 0) {
+            cudaStream_t st = (cudaStream_t)stream;
+            const int rc = verify_prologue_launch(heads, batch, cu_rows, p, p_stride, b_off, a, a_stride, conv, conv_off, conv_w, a_log, dt_bias,
+                                                  lower, out, out_stride, k_save, v_save, g_save, b_save, st);
+            if (rc != 0) return rc;
+            return layer_verify_tc_launch(heads, batch, cu_rows, state_in, state_off, g, g_stride, norm_w, eps, out, out_stride, k_save, v_save,
+                                          g_save, b_save, st);
+        }
+    }
     Params q{};
     q.H = heads;
     q.layers = 1;
@@ -1327,6 +1348,12 @@ extern "C" int glm53f_kda_device_status(void) {
     if (e != cudaSuccess) return (int)e;
     if (v != 0) cudaMemcpyToSymbol(g_status, &zero, sizeof zero);
     return v;
+}
+
+extern "C" int32_t glm53f_kda_verify_mode(int32_t mode) {
+    const int prev = kda::g_layer_verify_mode.load();
+    if (mode == 0 || mode == 1) kda::g_layer_verify_mode.store(mode);
+    return prev;
 }
 
 extern "C" int glm53f_kda_debug_wait_test(uint64_t wait_limit_ns, int32_t skip_first_state) {

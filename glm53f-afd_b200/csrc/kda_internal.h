@@ -50,6 +50,18 @@ int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, 
                           const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, const int64_t* state_off,
                           glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream);
 
+// The chunked form of a layer verify call (glm53f_kda_verify_mode): verify_prologue_launch cooks every window's rows into
+// the call's own buffers (k, v, the decay multiplier, beta into the replay saves with the exact form's bits; q as fp16
+// into the output rows), layer_verify_tc_launch, on the same stream, computes the windows' outputs from them with the
+// gated norm fused.  Saves and out rows 16-byte aligned, out_stride and gate_stride multiples of 8 elements.
+int verify_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                           const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* conv, const int64_t* conv_off,
+                           const glm53f_bf16* conv_w, const float* a_log, const float* dt_bias, float lower, glm53f_bf16* out,
+                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream);
+int layer_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const void* state_in, const int64_t* state_off,
+                           const glm53f_bf16* gate, int64_t gate_stride, const glm53f_bf16* norm_w, float eps, glm53f_bf16* out,
+                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream);
+
 // The layer prologue of a prefill pass (kda_prologue.cu): for rows row_shift .. row_shift + pass_rows - 1 of every request,
 // the short convolution + SiLU, the L2 norms, the log decay and beta, with the chain's arithmetic, written as core inputs
 // (q, k as fp16 bits, v bf16, g f32 log decay [batch * pass_rows][H][128]; beta f32 [batch * pass_rows][H]).  p, a, conv must be

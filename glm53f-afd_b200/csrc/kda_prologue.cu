@@ -13,6 +13,14 @@
 //
 // One warp per (request, head, run of 16 rows); a lane owns four consecutive channels, so the norms need no shared
 // memory, and the three earlier rows of the convolution slide along in registers.
+//
+// The same arithmetic feeds the chunked form of draft verification behind glm53f_kda_chain_batch_bf16state
+// (verify_prologue_kernel): there the call's own buffers take the results, so nothing is allocated -- k, v, the decay
+// multiplier exp(log decay) and beta go to the replay saves, which a verify call must write anyway and which hold
+// exactly these values (the bits the exact form saves), and q goes, as fp16, to the 256 bytes of `out` that the same
+// (row, head) output will overwrite.  Windows are short (up to 16 rows) and the work is bound by instruction issue
+// (IEEE divisions and exponentials), so there a warp takes ONE row and reads its three predecessors again (they come
+// from L1/L2): every load of a warp is in flight at once and the registers allow twice the resident warps.
 
 #include <cuda_fp16.h>
 
@@ -155,7 +163,125 @@ __global__ void __launch_bounds__(128) layer_prologue_kernel(const ProParams p) 
     }
 }
 
+struct VerifyProParams {
+    int H, batch;
+    const int32_t* cu;
+    const uint16_t* P;
+    long long p_stride, b_off;
+    const uint16_t* A;
+    long long a_stride;
+    const uint16_t* conv;
+    const long long* conv_off;
+    const uint16_t* cw;
+    const float* a_log;
+    const float* dt_bias;
+    float lower;
+    uint16_t* q;  // the output rows: q as fp16
+    long long out_stride;
+    float *k_save, *g_save, *b_save;
+    uint16_t* v_save;
+};
+constexpr int kVerifyWindow = 16;
+
+__global__ void __launch_bounds__(128, 6) verify_prologue_kernel(const VerifyProParams p) {
+    const int lane = threadIdx.x & 31, H = p.H;
+    // a block = four consecutive rows of one (request, head): neighbours share their predecessors in L1
+    const long long unit = blockIdx.x / (kVerifyWindow / 4);
+    const int j = (int)(blockIdx.x % (kVerifyWindow / 4)) * 4 + (threadIdx.x >> 5);
+    const int h = (int)(unit % H), b = (int)(unit / H);
+    const int r0 = p.cu[b], n = min(max(p.cu[b + 1] - r0, 0), kVerifyWindow);
+    if (j >= n) return;
+    const int c0 = lane * 4;
+    const long long C = 3LL * H * DK, gr = (long long)r0 + j;
+    const uint16_t* window = p.conv + p.conv_off[b];
+    uint2 x[TAPS][3];  // [tap: rows j-3 .. j][part]
+#pragma unroll
+    for (int d = 0; d < TAPS; ++d) {
+        const int jj = j - 3 + d;
+        const uint16_t* row = jj < 0 ? window + (long long)(WINDOW + jj) * C : p.P + ((long long)r0 + jj) * p.p_stride;
+#pragma unroll
+        for (int part = 0; part < 3; ++part) x[d][part] = *reinterpret_cast<const uint2*>(row + ((long long)part * H + h) * DK + c0);
+    }
+    uint4 wq[3][2];
+#pragma unroll
+    for (int part = 0; part < 3; ++part) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.cw + (((long long)part * H + h) * DK + c0) * TAPS);
+        wq[part][0] = src[0];
+        wq[part][1] = src[1];
+    }
+    const uint2 a_bits = *reinterpret_cast<const uint2*>(p.A + gr * p.a_stride + (long long)h * DK + c0);
+    const float4 dtb4 = *reinterpret_cast<const float4*>(p.dt_bias + (long long)h * DK + c0);
+    const float blogit = bf16_bits_to_f32(p.P[gr * p.p_stride + p.b_off + h]);
+    const float decay_rate = expf(p.a_log[h]);
+
+    float act[3][4];
+#pragma unroll
+    for (int part = 0; part < 3; ++part) {
+        float xv[TAPS][4];
+#pragma unroll
+        for (int d = 0; d < TAPS; ++d) unpack4(x[d][part], xv[d]);
+        const uint32_t ww[8] = {wq[part][0].x, wq[part][0].y, wq[part][0].z, wq[part][0].w, wq[part][1].x, wq[part][1].y, wq[part][1].z, wq[part][1].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float acc = 0.0f;
+            acc = acc + __uint_as_float(ww[2 * c] << 16) * xv[0][c];
+            acc = acc + __uint_as_float(ww[2 * c] & 0xffff0000u) * xv[1][c];
+            acc = acc + __uint_as_float(ww[2 * c + 1] << 16) * xv[2][c];
+            acc = acc + __uint_as_float(ww[2 * c + 1] & 0xffff0000u) * xv[3][c];
+            act[part][c] = bf16_round(acc / (1.0f + expf(-acc)));
+        }
+    }
+    float qn[4], kn[4];
+    {
+        float sq = 0.0f, sk = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            sq = sq + act[0][c] * act[0][c];
+            sk = sk + act[1][c] * act[1][c];
+        }
+        sq = butterfly(sq);
+        sk = butterfly(sk);
+        const float iq = 1.0f / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            qn[c] = (act[0][c] * iq) * (1.0f / sqrtf((float)DK));
+            kn[c] = act[1][c] * ik;
+        }
+    }
+    float a4[4], dec[4];
+    unpack4(a_bits, a4);
+    const float dtb[4] = {dtb4.x, dtb4.y, dtb4.z, dtb4.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) dec[c] = expf(p.lower * sigmoid_(decay_rate * (a4[c] + dtb[c])));
+    const long long sv = (gr * H + h) * DK + c0;
+    *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);
+    *reinterpret_cast<float4*>(p.k_save + sv) = make_float4(kn[0], kn[1], kn[2], kn[3]);
+    *reinterpret_cast<uint2*>(p.v_save + sv) = pack4(act[2]);
+    *reinterpret_cast<float4*>(p.g_save + sv) = make_float4(dec[0], dec[1], dec[2], dec[3]);
+    if (lane == 0) p.b_save[gr * H + h] = bf16_round(sigmoid_(blogit));
+}
+
 }  // namespace
+
+// The prologue of the chunked verify: windows of up to 16 rows per request; see the head of the file for where the
+// results go.  The caller checks the alignment of every row.
+int verify_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                           const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* conv, const int64_t* conv_off,
+                           const glm53f_bf16* conv_w, const float* a_log, const float* dt_bias, float lower, glm53f_bf16* out,
+                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
+    VerifyProParams pp{};
+    pp.H = heads; pp.batch = batch;
+    pp.cu = cu_rows;
+    pp.P = p; pp.p_stride = p_stride; pp.b_off = b_off;
+    pp.A = a; pp.a_stride = a_stride;
+    pp.conv = conv; pp.conv_off = reinterpret_cast<const long long*>(conv_off); pp.cw = conv_w;
+    pp.a_log = a_log; pp.dt_bias = dt_bias; pp.lower = lower;
+    pp.q = out; pp.out_stride = out_stride;
+    pp.k_save = k_save; pp.v_save = v_save; pp.g_save = g_save; pp.b_save = b_save;
+    const long long blocks = (long long)batch * heads * (kVerifyWindow / 4);
+    verify_prologue_kernel<<<(unsigned)blocks, 128, 0, stream>>>(pp);
+    return (int)cudaGetLastError();
+}
 
 int layer_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t pass_rows, int32_t row_shift,
                           const glm53f_bf16* p, int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride,

@@ -19,6 +19,11 @@
 // decode steps; only the window's OUTPUTS differ from the serial steps', by the rounding of bf16 operands (within the
 // task's tolerance: max-abs 2e-2, rel-L2 5e-3).  Selected by GLM53F_KDA_CORE_TENSOR on glm53f_kda_core_verify_batch.
 //
+// The layer form (LAYER = true; the chunked form of glm53f_kda_chain_batch_bf16state, glm53f_kda_verify_mode) runs after
+// the verify prologue (kda_prologue.cu) and takes a unit's rows from where that kernel left them: k, v, the decay
+// multiplier and beta from the replay saves, q as fp16 from the output rows; it writes no saves and fuses the gated
+// RMSNorm into its outputs.
+//
 // One block of 128 threads per (request, head) unit, three blocks per SM, blocks walk the units persistently.  A unit's
 // rows and state arrive by asynchronous 16-byte copies issued one unit ahead (the state straight into the 128-byte
 // swizzle the tensor core reads), so one unit's arithmetic covers the next one's loads.  All waits are bounded.
@@ -37,28 +42,44 @@ constexpr int WIN = 16, kVThreads = 128;
 // Shared memory map (bytes).  Tiles are boxes of R rows x 128 bytes in the 128-byte swizzle (16-byte piece p of row r at
 // piece p ^ (r & 7)), two boxes per tile (channels 0-63, 64-127).  The column-side tile Kc comes first: as the M = 128
 // operand of L^T and M^T its descriptor walks 128 rows although 16 are real, and what follows it is the state tile.
+// Once those two products are done Kc is dead, and L, M and T' (FP32, 3.1 KB) take its place until the unit ends.
 constexpr int vKc = 0, vS = 4096, vKgb = vS + 32768, vQgb = vKgb + 4096, vQg = vQgb + 4096, vRaw = vQg + 4096;
 constexpr int vW = vKgb;                                                 // W replaces Kgb once L^T is done
-constexpr int rQ = 0, rK = 4096, rV = 8192, rG = 12288, rB = 20480;      // raw rows inside vRaw
-constexpr int vL = vRaw + 20608, vM = vL + WIN * 17 * 4, vTp = vM + WIN * WIN * 4, vBeta = vTp + WIN * WIN * 4;
-constexpr int vBar = vBeta + 64, vCtl = vBar + 16, kVSmem = vCtl + 16;
-static_assert(vL % 16 == 0 && vBar % 8 == 0 && kVSmem <= 75 * 1024, "verify kernel shared memory");
+constexpr int vStage = vKgb;                                             // layer form: FP32 outputs [16][128] over W and Qgb
+constexpr int vL = vKc, vM = vL + WIN * 17 * 4, vTp = vM + WIN * WIN * 4;
+static_assert(vTp + WIN * WIN * 4 <= vS, "L, M, T' fit the dead column-side tile");
+// Raw rows of a unit.  Core form: q, k, v bf16 (256 bytes a row), log decay f32 (512), beta.  Layer form: q fp16, v bf16,
+// k f32, the decay multiplier f32, beta.
+template <bool LAYER>
+struct Raw {
+    static constexpr int Q = 0, V = 4096, K = 8192, G = LAYER ? 16384 : 12288, B = G + 8192, kBytes = B + 128;
+};
+template <bool LAYER>
+struct Map {
+    static constexpr int vBeta = vRaw + Raw<LAYER>::kBytes, vBar = vBeta + 64, vCtl = vBar + 16, kSmem = vCtl + 16;
+    static_assert(vBar % 8 == 0 && kSmem <= 75 * 1024, "three blocks per SM");
+};
 constexpr uint32_t kVCols = 32;  // tensor memory: [0, 16) L^T then (W S)^T, [16, 32) M^T then (Qg S)^T
 
 struct VParams {
     int H;
     long long units;
     const int32_t* cu;
-    const uint16_t *q, *k, *v;
+    const uint16_t *q, *k, *v;  // core form: bf16 rows
     const float* g;
     const float* beta;
     const uint16_t* state;
     const long long* state_off;
-    uint16_t* out;
-    float* k_save;
+    uint16_t* out;              // layer form: holds q as fp16 on entry
+    long long out_stride;
+    float* k_save;              // layer form: the sources of k, v, decay and beta
     uint16_t* v_save;
     float* g_save;
     float* b_save;
+    const uint16_t* gate;       // layer form: the output gate rows, the norm weight, eps
+    long long gate_stride;
+    const uint16_t* norm_w;
+    float eps;
     int* status;
 };
 
@@ -74,6 +95,7 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ int sw_elem(int R, int r, int c) {
     return (c >> 6) * R * 128 + r * 128 + (((((c & 63) >> 3) ^ (r & 7))) << 4) + (c & 7) * 2;
 }
+__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 struct Unit {
     int b, h, n;
@@ -90,30 +112,50 @@ __device__ __forceinline__ Unit unit_of(const VParams& p, long long u) {
     return x;
 }
 
-// The unit's raw rows: q, k, v (256 bytes a row), g (512), beta; rows past the window's end become zero.
+// The unit's raw rows; rows past the window's end become zero.
+template <bool LAYER>
 __device__ __forceinline__ void fetch_rows(const VParams& p, unsigned char* smem, const Unit& un, int t) {
+    using R = Raw<LAYER>;
     const int n = min(max(un.n, 0), WIN);
     unsigned char* raw = smem + vRaw;
-    for (int e = t; e < WIN * 16; e += kVThreads) {  // 16-byte pieces of the bf16 rows
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int e = t; e < WIN * 16; e += kVThreads) {  // 16-byte pieces of the 256-byte rows
         const int r = e >> 4, pc = e & 15;
         const long long at = ((un.row0 + r) * p.H + un.h) * DK + pc * 8;
         if (r < n) {
-            cp_async16(raw + rQ + e * 16, p.q + at);
-            cp_async16(raw + rK + e * 16, p.k + at);
-            cp_async16(raw + rV + e * 16, p.v + at);
+            if constexpr (LAYER) {
+                cp_async16(raw + R::Q + e * 16, p.out + (un.row0 + r) * p.out_stride + (long long)un.h * DK + pc * 8);
+                cp_async16(raw + R::V + e * 16, p.v_save + at);
+            } else {
+                cp_async16(raw + R::Q + e * 16, p.q + at);
+                cp_async16(raw + R::K + e * 16, p.k + at);
+                cp_async16(raw + R::V + e * 16, p.v + at);
+            }
         } else {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(raw + rQ + e * 16) = z;
-            *reinterpret_cast<uint4*>(raw + rK + e * 16) = z;
-            *reinterpret_cast<uint4*>(raw + rV + e * 16) = z;
+            *reinterpret_cast<uint4*>(raw + R::Q + e * 16) = z;
+            if constexpr (!LAYER) *reinterpret_cast<uint4*>(raw + R::K + e * 16) = z;
+            *reinterpret_cast<uint4*>(raw + R::V + e * 16) = z;
         }
     }
-    for (int e = t; e < WIN * 32; e += kVThreads) {
+    for (int e = t; e < WIN * 32; e += kVThreads) {  // and of the 512-byte rows
         const int r = e >> 5, pc = e & 31;
-        if (r < n) cp_async16(raw + rG + e * 16, p.g + ((un.row0 + r) * p.H + un.h) * DK + pc * 4);
-        else *reinterpret_cast<uint4*>(raw + rG + e * 16) = make_uint4(0, 0, 0, 0);
+        const long long at = ((un.row0 + r) * p.H + un.h) * DK + pc * 4;
+        if (r < n) {
+            if constexpr (LAYER) {
+                cp_async16(raw + R::K + e * 16, p.k_save + at);
+                cp_async16(raw + R::G + e * 16, p.g_save + at);
+            } else {
+                cp_async16(raw + R::G + e * 16, p.g + at);
+            }
+        } else {
+            if constexpr (LAYER) *reinterpret_cast<uint4*>(raw + R::K + e * 16) = z;
+            *reinterpret_cast<uint4*>(raw + R::G + e * 16) = z;
+        }
     }
-    if (t < WIN) reinterpret_cast<float*>(raw + rB)[t] = t < n ? p.beta[(un.row0 + t) * p.H + un.h] : 0.0f;
+    if (t < WIN) {
+        const float* src = LAYER ? p.b_save : p.beta;
+        reinterpret_cast<float*>(raw + R::B)[t] = t < n ? src[(un.row0 + t) * p.H + un.h] : 0.0f;
+    }
     cp_async_commit();
 }
 // The unit's state, 2,048 pieces of 16 bytes, into the swizzled tile.
@@ -131,10 +173,13 @@ __device__ __forceinline__ void fetch_state(const VParams& p, unsigned char* sme
     cp_async_commit();
 }
 
+template <bool LAYER>
 __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_constant__ VParams p) {
+    using R = Raw<LAYER>;
+    using MP = Map<LAYER>;
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + vBar);
-    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + vCtl);
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + MP::vBar);
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + MP::vCtl);
     uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     if (t == 0) {
@@ -153,12 +198,17 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
     float* Lf = reinterpret_cast<float*>(smem + vL);
     float* Mf = reinterpret_cast<float*>(smem + vM);
     float* Tp = reinterpret_cast<float*>(smem + vTp);
-    float* betas = reinterpret_cast<float*>(smem + vBeta);
+    float* betas = reinterpret_cast<float*>(smem + MP::vBeta);
+    float nw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if constexpr (LAYER) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) nw[i] = bf16_bits_to_f32(p.norm_w[lane * 4 + i]);
+    }
 
     long long u = blockIdx.x;
     if (u < p.units) {
         const Unit first = unit_of(p, u);
-        fetch_rows(p, smem, first, t);
+        fetch_rows<LAYER>(p, smem, first, t);
         fetch_state(p, smem, first, t);
     }
     for (; u < p.units; u += gridDim.x) {
@@ -171,7 +221,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
         const int n = min(max(un.n, 0), WIN);
 
         cp_async_wait<1>();  // this unit's rows have landed (its state may still be on the way)
-        __syncthreads();
+        __syncthreads();     // and every thread is done with the previous unit's L, M and staged outputs
 
         // ---- A. thread = channel c: the decay scan, the operand tiles, the replay saves ----------------------------------
         float kg[WIN], vv[WIN];
@@ -181,16 +231,24 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
             float G[WIN], acc = 0.0f;
 #pragma unroll
             for (int r = 0; r < WIN; ++r) {
-                acc += reinterpret_cast<const float*>(raw + rG)[r * DK + c];
+                const float x = reinterpret_cast<const float*>(raw + R::G)[r * DK + c];
+                // layer form: the saved multiplier exp(log decay) in (0, 1]; the rows past the window decay by nothing
+                acc += LAYER ? (r < n ? __logf(x) : 0.0f) : x;
                 G[r] = acc;
             }
             const float gm = G[WIN / 2];
             float amax = 0.0f;
 #pragma unroll
             for (int r = 0; r < WIN; ++r) {
-                const float kf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + rK)[r * DK + c]);
-                const float qf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + rQ)[r * DK + c]);
-                const uint16_t vb = reinterpret_cast<const uint16_t*>(raw + rV)[r * DK + c];
+                float kf, qf;
+                if constexpr (LAYER) {
+                    kf = reinterpret_cast<const float*>(raw + R::K)[r * DK + c];
+                    qf = __half2float(reinterpret_cast<const __half*>(raw + R::Q)[r * DK + c]);
+                } else {
+                    kf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + R::K)[r * DK + c]);
+                    qf = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(raw + R::Q)[r * DK + c]);
+                }
+                const uint16_t vb = reinterpret_cast<const uint16_t*>(raw + R::V)[r * DK + c];
                 const float a = __expf(G[r] - gm), e = __expf(G[r]);
                 amax = fmaxf(amax, a);
                 kg[r] = kf * e;
@@ -199,18 +257,22 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
                 *reinterpret_cast<uint16_t*>(smem + vQgb + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * a);
                 *reinterpret_cast<uint16_t*>(smem + vKc + sw_elem(WIN, r, c)) = f32_to_bf16_bits(kf * __fdividef(1.0f, a));
                 *reinterpret_cast<uint16_t*>(smem + vQg + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * e);
-                if (r < n && p.k_save != nullptr) {
-                    const long long at = ((un.row0 + r) * p.H + un.h) * DK + c;
-                    p.k_save[at] = kf;
-                    p.v_save[at] = vb;
-                    p.g_save[at] = expf(reinterpret_cast<const float*>(raw + rG)[r * DK + c]);
+                if constexpr (!LAYER) {
+                    if (r < n && p.k_save != nullptr) {
+                        const long long at = ((un.row0 + r) * p.H + un.h) * DK + c;
+                        p.k_save[at] = kf;
+                        p.v_save[at] = vb;
+                        p.g_save[at] = expf(reinterpret_cast<const float*>(raw + R::G)[r * DK + c]);
+                    }
                 }
             }
             if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
             if (t < WIN) {
-                const float bt = reinterpret_cast<const float*>(raw + rB)[t];
+                const float bt = reinterpret_cast<const float*>(raw + R::B)[t];
                 betas[t] = bt;
-                if (t < n && p.b_save != nullptr) p.b_save[(un.row0 + t) * p.H + un.h] = bt;
+                if constexpr (!LAYER) {
+                    if (t < n && p.b_save != nullptr) p.b_save[(un.row0 + t) * p.H + un.h] = bt;
+                }
             }
         }
         fence_proxy_async_smem();
@@ -218,7 +280,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
         __syncthreads();
         tc::fence_after_sync();
         // The raw rows are consumed: the next unit's may come in.
-        if (more) fetch_rows(p, smem, nxt, t);
+        if (more) fetch_rows<LAYER>(p, smem, nxt, t);
         else cp_async_commit();
 
         // ---- B. L^T and M^T -------------------------------------------------------------------------------------------------
@@ -235,7 +297,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
         phase ^= 1u;
         if (!__syncthreads_and(ok)) break;
         tc::fence_after_sync();
-        if (warp == 0) {  // lanes 0..15 hold column j of L and of M; tensor-memory column = row i
+        if (warp == 0) {  // lanes 0..15 hold column j of L and of M; tensor-memory column = row i.  Kc is dead: L, M go over it.
             uint32_t l16[16], m16[16];
             tc::tmem_ld16(tc::tmem_addr(tm, 0, 0), l16);
             tc::tmem_ld16(tc::tmem_addr(tm, 0, 16), m16);
@@ -325,10 +387,40 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
                 float o = __uint_as_float(qs[i]);
 #pragma unroll
                 for (int j = 0; j <= i; ++j) o = fmaf(Mf[i * WIN + j], D[j], o);
-                if (i < n) p.out[((un.row0 + i) * p.H + un.h) * DV + t] = f32_to_bf16_bits(o);
+                if constexpr (LAYER) reinterpret_cast<float*>(smem + vStage)[i * DV + t] = o;  // W and Qgb are dead
+                else if (i < n) p.out[(un.row0 + i) * p.out_stride + (long long)un.h * DV + t] = f32_to_bf16_bits(o);
             }
         }
         tc::fence_before_sync();  // the next unit's products overwrite these tensor-memory columns
+        if constexpr (LAYER) {
+            // The gated RMSNorm (reference kda.cu:188-201): a warp takes four rows, a lane four value channels.
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = warp * 4 + k;
+                if (i >= n) break;
+                const float4 y4 = *reinterpret_cast<const float4*>(smem + vStage + (i * DV + lane * 4) * 4);
+                const float y[4] = {y4.x, y4.y, y4.z, y4.w};
+                float ss = 0.0f;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) ss = ss + y[x] * y[x];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, o);
+                const float rinv = 1.0f / sqrtf(ss / (float)DV + p.eps);
+                const long long gr = un.row0 + i;
+                const uint2 gw = *reinterpret_cast<const uint2*>(p.gate + gr * p.gate_stride + (long long)un.h * DV + lane * 4);
+                const float gt[4] = {__uint_as_float(gw.x << 16), __uint_as_float(gw.x & 0xffff0000u), __uint_as_float(gw.y << 16),
+                                     __uint_as_float(gw.y & 0xffff0000u)};
+                uint32_t o2[2];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const float lo = (nw[2 * x] * (y[2 * x] * rinv)) * sigmoid_(gt[2 * x]);
+                    const float hi = (nw[2 * x + 1] * (y[2 * x + 1] * rinv)) * sigmoid_(gt[2 * x + 1]);
+                    o2[x] = (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+                }
+                *reinterpret_cast<uint2*>(p.out + gr * p.out_stride + (long long)un.h * DV + lane * 4) = make_uint2(o2[0], o2[1]);
+            }
+        }
     }
     cp_async_wait<0>();
     tc::fence_before_sync();
@@ -336,20 +428,29 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
     if (warp == 0) tc::tmem_dealloc(tm, kVCols);
 }
 
-}  // namespace
-
-// Whether the chunked verify can take this call: bf16 states, no state written, no fused norm, 16-byte aligned rows.
-int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
-                          const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, const int64_t* state_off,
-                          glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
+template <bool LAYER>
+int launch_verify(const VParams& p, cudaStream_t stream) {
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(verify_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVSmem);
+        const cudaError_t e = cudaFuncSetAttribute(verify_tc_kernel<LAYER>, cudaFuncAttributeMaxDynamicSharedMemorySize, Map<LAYER>::kSmem);
         if (e != cudaSuccess) return (int)e;
         configured_dev = dev;
     }
+    if (p.status == nullptr) return (int)cudaErrorUnknown;
+    const long long cap = 3LL * sm_count();
+    verify_tc_kernel<LAYER><<<(unsigned)(p.units < cap ? p.units : cap), kVThreads, Map<LAYER>::kSmem, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// The chunked verify of the core entry point: bf16 states, no state written, no fused norm, 16-byte aligned rows (the
+// caller checks).
+int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* q, const glm53f_bf16* k,
+                          const glm53f_bf16* v, const float* g, const float* beta, const void* state_in, const int64_t* state_off,
+                          glm53f_bf16* out, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
     VParams p{};
     p.H = heads;
     p.units = (long long)heads * batch;
@@ -358,12 +459,29 @@ int core_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, 
     p.state = reinterpret_cast<const uint16_t*>(state_in);
     p.state_off = reinterpret_cast<const long long*>(state_off);
     p.out = out;
+    p.out_stride = (long long)heads * DV;
     p.k_save = k_save; p.v_save = v_save; p.g_save = g_save; p.b_save = b_save;
     p.status = status_word();
-    if (p.status == nullptr) return (int)cudaErrorUnknown;
-    const long long cap = 3LL * sm_count();
-    verify_tc_kernel<<<(unsigned)(p.units < cap ? p.units : cap), kVThreads, kVSmem, stream>>>(p);
-    return (int)cudaGetLastError();
+    return launch_verify<false>(p, stream);
+}
+
+// The chunked verify of the layer entry point, after verify_prologue_launch on the same stream: the saves hold k, v, the
+// decay multiplier and beta of every window row, `out` holds q as fp16 and receives the gated, normalised outputs.
+int layer_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const void* state_in, const int64_t* state_off,
+                           const glm53f_bf16* gate, int64_t gate_stride, const glm53f_bf16* norm_w, float eps, glm53f_bf16* out,
+                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
+    VParams p{};
+    p.H = heads;
+    p.units = (long long)heads * batch;
+    p.cu = cu_rows;
+    p.state = reinterpret_cast<const uint16_t*>(state_in);
+    p.state_off = reinterpret_cast<const long long*>(state_off);
+    p.out = out;
+    p.out_stride = out_stride;
+    p.k_save = k_save; p.v_save = v_save; p.g_save = g_save; p.b_save = b_save;
+    p.gate = gate; p.gate_stride = gate_stride; p.norm_w = norm_w; p.eps = eps;
+    p.status = status_word();
+    return launch_verify<true>(p, stream);
 }
 
 }  // namespace kda

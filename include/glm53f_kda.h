@@ -397,6 +397,22 @@ int glm53f_kda_gather_close(const glm53f_kda_gather_handle* handle, void* full);
  * GLM53F_KDA_PREFILL=chunked makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */
 int32_t glm53f_kda_prefill_mode(int32_t mode);
 
+/* Which form glm53f_kda_chain_batch_bf16state runs for a draft-verification call, i.e. one with state_out == NULL and
+ * the four replay saves given (crates/glm53f-forward/src/forward.rs:3672-3735 with `saves`); not in the reference's
+ * header.  Every other call of the chain entry points is unaffected.
+ *   0  exact (the default): the row-by-row recurrence, bit for bit the reference kernel's outputs and saves
+ *   1  chunked: each request's window of up to 16 rows is one chunk on the tensor cores.  Two launches, nothing
+ *      allocated: the first writes the replay saves (k, v, exp(log decay), beta: the exact form's bits, so a commit
+ *      still leaves the states of serial decode steps) and parks q, as fp16, in the output rows; the second reads the
+ *      bf16 state once per (request, head) and overwrites the output rows with the gated, normalised outputs, which
+ *      agree with the exact form's to the rounding of bf16 operands (the task's tolerances: 2e-2 max-abs, 5e-3 rel-L2
+ *      before the norm).  A window longer than 16 rows records status 122 (glm53f_kda_device_status) and only its
+ *      first 16 rows are computed.  Calls whose rows are not aligned for vector access (p, a, g, conv 8 bytes; out,
+ *      the saves, the state base 16 bytes; strides multiples of 4, out_stride of 8 elements) run the exact form.
+ * Any other value only queries.  Returns the mode that was in force.  The environment variable GLM53F_KDA_VERIFY=chunked
+ * makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */
+int32_t glm53f_kda_verify_mode(int32_t mode);
+
 /* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The persistent recurrent kernel
  * (the layer entry points, the replays, and core calls with fused norms or an output gate) bounds every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
  * status code (101-108, which wait), makes its other waits return, and the kernel ends; the context stays usable and

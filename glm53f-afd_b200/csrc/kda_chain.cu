@@ -66,9 +66,18 @@ namespace {
 
 enum Mode : int { kLayer = 0, kCore = 1, kReplay = 2 };
 
-constexpr int kRecWarps = 16, kProWarps = 2;
-constexpr int kRecThreads = kRecWarps * 32, kProThreads = kProWarps * 32;
-constexpr int kThreads = kRecThreads + kProThreads + 64;  // + epilogue warp + mover warp
+constexpr int kRecWarps = 16, kRecThreads = kRecWarps * 32;
+// Prologue warps per mode.  The layer prologue (conv + SiLU, decay, gate: ~740 warp instructions per row in dependent
+// chains of divisions and exponentials) on two warps was the slowest stage of a layer call (measured: decode through
+// the layer symbol 0.746 -> 0.657 ms per step with four, the exact verify 24.5 -> 19.1 ms, an exact prefill lane
+// 2.05 -> 1.57 ms, the replay 4.97 -> 4.72 ms); the core prologue is a widening and one exponential per channel, and
+// there two more warps only take registers and issue slots from the recurrence (0.538 -> 0.566 ms).
+template <int MODE>
+constexpr int kProWarpsOf = MODE == 1 /* kCore */ ? 2 : 4;
+template <int MODE>
+constexpr int kProThreadsOf = kProWarpsOf<MODE> * 32;
+template <int MODE>
+constexpr int kThreadsOf = kRecThreads + kProThreadsOf<MODE> + 64;  // + epilogue warp + mover warp
 constexpr int kRowsPerLane = DV / kRecWarps;              // 8
 constexpr unsigned FULL = 0xffffffffu;
 
@@ -606,6 +615,7 @@ __device__ __forceinline__ void l2norm_warp(const float* x, float* y, int lane, 
 template <typename S, int MODE>
 __device__ void prologue_role(const Params& p, unsigned char* smem, uint64_t* bars, const WaitCtx& ctx, int t) {
     using L = Smem<S, MODE>;
+    constexpr int kProThreads = kProThreadsOf<MODE>;
     uint64_t* raw_full = bars + 2 * L::kStateSlots;
     uint64_t* raw_empty = raw_full + L::kRawSlots;
     uint64_t* row_full = raw_empty + L::kRawSlots;
@@ -838,8 +848,9 @@ __device__ void epilogue_role(const Params& p, unsigned char* smem, uint64_t* ba
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
 template <typename S, int MODE>
-__global__ void __launch_bounds__(kThreads, 1) recurrent_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(kThreadsOf<MODE>, 1) recurrent_kernel(const __grid_constant__ Params p) {
     using L = Smem<S, MODE>;
+    constexpr int kProWarps = kProWarpsOf<MODE>, kProThreads = kProThreadsOf<MODE>;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::oBars);
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + L::oCtl);
@@ -1038,7 +1049,7 @@ int launch(const Params& p, cudaStream_t stream) {
     }();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kThreadsOf<MODE>);
     cfg.dynamicSmemBytes = L::kBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -1,26 +1,30 @@
-// The layer prologue of the chunked prefill: projection rows to the core's inputs.
+// The layer prologue of the chunked forms: projection rows to the core's inputs.
 //
-// The layer entry points take the engine's rows (q | k | v projections, beta logits, the forget-gate row); the chunk-64
+// The layer entry points take the engine's rows (q | k | v projections, beta logits, the forget-gate row); the chunked
 // tensor-core kernels take what the recurrence is defined on: q and k after the short convolution, SiLU and the L2
-// norms, v after the convolution and SiLU, the per-channel LOG decay and beta.  This kernel computes those for one pass
-// of rows with the chain's own arithmetic (reference kernels/kda.cu:129-165 = kernels/kda_prefill.cu:121-208; this
-// file is compiled without multiply-add contraction like the chain): four taps summed in order, one bf16 rounding
-// after the SiLU, decay exp(lower * sigmoid(exp(A_log) (a + dt_bias))) kept as its logarithm, beta = bf16(sigmoid(b)),
-// each L2 norm as a lane's four consecutive channels summed in order, then the xor butterfly.  q and k are then
-// rounded to fp16 (they lie in [-1, 1]; eleven mantissa bits), the one place where the chunked path departs from the
-// chain's FP32 q and k before the tensor-core products: with bf16's eight bits the rounding of k alone, which reaches
-// the state through K^T D, would take the state's whole error budget when few rows dominate it.
+// norms, v after the convolution and SiLU, the per-channel decay and beta.  This kernel computes those with the
+// chain's own arithmetic (reference kernels/kda.cu:129-165 = kernels/kda_prefill.cu:121-208; this file is compiled
+// without multiply-add contraction like the chain): four taps summed in order, one bf16 rounding after the SiLU, decay
+// exp(lower * sigmoid(exp(A_log) (a + dt_bias))), beta = bf16(sigmoid(b)), each L2 norm as a lane's four consecutive
+// channels summed in order, then the xor butterfly.
 //
-// One warp per (request, head, run of 16 rows); a lane owns four consecutive channels, so the norms need no shared
-// memory, and the three earlier rows of the convolution slide along in registers.
+// One warp per (request, head, row); a lane owns four consecutive channels, so the norms need no shared memory.  The
+// work is bound by instruction issue (about 850 instructions per row and lane, most of them IEEE divisions and
+// exponentials), so a warp takes ONE row and reads its three predecessors again (the four warps of a block take four
+// consecutive rows; the predecessors come from L1/L2): every load of a warp is in flight at once and 79 registers
+// allow 24 resident warps per SM.  (A warp that walks 16 rows with the three earlier rows sliding in registers needs
+// 143 registers and was half as fast.)
 //
-// The same arithmetic feeds the chunked form of draft verification behind glm53f_kda_chain_batch_bf16state
-// (verify_prologue_kernel): there the call's own buffers take the results, so nothing is allocated -- k, v, the decay
-// multiplier exp(log decay) and beta go to the replay saves, which a verify call must write anyway and which hold
-// exactly these values (the bits the exact form saves), and q goes, as fp16, to the 256 bytes of `out` that the same
-// (row, head) output will overwrite.  Windows are short (up to 16 rows) and the work is bound by instruction issue
-// (IEEE divisions and exponentials), so there a warp takes ONE row and reads its three predecessors again (they come
-// from L1/L2): every load of a warp is in flight at once and the registers allow twice the resident warps.
+// Two sinks:
+//  * a prefill pass: dense core inputs for one pass of rows in the caller's workspace.  q and k are rounded to fp16
+//    (they lie in [-1, 1]; eleven mantissa bits), the one place where the chunked prefill departs from the chain's
+//    FP32 q and k before the tensor-core products: with bf16's eight bits the rounding of k alone, which reaches the
+//    state through K^T D, would take the state's whole error budget when few rows dominate it.  The decay is kept as
+//    its logarithm.
+//  * a verify call (VERIFY): the call's own buffers take the results, so nothing is allocated -- k (f32), v, the decay
+//    multiplier exp(log decay) and beta go to the replay saves, which a verify call must write anyway and which hold
+//    exactly these values (the bits the exact form saves), and q goes, as fp16, to the 256 bytes of `out` that the
+//    same (row, head) output will overwrite.  Windows of up to 16 rows.
 
 #include <cuda_fp16.h>
 
@@ -31,11 +35,11 @@
 namespace kda {
 namespace {
 
-constexpr int kRun = 16;  // rows per warp
 constexpr unsigned FULL = 0xffffffffu;
+constexpr int kVerifyWindow = 16;
 
 struct ProParams {
-    int H, batch, pass_rows, row_shift;
+    int H, batch, pass_rows, row_shift;  // rows row_shift .. row_shift + pass_rows - 1 of every request
     const int32_t* cu;
     const uint16_t* P;
     long long p_stride, b_off;
@@ -47,8 +51,13 @@ struct ProParams {
     const float* a_log;
     const float* dt_bias;
     float lower;
+    // prefill pass: [batch * pass_rows][H][128] (beta [batch * pass_rows][H])
     uint16_t *q, *k, *v;
     float *g, *beta;
+    // verify: q as fp16 into the output rows (through `q`), the rest into the replay saves
+    long long out_stride;
+    float *k_save, *g_save, *b_save;
+    uint16_t* v_save;
 };
 
 __device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -72,133 +81,24 @@ __device__ __forceinline__ uint2 pack4(const float (&x)[4]) {
                       (uint32_t)f32_to_bf16_bits(x[2]) | ((uint32_t)f32_to_bf16_bits(x[3]) << 16));
 }
 
-__global__ void __launch_bounds__(128) layer_prologue_kernel(const ProParams p) {
-    const int lane = threadIdx.x & 31;
-    const long long task = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int runs = p.pass_rows / kRun, H = p.H;
-    if (task >= (long long)p.batch * runs * H) return;
-    const int h = (int)(task % H), run = (int)((task / H) % runs), b = (int)(task / ((long long)H * runs));
-    const int r0 = p.cu[b], n = min(max(p.cu[b + 1] - r0 - p.row_shift, 0), p.pass_rows);
-    const int j0 = run * kRun;
-    if (j0 >= n) return;
-    const int j1 = min(j0 + kRun, n), c0 = lane * 4;
-    const long long C = 3LL * H * DK;
-    const uint16_t* window = p.conv + p.conv_off[b];
-    // Row jj of the request (jj < 0: the conv window), part 0..2, this lane's four channels.
-    auto load_x = [&](int jj, int part, float (&x)[4]) {
-        const uint16_t* row = jj < 0 ? window + (long long)(WINDOW + jj) * C : p.P + ((long long)r0 + jj) * p.p_stride;
-        unpack4(*reinterpret_cast<const uint2*>(row + ((long long)part * H + h) * DK + c0), x);
-    };
-    float w[3][4][TAPS];  // [part][channel][tap]
-#pragma unroll
-    for (int part = 0; part < 3; ++part) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.cw + (((long long)part * H + h) * DK + c0) * TAPS);
-        const uint4 lo = src[0], hi = src[1];
-        const uint32_t ww[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            w[part][c][0] = __uint_as_float(ww[2 * c] << 16);
-            w[part][c][1] = __uint_as_float(ww[2 * c] & 0xffff0000u);
-            w[part][c][2] = __uint_as_float(ww[2 * c + 1] << 16);
-            w[part][c][3] = __uint_as_float(ww[2 * c + 1] & 0xffff0000u);
-        }
-    }
-    const float4 dtb4 = *reinterpret_cast<const float4*>(p.dt_bias + (long long)h * DK + c0);
-    const float dtb[4] = {dtb4.x, dtb4.y, dtb4.z, dtb4.w};
-    const float decay_rate = expf(p.a_log[h]);
-    float hist[3][3][4];  // [rows back: 3, 2, 1][part][channel]
-    const int first = p.row_shift + j0;
-#pragma unroll
-    for (int d = 0; d < 3; ++d)
-#pragma unroll
-        for (int part = 0; part < 3; ++part) load_x(first - 3 + d, part, hist[d][part]);
-
-    for (int j = j0; j < j1; ++j) {
-        const int jj = p.row_shift + j;
-        const long long gr = (long long)r0 + jj, orow = (long long)b * p.pass_rows + j, at = (orow * H + h) * DK + c0;
-        float cur[3][4], act[3][4];
-#pragma unroll
-        for (int part = 0; part < 3; ++part) {
-            load_x(jj, part, cur[part]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float acc = 0.0f;
-                acc = acc + w[part][c][0] * hist[0][part][c];
-                acc = acc + w[part][c][1] * hist[1][part][c];
-                acc = acc + w[part][c][2] * hist[2][part][c];
-                acc = acc + w[part][c][3] * cur[part][c];
-                act[part][c] = bf16_round(acc / (1.0f + expf(-acc)));
-                hist[0][part][c] = hist[1][part][c];
-                hist[1][part][c] = hist[2][part][c];
-                hist[2][part][c] = cur[part][c];
-            }
-        }
-        // L2 norms of q and k (eps 1e-6 inside the root), q also times 128^-0.5.
-        float qn[4], kn[4];
-        {
-            float sq = 0.0f, sk = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                sq = sq + act[0][c] * act[0][c];
-                sk = sk + act[1][c] * act[1][c];
-            }
-            sq = butterfly(sq);
-            sk = butterfly(sk);
-            const float iq = 1.0f / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                qn[c] = (act[0][c] * iq) * (1.0f / sqrtf((float)DK));
-                kn[c] = act[1][c] * ik;
-            }
-        }
-        float a4[4], lg[4];
-        unpack4(*reinterpret_cast<const uint2*>(p.A + gr * p.a_stride + (long long)h * DK + c0), a4);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) lg[c] = p.lower * sigmoid_(decay_rate * (a4[c] + dtb[c]));
-        *reinterpret_cast<uint2*>(p.q + at) = pack4_fp16(qn);
-        *reinterpret_cast<uint2*>(p.k + at) = pack4_fp16(kn);
-        *reinterpret_cast<uint2*>(p.v + at) = pack4(act[2]);
-        *reinterpret_cast<float4*>(p.g + at) = make_float4(lg[0], lg[1], lg[2], lg[3]);
-        if (lane == 0) p.beta[orow * H + h] = bf16_round(sigmoid_(bf16_bits_to_f32(p.P[gr * p.p_stride + p.b_off + h])));
-    }
-}
-
-struct VerifyProParams {
-    int H, batch;
-    const int32_t* cu;
-    const uint16_t* P;
-    long long p_stride, b_off;
-    const uint16_t* A;
-    long long a_stride;
-    const uint16_t* conv;
-    const long long* conv_off;
-    const uint16_t* cw;
-    const float* a_log;
-    const float* dt_bias;
-    float lower;
-    uint16_t* q;  // the output rows: q as fp16
-    long long out_stride;
-    float *k_save, *g_save, *b_save;
-    uint16_t* v_save;
-};
-constexpr int kVerifyWindow = 16;
-
-__global__ void __launch_bounds__(128, 6) verify_prologue_kernel(const VerifyProParams p) {
+template <bool VERIFY>
+__global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams p) {
     const int lane = threadIdx.x & 31, H = p.H;
     // a block = four consecutive rows of one (request, head): neighbours share their predecessors in L1
-    const long long unit = blockIdx.x / (kVerifyWindow / 4);
-    const int j = (int)(blockIdx.x % (kVerifyWindow / 4)) * 4 + (threadIdx.x >> 5);
+    const int quads = p.pass_rows / 4;
+    const long long unit = blockIdx.x / quads;
+    const int j = (int)(blockIdx.x % quads) * 4 + (threadIdx.x >> 5);  // row of the pass
     const int h = (int)(unit % H), b = (int)(unit / H);
-    const int r0 = p.cu[b], n = min(max(p.cu[b + 1] - r0, 0), kVerifyWindow);
+    const int r0 = p.cu[b], n = min(max(p.cu[b + 1] - r0 - p.row_shift, 0), p.pass_rows);
     if (j >= n) return;
-    const int c0 = lane * 4;
-    const long long C = 3LL * H * DK, gr = (long long)r0 + j;
+    const int c0 = lane * 4, jj = p.row_shift + j;  // row of the request
+    const long long C = 3LL * H * DK, gr = (long long)r0 + jj;
     const uint16_t* window = p.conv + p.conv_off[b];
-    uint2 x[TAPS][3];  // [tap: rows j-3 .. j][part]
+    uint2 x[TAPS][3];  // [tap: rows jj-3 .. jj][part]; rows before the request's first come from the conv window
 #pragma unroll
     for (int d = 0; d < TAPS; ++d) {
-        const int jj = j - 3 + d;
-        const uint16_t* row = jj < 0 ? window + (long long)(WINDOW + jj) * C : p.P + ((long long)r0 + jj) * p.p_stride;
+        const int rr = jj - 3 + d;
+        const uint16_t* row = rr < 0 ? window + (long long)(WINDOW + rr) * C : p.P + ((long long)r0 + rr) * p.p_stride;
 #pragma unroll
         for (int part = 0; part < 3; ++part) x[d][part] = *reinterpret_cast<const uint2*>(row + ((long long)part * H + h) * DK + c0);
     }
@@ -231,6 +131,7 @@ __global__ void __launch_bounds__(128, 6) verify_prologue_kernel(const VerifyPro
             act[part][c] = bf16_round(acc / (1.0f + expf(-acc)));
         }
     }
+    // L2 norms of q and k (eps 1e-6 inside the root), q also times 128^-0.5.
     float qn[4], kn[4];
     {
         float sq = 0.0f, sk = 0.0f;
@@ -248,47 +149,45 @@ __global__ void __launch_bounds__(128, 6) verify_prologue_kernel(const VerifyPro
             kn[c] = act[1][c] * ik;
         }
     }
-    float a4[4], dec[4];
+    float a4[4], lg[4];
     unpack4(a_bits, a4);
     const float dtb[4] = {dtb4.x, dtb4.y, dtb4.z, dtb4.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) dec[c] = expf(p.lower * sigmoid_(decay_rate * (a4[c] + dtb[c])));
-    const long long sv = (gr * H + h) * DK + c0;
-    *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);
-    *reinterpret_cast<float4*>(p.k_save + sv) = make_float4(kn[0], kn[1], kn[2], kn[3]);
-    *reinterpret_cast<uint2*>(p.v_save + sv) = pack4(act[2]);
-    *reinterpret_cast<float4*>(p.g_save + sv) = make_float4(dec[0], dec[1], dec[2], dec[3]);
-    if (lane == 0) p.b_save[gr * H + h] = bf16_round(sigmoid_(blogit));
+    for (int c = 0; c < 4; ++c) lg[c] = p.lower * sigmoid_(decay_rate * (a4[c] + dtb[c]));
+    const float bt = bf16_round(sigmoid_(blogit));
+    if constexpr (VERIFY) {
+        const long long sv = (gr * H + h) * DK + c0;
+        *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);
+        *reinterpret_cast<float4*>(p.k_save + sv) = make_float4(kn[0], kn[1], kn[2], kn[3]);
+        *reinterpret_cast<uint2*>(p.v_save + sv) = pack4(act[2]);
+        *reinterpret_cast<float4*>(p.g_save + sv) = make_float4(expf(lg[0]), expf(lg[1]), expf(lg[2]), expf(lg[3]));
+        if (lane == 0) p.b_save[gr * H + h] = bt;
+    } else {
+        const long long orow = (long long)b * p.pass_rows + j, at = (orow * H + h) * DK + c0;
+        *reinterpret_cast<uint2*>(p.q + at) = pack4_fp16(qn);
+        *reinterpret_cast<uint2*>(p.k + at) = pack4_fp16(kn);
+        *reinterpret_cast<uint2*>(p.v + at) = pack4(act[2]);
+        *reinterpret_cast<float4*>(p.g + at) = make_float4(lg[0], lg[1], lg[2], lg[3]);
+        if (lane == 0) p.beta[orow * H + h] = bt;
+    }
+}
+
+template <bool VERIFY>
+int launch(const ProParams& pp, cudaStream_t stream) {
+    const long long blocks = (long long)pp.batch * pp.H * (pp.pass_rows / 4);
+    if (blocks > 0x7fffffffLL) return kInvalid;
+    layer_prologue_kernel<VERIFY><<<(unsigned)blocks, 128, 0, stream>>>(pp);
+    return (int)cudaGetLastError();
 }
 
 }  // namespace
-
-// The prologue of the chunked verify: windows of up to 16 rows per request; see the head of the file for where the
-// results go.  The caller checks the alignment of every row.
-int verify_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
-                           const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* conv, const int64_t* conv_off,
-                           const glm53f_bf16* conv_w, const float* a_log, const float* dt_bias, float lower, glm53f_bf16* out,
-                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
-    VerifyProParams pp{};
-    pp.H = heads; pp.batch = batch;
-    pp.cu = cu_rows;
-    pp.P = p; pp.p_stride = p_stride; pp.b_off = b_off;
-    pp.A = a; pp.a_stride = a_stride;
-    pp.conv = conv; pp.conv_off = reinterpret_cast<const long long*>(conv_off); pp.cw = conv_w;
-    pp.a_log = a_log; pp.dt_bias = dt_bias; pp.lower = lower;
-    pp.q = out; pp.out_stride = out_stride;
-    pp.k_save = k_save; pp.v_save = v_save; pp.g_save = g_save; pp.b_save = b_save;
-    const long long blocks = (long long)batch * heads * (kVerifyWindow / 4);
-    verify_prologue_kernel<<<(unsigned)blocks, 128, 0, stream>>>(pp);
-    return (int)cudaGetLastError();
-}
 
 int layer_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, int32_t pass_rows, int32_t row_shift,
                           const glm53f_bf16* p, int64_t p_stride, int64_t b_off, const glm53f_bf16* a, int64_t a_stride,
                           const glm53f_bf16* conv, const int64_t* conv_off, const glm53f_bf16* conv_w, const float* a_log,
                           const float* dt_bias, float lower, glm53f_bf16* q, glm53f_bf16* k, glm53f_bf16* v, float* g, float* beta,
                           cudaStream_t stream) {
-    if (pass_rows < kRun || pass_rows % kRun != 0) return kInvalid;
+    if (pass_rows < 16 || pass_rows % 16 != 0) return kInvalid;
     ProParams pp{};
     pp.H = heads; pp.batch = batch; pp.pass_rows = pass_rows; pp.row_shift = row_shift;
     pp.cu = cu_rows;
@@ -297,9 +196,25 @@ int layer_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, 
     pp.conv = conv; pp.conv_off = reinterpret_cast<const long long*>(conv_off); pp.cw = conv_w;
     pp.a_log = a_log; pp.dt_bias = dt_bias; pp.lower = lower;
     pp.q = q; pp.k = k; pp.v = v; pp.g = g; pp.beta = beta;
-    const long long tasks = (long long)batch * (pass_rows / kRun) * heads;
-    layer_prologue_kernel<<<(unsigned)((tasks + 3) / 4), 128, 0, stream>>>(pp);
-    return (int)cudaGetLastError();
+    return launch<false>(pp, stream);
+}
+
+// The prologue of the chunked verify: windows of up to 16 rows per request; see the head of the file for where the
+// results go.  The caller checks the alignment of every row.
+int verify_prologue_launch(int32_t heads, int32_t batch, const int32_t* cu_rows, const glm53f_bf16* p, int64_t p_stride, int64_t b_off,
+                           const glm53f_bf16* a, int64_t a_stride, const glm53f_bf16* conv, const int64_t* conv_off,
+                           const glm53f_bf16* conv_w, const float* a_log, const float* dt_bias, float lower, glm53f_bf16* out,
+                           int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream) {
+    ProParams pp{};
+    pp.H = heads; pp.batch = batch; pp.pass_rows = kVerifyWindow; pp.row_shift = 0;
+    pp.cu = cu_rows;
+    pp.P = p; pp.p_stride = p_stride; pp.b_off = b_off;
+    pp.A = a; pp.a_stride = a_stride;
+    pp.conv = conv; pp.conv_off = reinterpret_cast<const long long*>(conv_off); pp.cw = conv_w;
+    pp.a_log = a_log; pp.dt_bias = dt_bias; pp.lower = lower;
+    pp.q = out; pp.out_stride = out_stride;
+    pp.k_save = k_save; pp.v_save = v_save; pp.g_save = g_save; pp.b_save = b_save;
+    return launch<true>(pp, stream);
 }
 
 }  // namespace kda

@@ -461,20 +461,25 @@ __device__ __forceinline__ float butterfly1(float x) {
 }
 
 // One delta-rule step on a lane's 8 x 4 tile (reference kda.cu:38-53): decay, read with k, correct toward v.
-__device__ __forceinline__ void delta_rule(f32x2 (&s)[kPairs][4], const f32x2 (&kk)[4], const f32x2 (&gg)[4],
-                                           const float* vrow, int warp, int lane, float beta, f32x2 nz) {
+// `v_mine` is v at the value row lane l reduces: row (l >> 2) of the warp's eight.
+__device__ __forceinline__ void delta_rule_v(f32x2 (&s)[kPairs][4], const f32x2 (&kk)[4], const f32x2 (&gg)[4], float v_mine, int lane,
+                                             float beta, f32x2 nz) {
 #pragma unroll
     for (int jp = 0; jp < kPairs; ++jp)
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[jp][i] = mul2(s[jp][i], gg[i], nz);
     const float kv = rows_dot(s, kk, lane, nz);
-    const float mine = (vrow[warp * kRowsPerLane + (lane >> 2)] - kv) * beta;
+    const float mine = (v_mine - kv) * beta;
 #pragma unroll
     for (int jp = 0; jp < kPairs; ++jp) {
         const f32x2 delta = pack2(__shfl_sync(FULL, mine, 8 * jp), __shfl_sync(FULL, mine, 8 * jp + 4));
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[jp][i] = add2(s[jp][i], mul2(kk[i], delta, nz));
     }
+}
+__device__ __forceinline__ void delta_rule(f32x2 (&s)[kPairs][4], const f32x2 (&kk)[4], const f32x2 (&gg)[4],
+                                           const float* vrow, int warp, int lane, float beta, f32x2 nz) {
+    delta_rule_v(s, kk, gg, vrow[warp * kRowsPerLane + (lane >> 2)], lane, beta, nz);
 }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -1021,6 +1026,81 @@ int launch_small(const Params& p, cudaStream_t stream) {
     return (int)cudaLaunchKernelEx(&cfg, core_small_kernel<S>, q);
 }
 
+// ---- the replay on many small blocks ---------------------------------------------------------------------------
+// A commit replays keep[b] saved rows onto every (request, layer, head) state: no read-out, no norms, inputs that are
+// already cooked.  Eight of a unit's value rows never interact with the others, and what a lane needs of a saved row is
+// exactly a 16-byte piece of k and of the decay (its four key channels), one v and beta: so a WARP is the unit of work
+// here -- no shared memory, no barrier, the next row's inputs loaded into registers while the current row's delta rule
+// runs -- and 32 such warps are resident on an SM where the persistent kernel has one unit's 16.  Same delta_rule, same
+// rounding points (a bf16 state is rounded after every row), so the bits are the persistent kernel's and the
+// reference's.  Measured at 48 slots x 34 layers, accepted prefixes drawn from 0..16: see the bench's verify.commit.
+struct ReplayRow {
+    float4 k, g;
+    float v, beta;
+};
+__device__ __forceinline__ ReplayRow replay_row(const Params& p, long long kv_base, long long b_base, long long gr, int h, int uw, int lane) {
+    ReplayRow x;
+    const long long at = kv_base + (gr * p.H + h) * DK;
+    x.k = *reinterpret_cast<const float4*>(p.k_save + at + lane * 4);
+    x.g = *reinterpret_cast<const float4*>(p.g_save + at + lane * 4);
+    x.v = bf16_bits_to_f32(p.v_save[at + uw * kRowsPerLane + (lane >> 2)]);
+    x.beta = p.b_save[b_base + gr * p.H + h];
+    return x;
+}
+
+template <typename S>
+__global__ void __launch_bounds__(kSmallThreads, sizeof(S) == 4 ? 6 : 8) replay_small_kernel(const __grid_constant__ Params p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const long long unit = blockIdx.x / kSmallParts;
+    const int uw = (int)(blockIdx.x % kSmallParts) * kSmallWarps + warp;  // this warp's place among the unit's 16
+    const int h = (int)(unit % p.H), layer = (int)((unit / p.H) % p.layers), b = (int)(unit / ((long long)p.H * p.layers));
+    const long long r0 = p.cu_rows ? p.cu_rows[b] : 0;
+    int rows = p.keep ? p.keep[b] : p.rows1;
+    if (rows < 0) rows = 0;
+    if (rows == 0 && !copies_state(p)) return;
+    const long long s_elem = (long long)layer * p.state_stride + (p.state_off ? p.state_off[b] : 0) + (long long)h * DV * DK;
+    const long long kv_base = (long long)layer * p.kv_stride, b_base = (long long)layer * p.b_stride;
+    f32x2 s[kPairs][4];
+    load_rows_global<S>(reinterpret_cast<const S*>(p.state_in) + s_elem, uw, lane, s);
+    ReplayRow cur{};
+    if (rows > 0) cur = replay_row(p, kv_base, b_base, r0, h, uw, lane);
+    for (int r = 0; r < rows; ++r) {
+        ReplayRow nxt = cur;
+        if (r + 1 < rows) nxt = replay_row(p, kv_base, b_base, r0 + r + 1, h, uw, lane);
+        const f32x2 kk[4] = {pack2(cur.k.x, cur.k.x), pack2(cur.k.y, cur.k.y), pack2(cur.k.z, cur.k.z), pack2(cur.k.w, cur.k.w)};
+        const f32x2 gg[4] = {pack2(cur.g.x, cur.g.x), pack2(cur.g.y, cur.g.y), pack2(cur.g.z, cur.g.z), pack2(cur.g.w, cur.g.w)};
+        delta_rule_v(s, kk, gg, cur.v, lane, cur.beta, p.neg_zero2);
+        if constexpr (sizeof(S) == 2) {
+            if (r + 1 < rows) round_rows(s);  // the last row's rounding is the store's
+        }
+        cur = nxt;
+    }
+    store_rows_global<S>(reinterpret_cast<S*>(p.state_out) + s_elem, uw, lane, s);
+}
+
+template <typename S>
+int launch_replay_small(const Params& p, cudaStream_t stream) {
+    Params q = p;
+    q.neg_zero2 = 0x8000000080000000ull;
+    static const bool pdl = [] {
+        const char* v = getenv("GLM53F_KDA_PDL");
+        return !(v && v[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.units * kSmallParts));
+    cfg.blockDim = dim3(kSmallThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, replay_small_kernel<S>, q);
+}
+
 template <typename S, int MODE>
 int launch(const Params& p, cudaStream_t stream) {
     using L = Smem<S, MODE>;
@@ -1140,6 +1220,15 @@ int replay_entry(int32_t heads, int32_t layers, int32_t batch, bool batched, con
     q.k_save = const_cast<float*>(k_save); q.v_save = const_cast<glm53f_bf16*>(v_save);
     q.g_save = const_cast<float*>(g_save); q.b_save = const_cast<float*>(b_save);
     q.kv_stride = kv_stride; q.b_stride = b_stride;
+    // The warp-per-eight-rows kernel takes aligned saves and grids that fit; GLM53F_KDA_REPLAY=pipeline keeps the
+    // persistent kernel.
+    static const bool small = [] {
+        const char* e = getenv("GLM53F_KDA_REPLAY");
+        return !(e != nullptr && strcmp(e, "pipeline") == 0);
+    }();
+    auto al16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+    if (small && al16(k_save) && al16(g_save) && kv_stride % 4 == 0 && q.units * kSmallParts <= 0x7fffffffLL)
+        return bf16_state ? launch_replay_small<__nv_bfloat16>(q, (cudaStream_t)stream) : launch_replay_small<float>(q, (cudaStream_t)stream);
     return launch_typed<kReplay>(q, bf16_state, (cudaStream_t)stream);
 }
 

@@ -910,7 +910,9 @@ __global__ void __launch_bounds__(kThreadsOf<MODE>, 1) recurrent_kernel(const __
 // copies: with eight such blocks resident on an SM, and blocks handed out as SMs free up, the loads of some cover the
 // arithmetic and stores of others, a launch's last blocks end within one small block's time of each other, and the
 // next launch's blocks move in as room appears (programmatic dependent launch).  Used for the exact verify, whose 16
-// serial rows a unit want many warps; for single-row decode the persistent kernel above streams faster.
+// serial rows a unit want many warps; for single-row decode the persistent kernel above streams faster.  (A variant
+// without shared memory, every warp cooking its own lanes' pieces of a row as the replay below does, was slower: the
+// sixteen warps of a unit each repeat the row's exponentials -- exact verify 12.0 against 11.1 ms, decode 3,567 GB/s.)
 constexpr int kSmallWarps = 4, kSmallThreads = kSmallWarps * 32, kSmallParts = kRecWarps / kSmallWarps;
 
 template <typename S>

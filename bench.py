@@ -944,8 +944,17 @@ def bind_to_gpu_numa(torch, index):
 def e2e_stepper(torch, layers, layer_in, out_bytes, host_in, dev_in, dev_out, host_out, launch_layer, group=9):
     """One end-to-end step: the step's inputs go from one pinned host block to the device in a few large copies, one
     per group of layers on a copy stream, so that the transfer of the next group runs beside the launches of the
-    current one; the outputs come back the same way; the step ends when its outputs are on the host."""
-    groups = [(a, min(a + group, layers)) for a in range(0, layers, group)]
+    current one; the outputs come back the same way; the step ends when its outputs are on the host.  (34 layers with
+    group = 9: groups of 9, 9, 8, 4, 2, 1, 1 layers.)"""
+    # Groups of `group` layers while many layers remain, then halving down to one: the host-to-device pipe is the
+    # bottleneck, so what a step adds to the transfer time is the work left once the LAST group's inputs have arrived,
+    # and a last group of one layer makes that one launch and one small copy back.
+    groups, a = [], 0
+    while a < layers:
+        left = layers - a
+        n = 1 if left == 1 else min(group, max(1, left // 2))
+        groups.append((a, a + n))
+        a += n
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
 
     def step():

@@ -6,7 +6,8 @@
 // chain's own arithmetic (reference kernels/kda.cu:129-165 = kernels/kda_prefill.cu:121-208; this file is compiled
 // without multiply-add contraction like the chain): four taps summed in order, one bf16 rounding after the SiLU, decay
 // exp(lower * sigmoid(exp(A_log) (a + dt_bias))), beta = bf16(sigmoid(b)), each L2 norm as a lane's four consecutive
-// channels summed in order, then the xor butterfly.
+// channels summed in order, then the xor butterfly.  (Bit for bit in the verify sink; the prefill sink uses the
+// hardware's approximate division, exponential and reciprocal root, see sigmoid_ below.)
 //
 // One warp per (request, head, row); a lane owns four consecutive channels, so the norms need no shared memory.  The
 // work is bound by instruction issue (about 850 instructions per row and lane, most of them IEEE divisions and
@@ -60,7 +61,24 @@ struct ProParams {
     uint16_t* v_save;
 };
 
-__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// The verify sink keeps the chain's IEEE arithmetic (its results are the replay saves, bit for bit); the prefill sink
+// feeds tensor-core products that round every operand to bf16 anyway, so there the divisions, exponentials and
+// reciprocal roots are the hardware approximations (a few ulp of FP32): a third of the instructions.
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_(float x) {
+    if constexpr (FAST) return __fdividef(1.0f, 1.0f + __expf(-x));
+    else return 1.0f / (1.0f + expf(-x));
+}
+template <bool FAST>
+__device__ __forceinline__ float silu_(float x) {
+    if constexpr (FAST) return __fdividef(x, 1.0f + __expf(-x));
+    else return x / (1.0f + expf(-x));
+}
+template <bool FAST>
+__device__ __forceinline__ float inv_norm_(float ss) {
+    if constexpr (FAST) return rsqrtf(ss + 1e-6f);
+    else return 1.0f / sqrtf(ss + 1e-6f);
+}
 __device__ __forceinline__ float butterfly(float x) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) x = x + __shfl_xor_sync(FULL, x, o);
@@ -128,7 +146,7 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
             acc = acc + __uint_as_float(ww[2 * c] & 0xffff0000u) * xv[1][c];
             acc = acc + __uint_as_float(ww[2 * c + 1] << 16) * xv[2][c];
             acc = acc + __uint_as_float(ww[2 * c + 1] & 0xffff0000u) * xv[3][c];
-            act[part][c] = bf16_round(acc / (1.0f + expf(-acc)));
+            act[part][c] = bf16_round(silu_<!VERIFY>(acc));
         }
     }
     // L2 norms of q and k (eps 1e-6 inside the root), q also times 128^-0.5.
@@ -142,7 +160,7 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
         }
         sq = butterfly(sq);
         sk = butterfly(sk);
-        const float iq = 1.0f / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+        const float iq = inv_norm_<!VERIFY>(sq), ik = inv_norm_<!VERIFY>(sk);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             qn[c] = (act[0][c] * iq) * (1.0f / sqrtf((float)DK));
@@ -153,8 +171,8 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
     unpack4(a_bits, a4);
     const float dtb[4] = {dtb4.x, dtb4.y, dtb4.z, dtb4.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) lg[c] = p.lower * sigmoid_(decay_rate * (a4[c] + dtb[c]));
-    const float bt = bf16_round(sigmoid_(blogit));
+    for (int c = 0; c < 4; ++c) lg[c] = p.lower * sigmoid_<!VERIFY>(decay_rate * (a4[c] + dtb[c]));
+    const float bt = bf16_round(sigmoid_<!VERIFY>(blogit));
     if constexpr (VERIFY) {
         const long long sv = (gr * H + h) * DK + c0;
         *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);

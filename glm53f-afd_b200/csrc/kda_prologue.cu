@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
             acc = acc + __uint_as_float(ww[2 * c] & 0xffff0000u) * xv[1][c];
             acc = acc + __uint_as_float(ww[2 * c + 1] << 16) * xv[2][c];
             acc = acc + __uint_as_float(ww[2 * c + 1] & 0xffff0000u) * xv[3][c];
-            act[part][c] = bf16_round(silu_<!VERIFY>(acc));
+            // q reaches only the outputs, which carry bf16-operand rounding in both chunked forms: always the fast form
+            act[part][c] = bf16_round(part == 0 ? silu_<true>(acc) : silu_<!VERIFY>(acc));
         }
     }
     // L2 norms of q and k (eps 1e-6 inside the root), q also times 128^-0.5.
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
         }
         sq = butterfly(sq);
         sk = butterfly(sk);
-        const float iq = inv_norm_<!VERIFY>(sq), ik = inv_norm_<!VERIFY>(sk);
+        const float iq = inv_norm_<true>(sq), ik = inv_norm_<!VERIFY>(sk);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             qn[c] = (act[0][c] * iq) * (1.0f / sqrtf((float)DK));

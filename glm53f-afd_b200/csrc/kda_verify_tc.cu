@@ -95,7 +95,9 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ int sw_elem(int R, int r, int c) {
     return (c >> 6) * R * 128 + r * 128 + (((((c & 63) >> 3) ^ (r & 7))) << 4) + (c & 7) * 2;
 }
-__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// The output gate: these outputs carry the rounding of bf16 operands already, so the hardware's approximate exponential
+// and division do (the file's other divisions and exponentials keep IEEE arithmetic for the replay saves).
+__device__ __forceinline__ float sigmoid_(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 struct Unit {
     int b, h, n;
@@ -406,7 +408,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
                 for (int x = 0; x < 4; ++x) ss = ss + y[x] * y[x];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) ss = ss + __shfl_xor_sync(0xffffffffu, ss, o);
-                const float rinv = 1.0f / sqrtf(ss / (float)DV + p.eps);
+                const float rinv = rsqrtf(ss * (1.0f / (float)DV) + p.eps);
                 const long long gr = un.row0 + i;
                 const uint2 gw = *reinterpret_cast<const uint2*>(p.gate + gr * p.gate_stride + (long long)un.h * DV + lane * 4);
                 const float gt[4] = {__uint_as_float(gw.x << 16), __uint_as_float(gw.x & 0xffff0000u), __uint_as_float(gw.y << 16),

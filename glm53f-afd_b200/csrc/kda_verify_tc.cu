@@ -8,8 +8,8 @@
 //
 //   L = beta_i (k_i a_i).(k_j / a_j) for j < i,  M = (q_i a_i).(k_j / a_j) for j <= i,   a = exp(G - Gm)
 //                         as L^T, M^T = Kc x Kgb^T, Kc x Qgb^T (tcgen05, M = 128 of which 16 rows are real, N = 16)
-//   T = (I + L)^-1        16 x 16 forward substitution, FP32, one thread per column;  T' = T diag(beta)
-//   W = T' Kg,  U = T' V  FP32 on the CUDA cores (thread = channel: 136 multiply-adds each), Kg = k exp(G)
+//   W = (I + L)^-1 diag(beta) Kg,  U = (I + L)^-1 diag(beta) V   forward substitution down the 16 rows, FP32 on the CUDA
+//                         cores (thread = channel: 136 multiply-adds each; no explicit inverse), Kg = k exp(G)
 //   (W S)^T, (Qg S)^T     = S x W^T, S x Qg^T: tcgen05, M = 128 value channels, N = 16 rows, K = 128 key channels; the
 //                         bf16 state tile is the A operand exactly as it lies in HBM (rows of 128 key channels)
 //   D = U - W S,  O = Qg S + M D   FP32, thread = value channel (its tensor-memory lane)
@@ -42,12 +42,12 @@ constexpr int WIN = 16, kVThreads = 128;
 // Shared memory map (bytes).  Tiles are boxes of R rows x 128 bytes in the 128-byte swizzle (16-byte piece p of row r at
 // piece p ^ (r & 7)), two boxes per tile (channels 0-63, 64-127).  The column-side tile Kc comes first: as the M = 128
 // operand of L^T and M^T its descriptor walks 128 rows although 16 are real, and what follows it is the state tile.
-// Once those two products are done Kc is dead, and L, M and T' (FP32, 3.1 KB) take its place until the unit ends.
+// Once those two products are done Kc is dead, and L and M (FP32, 2.1 KB) take its place until the unit ends.
 constexpr int vKc = 0, vS = 4096, vKgb = vS + 32768, vQgb = vKgb + 4096, vQg = vQgb + 4096, vRaw = vQg + 4096;
 constexpr int vW = vKgb;                                                 // W replaces Kgb once L^T is done
 constexpr int vStage = vKgb;                                             // layer form: FP32 outputs [16][128] over W and Qgb
-constexpr int vL = vKc, vM = vL + WIN * 17 * 4, vTp = vM + WIN * WIN * 4;
-static_assert(vTp + WIN * WIN * 4 <= vS, "L, M, T' fit the dead column-side tile");
+constexpr int vL = vKc, vM = vL + WIN * 17 * 4;
+static_assert(vM + WIN * WIN * 4 <= vS, "L and M fit the dead column-side tile");
 // Raw rows of a unit.  Core form: q, k, v bf16 (256 bytes a row), log decay f32 (512), beta.  Layer form: q fp16, v bf16,
 // k f32, the decay multiplier f32, beta.
 template <bool LAYER>
@@ -199,7 +199,6 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
     uint32_t phase = 0;
     float* Lf = reinterpret_cast<float*>(smem + vL);
     float* Mf = reinterpret_cast<float*>(smem + vM);
-    float* Tp = reinterpret_cast<float*>(smem + vTp);
     float* betas = reinterpret_cast<float*>(smem + MP::vBeta);
     float nw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if constexpr (LAYER) {
@@ -226,7 +225,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
         __syncthreads();     // and every thread is done with the previous unit's L, M and staged outputs
 
         // ---- A. thread = channel c: the decay scan, the operand tiles, the replay saves ----------------------------------
-        float kg[WIN], vv[WIN];
+        float kg[WIN], vv[WIN], qe[WIN];
         {
             const int c = t;
             const unsigned char* raw = smem + vRaw;
@@ -258,7 +257,7 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
                 *reinterpret_cast<uint16_t*>(smem + vKgb + sw_elem(WIN, r, c)) = f32_to_bf16_bits(kf * a);
                 *reinterpret_cast<uint16_t*>(smem + vQgb + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * a);
                 *reinterpret_cast<uint16_t*>(smem + vKc + sw_elem(WIN, r, c)) = f32_to_bf16_bits(kf * __fdividef(1.0f, a));
-                *reinterpret_cast<uint16_t*>(smem + vQg + sw_elem(WIN, r, c)) = f32_to_bf16_bits(qf * e);
+                qe[r] = qf * e;  // the Qg tile is written while the first products run
                 if constexpr (!LAYER) {
                     if (r < n && p.k_save != nullptr) {
                         const long long at = ((un.row0 + r) * p.H + un.h) * DK + c;
@@ -295,6 +294,8 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
             tc::mma_commit(bar);
             atomicAdd(const_cast<uint32_t*>(ctl), 1u);
         }
+#pragma unroll
+        for (int r = 0; r < WIN; ++r) *reinterpret_cast<uint16_t*>(smem + vQg + sw_elem(WIN, r, t)) = f32_to_bf16_bits(qe[r]);
         bool ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
         phase ^= 1u;
         if (!__syncthreads_and(ok)) break;
@@ -312,43 +313,35 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
                     Mf[i * WIN + j] = i >= j ? __uint_as_float(m16[i]) : 0.0f;
                 }
             }
-            __syncwarp();
-            // T = (I + L)^-1, one thread per column (a column needs only its own earlier rows); T' = T diag(beta).
-            if (lane < WIN) {
-                const int j = lane;
-                float tcol[WIN];
-                const float bj = betas[j];
-#pragma unroll
-                for (int i = 0; i < WIN; ++i) {
-                    float a0 = i == j ? 1.0f : 0.0f, a1 = 0.0f;
-#pragma unroll
-                    for (int m = 0; m < i; ++m) {
-                        if (m & 1) a1 = fmaf(-Lf[i * 17 + m], tcol[m], a1);
-                        else a0 = fmaf(-Lf[i * 17 + m], tcol[m], a0);
-                    }
-                    tcol[i] = a0 + a1;
-                    Tp[i * WIN + j] = tcol[i] * bj;
-                }
-            }
         }
         tc::fence_before_sync();
         __syncthreads();
         tc::fence_after_sync();
 
-        // ---- C. W = T' Kg into its tile (thread = channel), U = T' V in registers (thread = value channel) ------------------------
+        // ---- C. W = (I + L)^-1 diag(beta) Kg into its tile (thread = channel), U = (I + L)^-1 diag(beta) V in registers
+        //         (thread = value channel), both by forward substitution down the 16 rows: the same multiply-adds as a product
+        //         with an explicit inverse, without the inverse
         float U[WIN];
         {
+            float W[WIN];
 #pragma unroll
             for (int i = 0; i < WIN; ++i) {
-                float w = 0.0f, uu = 0.0f;
+                const float bi = betas[i];
+                float w0 = bi * kg[i], w1 = 0.0f, u0 = bi * vv[i], u1 = 0.0f;
 #pragma unroll
-                for (int j = 0; j <= i; ++j) {
-                    const float tp = Tp[i * WIN + j];
-                    w = fmaf(tp, kg[j], w);
-                    uu = fmaf(tp, vv[j], uu);
+                for (int j = 0; j < i; ++j) {
+                    const float l = Lf[i * 17 + j];
+                    if (j & 1) {
+                        w1 = fmaf(-l, W[j], w1);
+                        u1 = fmaf(-l, U[j], u1);
+                    } else {
+                        w0 = fmaf(-l, W[j], w0);
+                        u0 = fmaf(-l, U[j], u0);
+                    }
                 }
-                U[i] = uu;
-                *reinterpret_cast<uint16_t*>(smem + vW + sw_elem(WIN, i, t)) = f32_to_bf16_bits(w);
+                W[i] = w0 + w1;
+                U[i] = u0 + u1;
+                *reinterpret_cast<uint16_t*>(smem + vW + sw_elem(WIN, i, t)) = f32_to_bf16_bits(W[i]);
             }
         }
         cp_async_wait<1>();  // this unit's state has landed (the next unit's rows may still be on the way)

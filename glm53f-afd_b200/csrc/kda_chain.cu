@@ -46,6 +46,12 @@ static std::atomic<int> g_layer_verify_mode{[] {
     const char* e = getenv("GLM53F_KDA_VERIFY");
     return e != nullptr && strcmp(e, "chunked") == 0 ? 1 : 0;
 }()};
+// How the bf16-state replays run: 0 = the exact row-by-row form, 1 = chunks of 16 rows on the tensor cores;
+// GLM53F_KDA_COMMIT=chunked makes 1 the default.
+static std::atomic<int> g_commit_mode{[] {
+    const char* e = getenv("GLM53F_KDA_COMMIT");
+    return e != nullptr && strcmp(e, "chunked") == 0 ? 1 : 0;
+}()};
 static int g_skip_first_state = 0;
 
 int sm_count() {
@@ -1222,6 +1228,9 @@ int replay_entry(int32_t heads, int32_t layers, int32_t batch, bool batched, con
     q.k_save = const_cast<float*>(k_save); q.v_save = const_cast<glm53f_bf16*>(v_save);
     q.g_save = const_cast<float*>(g_save); q.b_save = const_cast<float*>(b_save);
     q.kv_stride = kv_stride; q.b_stride = b_stride;
+    if (bf16_state && g_commit_mode.load() == 1)
+        return commit_tc_launch(heads, layers, batch, cu_rows, keep, rows, state_in, state_out, state_stride, state_off, k_save, v_save, g_save,
+                                b_save, kv_stride, b_stride, (cudaStream_t)stream);
     // The warp-per-eight-rows kernel takes aligned saves and grids that fit; GLM53F_KDA_REPLAY=pipeline keeps the
     // persistent kernel.
     static const bool small = [] {
@@ -1455,6 +1464,12 @@ extern "C" int glm53f_kda_device_status(void) {
 extern "C" int32_t glm53f_kda_verify_mode(int32_t mode) {
     const int prev = kda::g_layer_verify_mode.load();
     if (mode == 0 || mode == 1) kda::g_layer_verify_mode.store(mode);
+    return prev;
+}
+
+extern "C" int32_t glm53f_kda_commit_mode(int32_t mode) {
+    const int prev = kda::g_commit_mode.load();
+    if (mode == 0 || mode == 1) kda::g_commit_mode.store(mode);
     return prev;
 }
 

@@ -62,6 +62,12 @@ int layer_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows,
                            const glm53f_bf16* gate, int64_t gate_stride, const glm53f_bf16* norm_w, float eps, glm53f_bf16* out,
                            int64_t out_stride, float* k_save, glm53f_bf16* v_save, float* g_save, float* b_save, cudaStream_t stream);
 
+// The commit as chunks of 16 rows on the tensor cores (kda_verify_tc.cu): bf16 states; the committed state agrees with
+// the exact replay to the last bits of bf16, not bit for bit.
+int commit_tc_launch(int32_t heads, int32_t layers, int32_t batch, const int32_t* cu_rows, const int32_t* keep, int32_t rows1, const void* state_in,
+                     void* state_out, int64_t state_stride, const int64_t* state_off, const float* k_save, const glm53f_bf16* v_save,
+                     const float* g_save, const float* b_save, int64_t kv_stride, int64_t b_stride, cudaStream_t stream);
+
 // The layer prologue of a prefill pass (kda_prologue.cu): for rows row_shift .. row_shift + pass_rows - 1 of every request,
 // the short convolution + SiLU, the L2 norms, the log decay and beta, with the chain's arithmetic, written as core inputs
 // (q, k as fp16 bits, v bf16, g f32 log decay [batch * pass_rows][H][128]; beta f32 [batch * pass_rows][H]).  p, a, conv must be

@@ -423,6 +423,293 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
     if (warp == 0) tc::tmem_dealloc(tm, kVCols);
 }
 
+// ---- the commit as chunks of 16 rows ---------------------------------------------------------------------------------
+// The state after the first keep[b] saved rows, for every (request, layer, head): S <- E S + Kdec^T D per chunk of up to
+// 16 rows, with D = U - W S as above, E = exp(G_last) and Kdec_i = k_i exp(G_last - G_i).  The inputs are the replay
+// saves (k and the decay multiplier f32, v bf16, beta).  The bf16 state tile is the A operand of S W^T where it lies;
+// the update D^T x Kdec (M = 128 value rows, N = 128 key channels, K = 16 rows) runs as three products of bf16 hi/lo
+// halves (the path into the state keeps 16 bits of operand mantissa, as in the prefill), its FP32 accumulator is read
+// back lane = value row, E S is added in FP32 and the rounded row goes back into the tile, which is then the next
+// chunk's state or is copied out.  Unlike the exact replay this rounds the state to bf16 once per chunk instead of
+// after every row, and its sums run in another order: the committed state agrees with serial decode steps to the last
+// bits of bf16, not bit for bit (glm53f_kda_commit_mode).
+constexpr int cS = 0, cKc = 32768, cKgb = cKc + 4096, cDT = cKgb + 4096, cKdT = cDT + 8192, cE = cKdT + 8192, cBeta = cE + 512;
+constexpr int cBar = cBeta + 64, cCtl = cBar + 16, kCSmem = cCtl + 16;
+constexpr int cW = cKgb, cL = cKc;                    // W replaces Kgb, L replaces Kc once L^T is done
+constexpr uint32_t kCCols = 128;                      // tensor memory: L^T, then (W S)^T, then the 128 x 128 update
+static_assert(kCSmem <= 75 * 1024, "three blocks per SM");
+
+struct CParams {
+    int H, layers, rows1;
+    long long units;
+    const int32_t* cu;
+    const int32_t* keep;
+    const uint16_t* state_in;
+    uint16_t* state_out;
+    long long state_stride;
+    const long long* state_off;
+    const float* k_save;
+    const uint16_t* v_save;
+    const float* g_save;
+    const float* b_save;
+    long long kv_stride, b_stride;
+    int* status;
+};
+
+__device__ __forceinline__ int state_piece(int v, int pk) { return cS + (pk >> 3) * 16384 + v * 128 + (((pk & 7) ^ (v & 7)) << 4); }
+
+__global__ void __launch_bounds__(kVThreads, 3) commit_tc_kernel(const __grid_constant__ CParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + cBar);
+    volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + cCtl);
+    uint32_t* tmem_slot = const_cast<uint32_t*>(ctl) + 2;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    if (t == 0) {
+        mbar_init(bar, 1);
+        ctl[0] = 0u;
+        ctl[1] = 0u;
+        mbar_init_fence();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, kCCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tm = *tmem_slot;
+    const WaitCtx ctx{ctl, ctl + 1, p.status};
+    uint32_t phase = 0;
+    float* Lf = reinterpret_cast<float*>(smem + cL);
+    float* En = reinterpret_cast<float*>(smem + cE);
+    float* betas = reinterpret_cast<float*>(smem + cBeta);
+    bool ok = true;
+
+    for (long long u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        const int h = (int)(u % p.H), layer = (int)((u / p.H) % p.layers), b = (int)(u / ((long long)p.H * p.layers));
+        const long long row0 = p.cu ? p.cu[b] : 0;
+        int n = p.keep ? p.keep[b] : p.rows1;
+        if (n < 0) n = 0;
+        const long long s_elem = (long long)layer * p.state_stride + (p.state_off ? p.state_off[b] : 0) + (long long)h * DV * DK;
+        const uint16_t* src = p.state_in + s_elem;
+        uint16_t* dst = p.state_out + s_elem;
+        if (n == 0 && dst == src) continue;
+        const long long kv_base = (long long)layer * p.kv_stride, b_base = (long long)layer * p.b_stride;
+        __syncthreads();  // the previous unit's tile has been copied out
+        // The unit's state into the swizzled tile.
+        const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int e = t + i * kVThreads;
+                cp_async16(smem + state_piece(e >> 4, e & 15), src + (long long)e * 8);
+            }
+        } else {
+            for (int e = t; e < DV * DK; e += kVThreads) *reinterpret_cast<uint16_t*>(smem + cS + sw_elem(DV, e >> 7, e & 127)) = src[e];
+        }
+        cp_async_commit();
+
+        for (int c0 = 0; c0 < n && ok; c0 += WIN) {
+            const int nr = min(WIN, n - c0);
+            // ---- A. thread = channel: the decay scan and the operand tiles; thread = value channel: v ----------------------
+            float kg[WIN], vv[WIN];
+            {
+                float kf[WIN], G[WIN], acc = 0.0f;
+#pragma unroll
+                for (int r = 0; r < WIN; ++r) {
+                    const long long at = kv_base + ((row0 + c0 + r) * p.H + h) * DK + t;
+                    const bool live = r < nr;
+                    kf[r] = live ? p.k_save[at] : 0.0f;
+                    vv[r] = live ? bf16_bits_to_f32(p.v_save[at]) : 0.0f;
+                    acc += live ? __logf(p.g_save[at]) : 0.0f;
+                    G[r] = acc;
+                }
+                const float gm = G[WIN / 2], gl = G[WIN - 1];
+                float amax = 0.0f;
+                uint32_t dh[WIN / 2], dl[WIN / 2];
+#pragma unroll
+                for (int r = 0; r < WIN; r += 2) {
+                    float hi[2], lo[2];
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const float a = __expf(G[r + x] - gm);
+                        amax = fmaxf(amax, a);
+                        kg[r + x] = kf[r + x] * __expf(G[r + x]);
+                        *reinterpret_cast<uint16_t*>(smem + cKgb + sw_elem(WIN, r + x, t)) = f32_to_bf16_bits(kf[r + x] * a);
+                        *reinterpret_cast<uint16_t*>(smem + cKc + sw_elem(WIN, r + x, t)) = f32_to_bf16_bits(kf[r + x] * __fdividef(1.0f, a));
+                        tc::split_bf16(kf[r + x] * __expf(gl - G[r + x]), hi[x], lo[x]);
+                    }
+                    dh[r / 2] = tc::bf16x2(hi[0], hi[1]);
+                    dl[r / 2] = tc::bf16x2(lo[0], lo[1]);
+                }
+                // Kdec^T: row = key channel t, 16 row indices along K = two 16-byte cells
+                *reinterpret_cast<uint4*>(smem + cKdT + (0 * DK + t) * 16) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(smem + cKdT + (1 * DK + t) * 16) = make_uint4(dh[4], dh[5], dh[6], dh[7]);
+                *reinterpret_cast<uint4*>(smem + cKdT + 4096 + (0 * DK + t) * 16) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+                *reinterpret_cast<uint4*>(smem + cKdT + 4096 + (1 * DK + t) * 16) = make_uint4(dl[4], dl[5], dl[6], dl[7]);
+                En[t] = __expf(gl);
+                if (!(amax < 1e37f)) atomicCAS(p.status, 0, kStatusPrefillRange);
+                if (t < WIN) betas[t] = t < nr ? p.b_save[b_base + (row0 + c0 + t) * p.H + h] : 0.0f;
+            }
+            fence_proxy_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            tc::fence_after_sync();
+
+            // ---- B. L^T ---------------------------------------------------------------------------------------------------
+            if (t == 0) {
+                constexpr uint32_t id = tc::idesc_bf16(128, WIN, 0, 0, 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm, tc::desc_sw128_kmajor(smem + cKc, WIN, k0), tc::desc_sw128_kmajor(smem + cKgb, WIN, k0), id, k0 > 0);
+                tc::mma_commit(bar);
+                atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+            }
+            ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
+            phase ^= 1u;
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+            if (warp == 0) {
+                uint32_t l16[16];
+                tc::tmem_ld16(tc::tmem_addr(tm, 0, 0), l16);
+                tc::tmem_ld_wait();
+                if (lane < WIN) {
+#pragma unroll
+                    for (int i = 0; i < WIN; ++i) Lf[i * 17 + lane] = i > lane ? betas[i] * __uint_as_float(l16[i]) : 0.0f;
+                }
+            }
+            tc::fence_before_sync();
+            __syncthreads();
+            tc::fence_after_sync();
+
+            // ---- C. W and U by forward substitution ---------------------------------------------------------------------------
+            float U[WIN];
+            {
+                float W[WIN];
+#pragma unroll
+                for (int i = 0; i < WIN; ++i) {
+                    const float bi = betas[i];
+                    float w0 = bi * kg[i], w1 = 0.0f, u0 = bi * vv[i], u1 = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < i; ++j) {
+                        const float l = Lf[i * 17 + j];
+                        if (j & 1) {
+                            w1 = fmaf(-l, W[j], w1);
+                            u1 = fmaf(-l, U[j], u1);
+                        } else {
+                            w0 = fmaf(-l, W[j], w0);
+                            u0 = fmaf(-l, U[j], u0);
+                        }
+                    }
+                    W[i] = w0 + w1;
+                    U[i] = u0 + u1;
+                    *reinterpret_cast<uint16_t*>(smem + cW + sw_elem(WIN, i, t)) = f32_to_bf16_bits(W[i]);  // over Kgb, which is consumed
+                }
+            }
+            cp_async_wait<0>();  // the state has landed (first chunk)
+            fence_proxy_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            tc::fence_after_sync();
+
+            // ---- D. (W S)^T = S W^T --------------------------------------------------------------------------------------------
+            if (t == 0) {
+                constexpr uint32_t id = tc::idesc_bf16(128, WIN, 0, 0, 0);
+                for (int k0 = 0; k0 < DK; k0 += 16)
+                    tc::mma_bf16(tm, tc::desc_sw128_kmajor(smem + cS, DV, k0), tc::desc_sw128_kmajor(smem + cW, WIN, k0), id, k0 > 0);
+                tc::mma_commit(bar);
+                atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+            }
+            ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
+            phase ^= 1u;
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+
+            // ---- E. D = U - W S as the A operand D^T (row = value channel t, hi and lo halves) ------------------------------
+            {
+                uint32_t ws[16];
+                tc::tmem_ld16(tc::tmem_addr(tm, warp, 0), ws);
+                tc::tmem_ld_wait();
+                uint32_t dh[WIN / 2], dl[WIN / 2];
+#pragma unroll
+                for (int i = 0; i < WIN; i += 2) {
+                    float hi[2], lo[2];
+                    tc::split_bf16(U[i] - __uint_as_float(ws[i]), hi[0], lo[0]);
+                    tc::split_bf16(U[i + 1] - __uint_as_float(ws[i + 1]), hi[1], lo[1]);
+                    dh[i / 2] = tc::bf16x2(hi[0], hi[1]);
+                    dl[i / 2] = tc::bf16x2(lo[0], lo[1]);
+                }
+                *reinterpret_cast<uint4*>(smem + cDT + (0 * DV + t) * 16) = make_uint4(dh[0], dh[1], dh[2], dh[3]);
+                *reinterpret_cast<uint4*>(smem + cDT + (1 * DV + t) * 16) = make_uint4(dh[4], dh[5], dh[6], dh[7]);
+                *reinterpret_cast<uint4*>(smem + cDT + 4096 + (0 * DV + t) * 16) = make_uint4(dl[0], dl[1], dl[2], dl[3]);
+                *reinterpret_cast<uint4*>(smem + cDT + 4096 + (1 * DV + t) * 16) = make_uint4(dl[4], dl[5], dl[6], dl[7]);
+            }
+            fence_proxy_async_smem();
+            tc::fence_before_sync();
+            __syncthreads();
+            tc::fence_after_sync();
+
+            // ---- F. the update D^T x Kdec: [value row][key channel], three products of halves ------------------------------------
+            if (t == 0) {
+                constexpr uint32_t id = tc::idesc_bf16(128, 128, 0, 0, 0);
+                tc::mma_bf16(tm, tc::desc_kmajor_bf16(smem + cDT, DV, 0, 0), tc::desc_kmajor_bf16(smem + cKdT, DK, 0, 0), id, false);
+                tc::mma_bf16(tm, tc::desc_kmajor_bf16(smem + cDT, DV, 0, 0), tc::desc_kmajor_bf16(smem + cKdT + 4096, DK, 0, 0), id, true);
+                tc::mma_bf16(tm, tc::desc_kmajor_bf16(smem + cDT + 4096, DV, 0, 0), tc::desc_kmajor_bf16(smem + cKdT, DK, 0, 0), id, true);
+                tc::mma_commit(bar);
+                atomicAdd(const_cast<uint32_t*>(ctl), 1u);
+            }
+            ok = mbar_wait(bar, phase, ctx, kStatusWaitPrefill);
+            phase ^= 1u;
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+
+            // ---- G. S <- E S + update, rounded to bf16, back into the tile (thread = value row) ------------------------------
+#pragma unroll 1
+            for (int cg = 0; cg < DK / 16; ++cg) {
+                uint32_t a16[16];
+                tc::tmem_ld16(tc::tmem_addr(tm, warp, cg * 16), a16);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    unsigned char* at = smem + state_piece(t, cg * 2 + half);
+                    const uint4 sv = *reinterpret_cast<const uint4*>(at);
+                    const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+                    uint32_t out[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const int k = cg * 16 + half * 8 + 2 * x;
+                        const float2 e2 = *reinterpret_cast<const float2*>(&En[k]);
+                        const float lo = fmaf(e2.x, __uint_as_float(sw[x] << 16), __uint_as_float(a16[half * 8 + 2 * x]));
+                        const float hi = fmaf(e2.y, __uint_as_float(sw[x] & 0xffff0000u), __uint_as_float(a16[half * 8 + 2 * x + 1]));
+                        out[x] = tc::bf16x2(lo, hi);
+                    }
+                    *reinterpret_cast<uint4*>(at) = make_uint4(out[0], out[1], out[2], out[3]);
+                }
+            }
+            fence_proxy_async_smem();  // the next chunk's S W^T reads the tile through the async proxy
+            tc::fence_before_sync();
+            __syncthreads();
+            tc::fence_after_sync();
+        }
+        if (!ok) break;
+        cp_async_wait<0>();  // a unit without rows: its state is only copied
+        __syncthreads();
+        // ---- the tile back to global memory, coalesced ------------------------------------------------------------------------
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int e = t + i * kVThreads;
+                *reinterpret_cast<uint4*>(dst + (long long)e * 8) = *reinterpret_cast<const uint4*>(smem + state_piece(e >> 4, e & 15));
+            }
+        } else {
+            for (int e = t; e < DV * DK; e += kVThreads) dst[e] = *reinterpret_cast<const uint16_t*>(smem + cS + sw_elem(DV, e >> 7, e & 127));
+        }
+    }
+    cp_async_wait<0>();
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tm, kCCols);
+}
+
 template <bool LAYER>
 int launch_verify(const VParams& p, cudaStream_t stream) {
     static int configured_dev = -1;
@@ -477,6 +764,35 @@ int layer_verify_tc_launch(int32_t heads, int32_t batch, const int32_t* cu_rows,
     p.gate = gate; p.gate_stride = gate_stride; p.norm_w = norm_w; p.eps = eps;
     p.status = status_word();
     return launch_verify<true>(p, stream);
+}
+
+// The chunked commit (bf16 states; the caller checks that the saves are 4-byte aligned, which every float array is).
+int commit_tc_launch(int32_t heads, int32_t layers, int32_t batch, const int32_t* cu_rows, const int32_t* keep, int32_t rows1, const void* state_in,
+                     void* state_out, int64_t state_stride, const int64_t* state_off, const float* k_save, const glm53f_bf16* v_save,
+                     const float* g_save, const float* b_save, int64_t kv_stride, int64_t b_stride, cudaStream_t stream) {
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(commit_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured_dev = dev;
+    }
+    CParams p{};
+    p.H = heads; p.layers = layers; p.rows1 = rows1;
+    p.units = (long long)heads * layers * batch;
+    p.cu = cu_rows; p.keep = keep;
+    p.state_in = reinterpret_cast<const uint16_t*>(state_in);
+    p.state_out = reinterpret_cast<uint16_t*>(state_out);
+    p.state_stride = state_stride;
+    p.state_off = reinterpret_cast<const long long*>(state_off);
+    p.k_save = k_save; p.v_save = v_save; p.g_save = g_save; p.b_save = b_save;
+    p.kv_stride = kv_stride; p.b_stride = b_stride;
+    p.status = status_word();
+    if (p.status == nullptr) return (int)cudaErrorUnknown;
+    const long long cap = 3LL * sm_count();
+    commit_tc_kernel<<<(unsigned)(p.units < cap ? p.units : cap), kVThreads, kCSmem, stream>>>(p);
+    return (int)cudaGetLastError();
 }
 
 }  // namespace kda

@@ -44,6 +44,7 @@ SIGNATURES = {
     "glm53f_kda_debug_wait_test": (C.c_int, [C.c_uint64, I32]),
     "glm53f_kda_prefill_mode": (I32, [I32]),
     "glm53f_kda_verify_mode": (I32, [I32]),
+    "glm53f_kda_commit_mode": (I32, [I32]),
     "glm53f_kda_gather_head_range": (C.c_int, [I32, I32, I32, P, P]),
     "glm53f_kda_gather_export": (C.c_int, [P, I64, P]),
     "glm53f_kda_gather_open": (C.c_int, [P, P, P]),
@@ -58,7 +59,7 @@ SIGNATURES = {
 }
 
 # The reference's thirteen (crates/glm53f-kda/tests/provenance.rs:41-69 asserts exactly these).
-REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and "_gather_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_debug_wait_test", "glm53f_kda_prefill_mode", "glm53f_kda_verify_mode", "glm53f_kda_mark_copy", "glm53f_kda_mark_copy_slots", "glm53f_kda_proj_bf16", "glm53f_kda_chain_commit_batch")]
+REFERENCE_SYMBOLS = [n for n in SIGNATURES if n.startswith("glm53f_kda_") and "_core_" not in n and "_gather_" not in n and n not in ("glm53f_kda_device_status", "glm53f_kda_debug_wait_test", "glm53f_kda_prefill_mode", "glm53f_kda_verify_mode", "glm53f_kda_commit_mode", "glm53f_kda_mark_copy", "glm53f_kda_mark_copy_slots", "glm53f_kda_proj_bf16", "glm53f_kda_chain_commit_batch")]
 
 
 def library_path() -> str:

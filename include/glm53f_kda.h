@@ -413,6 +413,18 @@ int32_t glm53f_kda_prefill_mode(int32_t mode);
  * makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */
 int32_t glm53f_kda_verify_mode(int32_t mode);
 
+/* Which form the replays of bf16 states run (glm53f_kda_replay_batch_bf16state, glm53f_kda_core_commit_batch with
+ * state_bf16 != 0); not in the reference's header.  Replays of f32 states are unaffected.
+ *   0  exact (the default): row by row, the state rounded to bf16 after every row: the bits of serial decode steps
+ *      (crates/glm53f-kda/kernels/glm53f_kda.h:111-116)
+ *   1  chunked: each request's kept rows in chunks of 16 on the tensor cores, the state read once and written once,
+ *      rounded to bf16 once per chunk.  The committed state then agrees with serial decode steps to the last bits of
+ *      bf16 (rel-L2 about 1e-3, the size of one bf16 rounding; the task's bound on a bf16 state is 2e-2), not bit for
+ *      bit: a host that relies on verify + commit(k) == k decode steps EXACTLY keeps mode 0.
+ * Any other value only queries.  Returns the mode that was in force.  GLM53F_KDA_COMMIT=chunked makes 1 the initial
+ * mode.  Process-wide; set it before the launches it should affect. */
+int32_t glm53f_kda_commit_mode(int32_t mode);
+
 /* Diagnostic hook, for tests of the failure path; no counterpart in the reference.  The persistent recurrent kernel
  * (the layer entry points, the replays, and core calls with fused norms or an output gate) bounds every device-side wait: a block whose waits see no progress for the limit (2 s by default) records a
  * status code (101-108, which wait), makes its other waits return, and the kernel ends; the context stays usable and

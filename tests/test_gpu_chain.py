@@ -85,6 +85,34 @@ def test_chain_equals_the_reference_kernels_bitwise(G, oracle, heads, r, bf16):
     G.check_status()
 
 
+@pytest.mark.parametrize("bf16", [False, True])
+def test_both_replay_kernels_leave_the_same_bits(G, oracle, bf16):
+    """Saves that are 16-byte aligned replay on independent warps, others on the persistent kernel: one result."""
+    o, lib, h, r = oracle, G.product(), 3, 7
+    p, conv, s0, rows = case(o, h, r, 333)
+    if bf16:
+        s0 = o.bf16_round_np(s0)
+    sv = G.run_chain(lib, p, conv, s0, rows, bf16_state=bf16)
+    n = r * h * DK
+    k_pad, g_pad = torch.zeros(n + 4, device="cuda"), torch.zeros(n + 4, device="cuda")
+    k_pad[1:n + 1] = torch.from_numpy(sv.k).cuda()   # one float in: the rows start 4 bytes off a 16-byte boundary
+    g_pad[1:n + 1] = torch.from_numpy(sv.g).cuda()
+    d_v, d_b = G.dev_bf16(sv.v), G.dev_f32(sv.beta)
+    cu, zoff = G.dev_i32([0, r]), G.dev_i64([0])
+    for keep in (0, 1, 4, r):
+        want = G.run_replay(lib, h, s0, sv, keep, bf16_state=bf16)
+        d_sin = G.dev_bf16(s0) if bf16 else G.dev_f32(s0)
+        d_sout = torch.zeros_like(d_sin)
+        kp = G.dev_i32([keep])
+        fn = lib.glm53f_kda_replay_batch_bf16state if bf16 else lib.glm53f_kda_replay_batch
+        rc = fn(h, 1, 1, G.ptr(cu), G.ptr(kp), G.ptr(d_sin), G.ptr(d_sout), 0, G.ptr(zoff), C.c_void_p(k_pad.data_ptr() + 4), G.ptr(d_v),
+                C.c_void_p(g_pad.data_ptr() + 4), G.ptr(d_b), 0, 0, None)
+        assert rc == 0
+        got = G.host_bf16(d_sout) if bf16 else G.host_f32(d_sout)
+        assert np.array_equal(G.bits(got), G.bits(want)), keep
+    G.check_status()
+
+
 # gpu.rs:398-474, gpu_bf16_state.rs:331-382
 @pytest.mark.parametrize("bf16", [False, True])
 def test_prefixes_and_serial_steps_are_bitwise(G, oracle, bf16):

@@ -86,6 +86,13 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) { asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory"); }
+// Programmatic dependent launch: the next kernel of the stream may be scheduled once every block has said so, and a
+// block touches nothing an earlier kernel may still write (or read, where this kernel writes) before grid_dependency_wait.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -142,12 +149,21 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NR, (KS > 1)>::kBlocksPerSm)
         mbar_init_fence();
     }
     if (warp == 1) tc::tmem_alloc(tmem_slot, C::kTmemCols);
+    if (tid == 0) {
+        prefetch_tensormap(&p.tm_w);
+        prefetch_tensormap(&p.tm_x);
+    }
     tc::fence_before_sync();
     __syncthreads();
-    if (SPLIT) cluster_sync_all();  // every block's barriers exist before a peer arrives on one
+    // Every block's barriers exist before a peer arrives on one: the blocks say so here and check it only before their
+    // first remote arrival (the end of their first tile), so nobody stands still at the start.
+    if (SPLIT) cluster_arrive();
     tc::fence_after_sync();
     const uint32_t tm = *tmem_slot;
     const WaitCtx ctx{ctl, ctl + 1, p.status};
+    launch_dependents();
+    bool opened = !SPLIT;  // whether this thread has completed the opening cluster barrier
+    grid_dependency_wait();  // before the first global access: an earlier kernel may be writing the weight or the rows
 
     if (warp == 0) {
         if (lane == 0) {
@@ -240,6 +256,10 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NR, (KS > 1)>::kBlocksPerSm)
                 // through distributed shared memory, and stores.  32 columns at a time.
                 constexpr int CW = NR < 32 ? NR : 32;
                 float* red = reinterpret_cast<float*>(smem + C::oRed) + fl * NR;
+                if (!opened) {  // the opening cluster barrier: every peer's barriers and buffers exist
+                    cluster_wait();
+                    opened = true;
+                }
                 if (kr != 0) {
                     if (!mbar_wait(red_empty, red_ph ^ 1u, ctx, kStatusGemmRedEmpty)) goto done;  // rank 0 is done with the last one
                     fence_cluster();
@@ -303,7 +323,10 @@ done:
     __syncthreads();
     if (warp == 1) tc::tmem_dealloc(tm, C::kTmemCols);
     // No block leaves while a peer may still read its partial tile or arrive on its barriers.
-    if (SPLIT) cluster_sync_all();
+    if (SPLIT) {
+        if (!opened) cluster_wait();  // the threads that never needed the opening barrier complete it here
+        cluster_sync_all();
+    }
 }
 
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -363,13 +386,28 @@ int launch_one(GemmParams& p, long long clusters, cudaStream_t stream) {
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = C::kBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)KS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    // Programmatic stream serialization: the kernel waits for its predecessors itself (grid_dependency_wait) before its
+    // first global access, so its blocks' set-up (barriers, tensor memory, descriptor fetch) overlaps their tail.
+    static const bool pdl = [] {
+        const char* v = getenv("GLM53F_KDA_PDL");
+        return !(v && v[0] == '0');
+    }();
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (KS > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)KS;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = KS > 1 ? 1 : 0;
+    cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, proj_gemm_kernel<NR, KS>, p);
 }
 

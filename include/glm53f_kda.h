@@ -418,9 +418,10 @@ int32_t glm53f_kda_verify_mode(int32_t mode);
  *   0  exact (the default): row by row, the state rounded to bf16 after every row: the bits of serial decode steps
  *      (crates/glm53f-kda/kernels/glm53f_kda.h:111-116)
  *   1  chunked: each request's kept rows in chunks of 16 on the tensor cores, the state read once and written once,
- *      rounded to bf16 once per chunk.  The committed state then agrees with serial decode steps to the last bits of
- *      bf16 (rel-L2 about 1e-3, the size of one bf16 rounding; the task's bound on a bf16 state is 2e-2), not bit for
- *      bit: a host that relies on verify + commit(k) == k decode steps EXACTLY keeps mode 0.
+ *      rounded to bf16 once per chunk.  The committed state then agrees with serial decode steps to bf16's own rounding
+ *      (rel-L2 of a few 1e-3 between the two; the task's bound on a bf16 state is 2e-2), not bit for bit -- against the
+ *      FP32 recurrence it is the closer of the two, since mode 0 rounds after every row -- so a host that relies on
+ *      verify + commit(k) == k decode steps EXACTLY keeps mode 0.
  * Any other value only queries.  Returns the mode that was in force.  GLM53F_KDA_COMMIT=chunked makes 1 the initial
  * mode.  Process-wide; set it before the launches it should affect. */
 int32_t glm53f_kda_commit_mode(int32_t mode);

@@ -196,6 +196,77 @@ def test_config4_verify_and_rollback_at_full_size(env):
     assert torch.equal(arena.view(torch.int16), serial.view(torch.int16))
 
 
+def test_config4_chunked_forms_at_full_size(env):
+    """Configuration 4 through the tensor-core forms: the verify window as one chunk (GLM53F_KDA_CORE_TENSOR) and the
+    commit in chunks (glm53f_kda_commit_mode), held to the exact forms -- which the test above holds to serial decode
+    bit for bit -- within the task's tolerances: outputs max-abs 2e-2 and rel-L2 5e-3; the replay saves must be the exact
+    form's bits; the committed bf16 states within 2e-3 rel-L2 of the FP32 replay of the same saves and never further from
+    it than the exact bf16 replay is."""
+    pkg, core = env
+    lib = pkg.ffi.load()
+    slots, window, layers = 48, 16, 34
+    per, rows = H * DV * DK, slots * window
+    rng = np.random.default_rng(0x53454548)
+    keeps = [int(x) for x in rng.integers(0, window + 1, slots)]
+    keeps[0], keeps[1] = 0, window
+    gs = torch.Generator(device="cuda").manual_seed(11)
+    arena = (torch.randn(layers * slots * per, device="cuda", generator=gs) * 0.05).to(torch.bfloat16)
+    exact_arena = arena.clone()
+    before = arena[:4 * slots * per].clone()
+    cu = torch.arange(slots + 1, dtype=torch.int32, device="cuda") * window
+    keep_d = torch.tensor(keeps, dtype=torch.int32, device="cuda")
+    off = torch.arange(slots, dtype=torch.int64, device="cuda") * per
+    nkv, nb = rows * H * DK, rows * H
+    mk = lambda: (torch.zeros(layers * nkv, device="cuda"), torch.zeros(layers * nkv, dtype=torch.bfloat16, device="cuda"),
+                  torch.zeros(layers * nkv, device="cuda"), torch.zeros(layers * nb, device="cuda"))
+    sv_t, sv_e = mk(), mk()
+    out_t = torch.zeros(rows * H * DV, dtype=torch.bfloat16, device="cuda")
+    out_e = torch.zeros_like(out_t)
+    worst_abs, worst_rel = 0.0, 0.0
+    for l in range(layers):
+        q, k, v, g, beta = tokens(rows, H, 1000 + l)
+        st = arena[l * slots * per:(l + 1) * slots * per]
+        at = lambda sv: (sv[0][l * nkv:], sv[1][l * nkv:], sv[2][l * nkv:], sv[3][l * nb:])
+        core.decode_batch(H, rows, cu, q, k, v, g, beta, st, off, state_out=None, out=out_e, saves=at(sv_e))
+        core.decode_batch(H, rows, cu, q, k, v, g, beta, st, off, state_out=None, out=out_t, saves=at(sv_t), flags=core.TENSOR)
+        a, b = out_t.float(), out_e.float()
+        worst_abs = max(worst_abs, float((a - b).abs().max()))
+        worst_rel = max(worst_rel, float(((a - b).norm() / b.norm())))
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    assert worst_abs <= 2e-2 and worst_rel <= 5e-3, (worst_abs, worst_rel)
+    for x, y in zip(sv_t, sv_e):
+        assert torch.equal(x.view(torch.int16) if x.dtype == torch.bfloat16 else x.view(torch.int32),
+                           y.view(torch.int16) if y.dtype == torch.bfloat16 else y.view(torch.int32))
+    core.commit_batch(H, layers, cu, keep_d, exact_arena, slots * per, off, (sv_e[0], sv_e[1], sv_e[2], sv_e[3]), nkv, nb)
+    prev = lib.glm53f_kda_commit_mode(1)
+    try:
+        core.commit_batch(H, layers, cu, keep_d, arena, slots * per, off, (sv_t[0], sv_t[1], sv_t[2], sv_t[3]), nkv, nb)
+    finally:
+        lib.glm53f_kda_commit_mode(prev)
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    # The exact replay rounds a bf16 state after every row, the chunked one once per chunk: the yardstick for both is the
+    # replay of the same saves on FP32 copies of the states (no rounding at all), here for the first four layers.
+    tl = 4
+    truth = before[:tl * slots * per].float()
+    core.commit_batch(H, tl, cu, keep_d, truth, slots * per, off, (sv_e[0], sv_e[1], sv_e[2], sv_e[3]), nkv, nb)
+    torch.cuda.synchronize()
+    assert core.device_status() == 0
+    for l in range(layers):
+        a = arena[l * slots * per:(l + 1) * slots * per].float().view(slots, per)
+        b = exact_arena[l * slots * per:(l + 1) * slots * per].float().view(slots, per)
+        rel = ((a - b).norm(dim=1) / b.norm(dim=1))
+        assert float(rel.max()) <= 1e-2, (l, float(rel.max()))   # both carry bf16 roundings: 16 of them in the exact form
+        assert torch.equal(a[0], b[0])   # slot 0 keeps nothing: untouched either way
+        if l < tl:
+            t = truth[l * slots * per:(l + 1) * slots * per].view(slots, per)
+            err_c = (a - t).norm(dim=1) / t.norm(dim=1)
+            err_e = (b - t).norm(dim=1) / t.norm(dim=1)
+            assert float(err_c.max()) <= 2e-3, (l, float(err_c.max()))            # one bf16 rounding is 1.1e-3
+            assert bool((err_c <= err_e + 2e-4).all()), (l, err_c, err_e)          # never further from the truth than the exact form
+
+
 def test_config1_decode_in_place_equals_out_of_place(env):
     pkg, core = env
     slots, layers, per = 16, 34, H * DV * DK

@@ -302,6 +302,15 @@ def run_layer_abi(torch, lib, rank, layers, steps, prefill_lib_ok=True):
                             "ms_per_lane": ms / pl / batch, "rows_per_s": batch * lane_rows * pl / (ms * 1e-3), "workspace_bytes": wsb,
                             "rows_per_pass": 256, "value_blocks": 2}
                         del _g
+                        if mode == 1 and batch == lanes and not bf16:
+                            # the same call with a workspace for a whole lane per pass (the reference's default is 256 rows)
+                            wsb2 = int(lib.glm53f_kda_prefill_workspace_bytes(HEADS, batch, lane_rows))
+                            ws2 = torch.empty(wsb2, dtype=torch.uint8, device="cuda")
+                            ms2, _g = graph_ms(torch, lambda st: [f.prefill(lib, l, st, ws2, wsb2, lane_rows, 2) for l in range(pl)], max(2, steps // 5), warm=2)
+                            res["prefill_layer"][f"{mode_name}_f32state_batch{batch}_whole_lane_passes"] = {
+                                "ms_per_lane": ms2 / pl / batch, "rows_per_s": batch * lane_rows * pl / (ms2 * 1e-3), "workspace_bytes": wsb2,
+                                "rows_per_pass": lane_rows, "value_blocks": 2}
+                            del _g, ws2
                     finally:
                         del f, ws
                         torch.cuda.empty_cache()

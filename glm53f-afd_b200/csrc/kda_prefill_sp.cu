@@ -84,6 +84,8 @@ struct SpParams {
     //   pass 2  blocks (chain, s): the walk of segment s with outputs from its true incoming state scan_start (composed
     //           from the A_s, B_s between the two passes); the last segment writes the final state
     int scan_pass, scan_k, scan_chunks;
+    int scan_open;      // pass 2: the last segment runs to the sequence's end (the call's last super-block), else to the
+                        // end of this launch's chunk range [state_chunk0, state_chunk0 + seg_chunks)
     float* scan_ab;     // [chain][K - 1][2][128 x 128]: B_s, A_s in the state's layout
     float* scan_start;  // [chain][K][128 x 128]: the state before each segment (segment 0: unused, the caller's state)
 };
@@ -915,7 +917,9 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
         ctl[0] = 0u;
         ctl[1] = 0u;
         mbar_init_fence();
-        if (blockIdx.x == 0) p.counters[p.ctr ^ 1] = 0u;  // the next launch's counter; nobody reads it during this launch
+        // the next intra launch's counter; nobody reads it during this launch.  (Only launches that hand items out touch
+        // the counters: a scan pass may run beside the next super-block's intra launch on another stream.)
+        if (blockIdx.x == 0 && p.has_intra) p.counters[p.ctr ^ 1] = 0u;
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
     tc::fence_before_sync();
@@ -926,7 +930,8 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
     if (p.scan_pass == 1) {  // (chain, segment s < K - 1, kind): the segment's offset and transition
         const int kind = blockIdx.x & 1, sg = (blockIdx.x >> 1) % (p.scan_k - 1), chain = (blockIdx.x >> 1) / (p.scan_k - 1);
         if (chain < chains) {
-            const Walk wk{sg * p.scan_chunks, (sg + 1) * p.scan_chunks, kind ? 2 : 1, nullptr, 1,
+            const int hi = p.state_chunk0 + p.seg_chunks;  // the launch's chunk range ends here
+            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), min(p.state_chunk0 + (sg + 1) * p.scan_chunks, hi), kind ? 2 : 1, nullptr, 1,
                           p.scan_ab + (((size_t)chain * (p.scan_k - 1) + sg) * 2 + kind) * DV * DK, kind == 0, false};
             state_role<DV>(p, smem, tm, chain, 0, wk);
         }
@@ -935,7 +940,9 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
         if (chain < chains) {
             // Only the last segment delivers the sequence's final state; the others end where the next one starts.
             const bool last = sg == p.scan_k - 1;
-            const Walk wk{sg * p.scan_chunks, last ? 0x7fffffff : (sg + 1) * p.scan_chunks, sg == 0 ? 0 : 3,
+            const int hi = p.state_chunk0 + p.seg_chunks;
+            const int end = last ? (p.scan_open ? 0x7fffffff : hi) : min(p.state_chunk0 + (sg + 1) * p.scan_chunks, hi);
+            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), end, sg == 0 ? 0 : 3,
                           p.scan_start + ((size_t)chain * p.scan_k + sg) * DV * DK, last ? 0 : 2, nullptr, true, true};
             state_role<DV>(p, smem, tm, chain, 0, wk);
         }
@@ -1023,6 +1030,37 @@ int64_t core_prefill_workspace_bytes(int32_t heads, int32_t batch, int32_t chunk
 // The launches over every segment of the longest sequence, in stream order.  A workspace of two or more chunks per
 // chain is split into halves so that the state role of one segment runs beside the intra role of the next; a
 // workspace of one chunk per chain alternates intra-only and state-only launches.
+// Two side streams and their events per device, made on the first head-sharded scan (host objects only; no device memory).
+constexpr int kMaxSuperBlocks = 16;
+struct SideStreams {
+    cudaStream_t a = nullptr, b = nullptr;
+    cudaEvent_t fork = nullptr, join_a = nullptr, join_b = nullptr, ready[kMaxSuperBlocks] = {};
+};
+static SideStreams* side_streams() {
+    constexpr int kMaxDevices = 64;
+    static SideStreams table[kMaxDevices];
+    static bool made[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    SideStreams& t = table[dev];
+    if (!made[dev]) {
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);  // hi is the numerically lowest = the most urgent
+        bool ok = cudaStreamCreateWithPriority(&t.a, cudaStreamNonBlocking, lo) == cudaSuccess &&
+                  cudaStreamCreateWithPriority(&t.b, cudaStreamNonBlocking, hi) == cudaSuccess;  // the stores go first
+        ok = ok && cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&t.join_a, cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&t.join_b, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < kMaxSuperBlocks; ++i) ok = cudaEventCreateWithFlags(&t.ready[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        made[dev] = true;
+    }
+    return &t;
+}
+
 int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len, const glm53f_bf16* q,
                            const glm53f_bf16* k, const glm53f_bf16* v, const float* g, const float* beta, const void* state_in,
                            void* state_out, const int64_t* state_off, bool bf16_state, const glm53f_bf16* gate,
@@ -1101,6 +1139,76 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             if (K > need / 32) K = need / 32;  // a segment of fewer than 32 chunks is not worth three walks
         }
         if (K > need) K = need;
+        // A head-sharded launch sends every output row to every rank, and the scan emits all outputs in its last pass: the
+        // NVLink time (15 GB per GPU at 8 ranks) would follow the compute instead of running beside it.  So there the
+        // sequence is cut into super-blocks, each scanned on its own: the intra role and pass 1 of super-block b + 1 run on
+        // one side stream while the composition and pass 2 of super-block b -- the stores -- run on another.  Pass 2 then
+        // holds SMs while it waits for the links, so it gets fewer, longer segments (K <= 48 / chains).
+        // GLM53F_KDA_PREFILL_SUPERBLOCKS overrides the count (1 = off).
+        long long SB = (scatter != nullptr && scatter->ranks > 1) ? 8 : 1;
+        long long min_seg = 32;  // a segment of fewer than 32 chunks is not worth three walks (an override may ask for any)
+        if (const char* env = getenv("GLM53F_KDA_PREFILL_SUPERBLOCKS")) {
+            SB = atoll(env);
+            min_seg = 1;
+        }
+        if (SB > kMaxSuperBlocks) SB = kMaxSuperBlocks;
+        if (SB > 1 && K >= 2 && !bf16_state) {
+            long long Ks = K;
+            if (getenv("GLM53F_KDA_PREFILL_SEGMENTS") == nullptr && Ks > 48 / chains) Ks = 48 / chains > 2 ? 48 / chains : 2;
+            while (SB > 1 && need / (SB * Ks) < min_seg) --SB;
+            const long long sb = (need + SB - 1) / SB;
+            const long long scratch_sb = chains * (3 * Ks - 2) * (long long)(DV * DK * sizeof(float));
+            SideStreams* side = SB > 1 && chains * SB * sb * kSlotBytes + SB * scratch_sb <= usable ? side_streams() : nullptr;
+            if (side != nullptr) {
+                if ((e = cudaEventRecord(side->fork, stream)) != cudaSuccess) return (int)e;
+                cudaStreamWaitEvent(side->a, side->fork, 0);
+                cudaStreamWaitEvent(side->b, side->fork, 0);
+                unsigned char* scratch0 = base + chains * SB * sb * kSlotBytes;
+                for (long long b = 0; b < SB; ++b) {
+                    const long long c0 = b * sb, cnt = (need - c0) < sb ? (need - c0) : sb;
+                    if (cnt <= 0) break;
+                    const long long Kb = cnt >= min_seg * Ks ? Ks : (cnt / min_seg > 1 ? cnt / min_seg : 1);
+                    p.parts = 1;
+                    p.seg_chunks = (int)cnt;
+                    p.intra_chunk0 = p.state_chunk0 = (int)c0;
+                    p.ws_intra = p.ws_state = base + b * chains * sb * kSlotBytes;
+                    p.ctr = (int)(b & 1);
+                    p.scan_k = (int)Kb;
+                    p.scan_chunks = (int)((cnt + Kb - 1) / Kb);
+                    p.scan_open = (c0 + cnt >= need) ? 1 : 0;
+                    p.scan_ab = reinterpret_cast<float*>(scratch0 + b * scratch_sb);
+                    p.scan_start = p.scan_ab + chains * (Kb - 1) * 2 * DV * DK;
+                    // one side: everything that does not need the state before this super-block
+                    p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
+                    const long long items = chains * cnt;
+                    prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, side->a>>>(p);
+                    if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    p.has_intra = 0; p.has_state = 1;
+                    if (Kb > 1) {
+                        p.scan_pass = 1;
+                        prefill_sp_kernel<<<(unsigned)(2 * (Kb - 1) * chains), kThreadsSp, kSmemSp, side->a>>>(p);
+                        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    }
+                    cudaEventRecord(side->ready[b], side->a);
+                    // the other: the states before its segments, then the walk with the outputs (and the stores to the peers)
+                    cudaStreamWaitEvent(side->b, side->ready[b], 0);
+                    SpParams q2 = p;
+                    if (b > 0) q2.state_in = q2.state_out;  // continue from the state the previous super-block left
+                    if (Kb > 1) {
+                        scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, side->b>>>(q2);
+                        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    }
+                    q2.scan_pass = 2;
+                    prefill_sp_kernel<<<(unsigned)(Kb * chains), kThreadsSp, kSmemSp, side->b>>>(q2);
+                    if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                }
+                cudaEventRecord(side->join_a, side->a);
+                cudaEventRecord(side->join_b, side->b);
+                cudaStreamWaitEvent(stream, side->join_a, 0);
+                if ((e = cudaStreamWaitEvent(stream, side->join_b, 0)) != cudaSuccess) return (int)e;
+                return 0;
+            }
+        }
         const long long scratch = chains * (3 * K - 2) * (long long)(DV * DK * sizeof(float));
         if (K >= 2 && !bf16_state && chains * need * kSlotBytes + scratch <= usable) {
             p.seg_chunks = (int)need;
@@ -1112,6 +1220,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             p.scan_chunks = (int)((need + K - 1) / K);
             p.scan_ab = reinterpret_cast<float*>(base + chains * need * kSlotBytes);
             p.scan_start = p.scan_ab + chains * (K - 1) * 2 * DV * DK;
+            p.scan_open = 1;
             p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
             const long long items = chains * need;
             prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, stream>>>(p);

@@ -418,6 +418,14 @@ def test_prefill_scan_over_segments(G, core, oracle, pkg, segments, monkeypatch)
     out, st = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=need + 12)   # against the oracle, inside
     assert G.max_abs(out, base_out) / G.max_abs(base_out) <= 1.0 / 128.0
     assert G.rel_l2(st, base_st) <= 3e-4
+    # the same scan in super-blocks of the sequence on two streams (what a head-sharded launch does so that its stores to
+    # the peers run beside the next super-block's passes): other segment boundaries, the same tolerances
+    for blocks in (2, 3):
+        monkeypatch.setenv("GLM53F_KDA_PREFILL_SUPERBLOCKS", str(blocks))
+        out_sb, st_sb = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=need + 40)   # against the oracle, inside
+        assert G.max_abs(out_sb, base_out) / G.max_abs(base_out) <= 1.0 / 128.0
+        assert G.rel_l2(st_sb, base_st) <= 3e-4
+    monkeypatch.delenv("GLM53F_KDA_PREFILL_SUPERBLOCKS")
     # a workspace that cannot hold every chunk: no scan, the unsegmented run's bits
     out2, st2 = prefill_case(G, core, oracle, pkg.synth, 2, heads, lens, carried, ws_chunks=8)
     small_out, small_st = out2, st2

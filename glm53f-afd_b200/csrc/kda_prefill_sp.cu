@@ -84,8 +84,11 @@ struct SpParams {
     //   pass 2  blocks (chain, s): the walk of segment s with outputs from its true incoming state scan_start (composed
     //           from the A_s, B_s between the two passes); the last segment writes the final state
     int scan_pass, scan_k, scan_chunks;
-    int scan_open;      // pass 2: the last segment runs to the sequence's end (the call's last super-block), else to the
-                        // end of this launch's chunk range [state_chunk0, state_chunk0 + seg_chunks)
+    int scan_open;      // the last segment runs to the sequence's end (the call's last super-block), else to the end of
+                        // this launch's chunk range [state_chunk0, state_chunk0 + seg_chunks)
+    int scan_p1;        // segments pass 1 walks: K - 1, or K when the state after the range is wanted before pass 2 runs
+    const float* scan_carry_in;  // super-blocks: the FP32 state before this launch's range, [chain][128 x 128] (NULL: state_in)
+    float* scan_carry_out;       // super-blocks: the FP32 state after this launch's range (scan_p1 == K)
     float* scan_ab;     // [chain][K - 1][2][128 x 128]: B_s, A_s in the state's layout
     float* scan_start;  // [chain][K][128 x 128]: the state before each segment (segment 0: unused, the caller's state)
 };
@@ -917,9 +920,9 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
         ctl[0] = 0u;
         ctl[1] = 0u;
         mbar_init_fence();
-        // the next intra launch's counter; nobody reads it during this launch.  (Only launches that hand items out touch
-        // the counters: a scan pass may run beside the next super-block's intra launch on another stream.)
-        if (blockIdx.x == 0 && p.has_intra) p.counters[p.ctr ^ 1] = 0u;
+        // the next launch's counter; nobody reads it during this launch.  (A scan pass leaves the counters alone: it may run
+        // beside the next super-block's intra launch on another stream.)
+        if (blockIdx.x == 0 && p.scan_pass == 0) p.counters[p.ctr ^ 1] = 0u;
     }
     if (warp == 0) tc::tmem_alloc(tmem_slot, kTmemCols);
     tc::fence_before_sync();
@@ -927,12 +930,14 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
     tc::fence_after_sync();
     const uint32_t tm = *tmem_slot;
     const int chains = p.batch * p.H;
-    if (p.scan_pass == 1) {  // (chain, segment s < K - 1, kind): the segment's offset and transition
-        const int kind = blockIdx.x & 1, sg = (blockIdx.x >> 1) % (p.scan_k - 1), chain = (blockIdx.x >> 1) / (p.scan_k - 1);
+    if (p.scan_pass == 1) {  // (chain, segment s < scan_p1, kind): the segment's offset and transition
+        const int kind = blockIdx.x & 1, sg = (blockIdx.x >> 1) % p.scan_p1, chain = (blockIdx.x >> 1) / p.scan_p1;
         if (chain < chains) {
             const int hi = p.state_chunk0 + p.seg_chunks;  // the launch's chunk range ends here
-            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), min(p.state_chunk0 + (sg + 1) * p.scan_chunks, hi), kind ? 2 : 1, nullptr, 1,
-                          p.scan_ab + (((size_t)chain * (p.scan_k - 1) + sg) * 2 + kind) * DV * DK, kind == 0, false};
+            const bool last = sg == p.scan_k - 1;
+            const int end = last ? (p.scan_open ? 0x7fffffff : hi) : min(p.state_chunk0 + (sg + 1) * p.scan_chunks, hi);
+            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), end, kind ? 2 : 1, nullptr, 1,
+                          p.scan_ab + (((size_t)chain * p.scan_p1 + sg) * 2 + kind) * DV * DK, kind == 0, false};
             state_role<DV>(p, smem, tm, chain, 0, wk);
         }
     } else if (p.scan_pass == 2) {  // (chain, segment): the walk with outputs from the segment's true incoming state
@@ -942,8 +947,10 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
             const bool last = sg == p.scan_k - 1;
             const int hi = p.state_chunk0 + p.seg_chunks;
             const int end = last ? (p.scan_open ? 0x7fffffff : hi) : min(p.state_chunk0 + (sg + 1) * p.scan_chunks, hi);
-            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), end, sg == 0 ? 0 : 3,
-                          p.scan_start + ((size_t)chain * p.scan_k + sg) * DV * DK, last ? 0 : 2, nullptr, true, true};
+            const bool carried = sg == 0 && p.scan_carry_in != nullptr;  // a later super-block: its incoming state is a composed one
+            const Walk wk{min(p.state_chunk0 + sg * p.scan_chunks, hi), end, sg == 0 && !carried ? 0 : 3,
+                          carried ? p.scan_carry_in + (size_t)chain * DV * DK : p.scan_start + ((size_t)chain * p.scan_k + sg) * DV * DK,
+                          last ? 0 : 2, nullptr, true, true};
             state_role<DV>(p, smem, tm, chain, 0, wk);
         }
     } else if (p.has_state && blockIdx.x < (unsigned)(chains * p.parts)) {
@@ -966,12 +973,13 @@ __global__ void __launch_bounds__(128) scan_compose_kernel(const __grid_constant
     __shared__ float S[8][DK];
     const int chain = blockIdx.x >> 4, v0 = (blockIdx.x & 15) * 8, k = threadIdx.x;
     const int b = chain / p.H, h = chain % p.H;
-    const float* s0 = reinterpret_cast<const float*>(p.state_in) + p.state_off[b] + (long long)h * DV * DK;
+    const float* s0 = p.scan_carry_in != nullptr ? p.scan_carry_in + (size_t)chain * DV * DK
+                                                 : reinterpret_cast<const float*>(p.state_in) + p.state_off[b] + (long long)h * DV * DK;
 #pragma unroll
     for (int vi = 0; vi < 8; ++vi) S[vi][k] = s0[(v0 + vi) * DK + k];
     __syncthreads();
-    for (int sg = 0; sg + 1 < p.scan_k; ++sg) {
-        const float* B = p.scan_ab + ((size_t)chain * (p.scan_k - 1) + sg) * 2 * DV * DK;
+    for (int sg = 0; sg < p.scan_p1; ++sg) {
+        const float* B = p.scan_ab + ((size_t)chain * p.scan_p1 + sg) * 2 * DV * DK;
         const float* A = B + DV * DK;
         float acc[8];
 #pragma unroll
@@ -982,7 +990,8 @@ __global__ void __launch_bounds__(128) scan_compose_kernel(const __grid_constant
             for (int vi = 0; vi < 8; ++vi) acc[vi] = fmaf(a, S[vi][kp], acc[vi]);
         }
         __syncthreads();
-        float* out = p.scan_start + ((size_t)chain * p.scan_k + sg + 1) * DV * DK;
+        // the state before segment sg + 1, or, after the last segment (scan_p1 == K), the state after the launch's range
+        float* out = sg + 1 < p.scan_k ? p.scan_start + ((size_t)chain * p.scan_k + sg + 1) * DV * DK : p.scan_carry_out + (size_t)chain * DV * DK;
 #pragma unroll
         for (int vi = 0; vi < 8; ++vi) {
             S[vi][k] = acc[vi];
@@ -1157,13 +1166,15 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             if (getenv("GLM53F_KDA_PREFILL_SEGMENTS") == nullptr && Ks > 48 / chains) Ks = 48 / chains > 2 ? 48 / chains : 2;
             while (SB > 1 && need / (SB * Ks) < min_seg) --SB;
             const long long sb = (need + SB - 1) / SB;
-            const long long scratch_sb = chains * (3 * Ks - 2) * (long long)(DV * DK * sizeof(float));
+            // per super-block: K transitions and offsets, K incoming states, and the state after the super-block
+            const long long scratch_sb = chains * (3 * Ks + 1) * (long long)(DV * DK * sizeof(float));
             SideStreams* side = SB > 1 && chains * SB * sb * kSlotBytes + SB * scratch_sb <= usable ? side_streams() : nullptr;
             if (side != nullptr) {
                 if ((e = cudaEventRecord(side->fork, stream)) != cudaSuccess) return (int)e;
                 cudaStreamWaitEvent(side->a, side->fork, 0);
                 cudaStreamWaitEvent(side->b, side->fork, 0);
                 unsigned char* scratch0 = base + chains * SB * sb * kSlotBytes;
+                const float* carry = nullptr;
                 for (long long b = 0; b < SB; ++b) {
                     const long long c0 = b * sb, cnt = (need - c0) < sb ? (need - c0) : sb;
                     if (cnt <= 0) break;
@@ -1174,33 +1185,32 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
                     p.ws_intra = p.ws_state = base + b * chains * sb * kSlotBytes;
                     p.ctr = (int)(b & 1);
                     p.scan_k = (int)Kb;
+                    p.scan_p1 = (int)Kb;  // every segment: the state after the super-block is composed, not walked for
                     p.scan_chunks = (int)((cnt + Kb - 1) / Kb);
                     p.scan_open = (c0 + cnt >= need) ? 1 : 0;
                     p.scan_ab = reinterpret_cast<float*>(scratch0 + b * scratch_sb);
-                    p.scan_start = p.scan_ab + chains * (Kb - 1) * 2 * DV * DK;
-                    // one side: everything that does not need the state before this super-block
+                    p.scan_start = p.scan_ab + chains * Kb * 2 * DV * DK;
+                    p.scan_carry_in = carry;
+                    p.scan_carry_out = p.scan_start + chains * Kb * DV * DK;
+                    // one stream: everything up to the states before this super-block's segments and after it -- the intra
+                    // role, both walks of every segment, the composition (which needs the previous super-block's, not its
+                    // pass 2)
                     p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
                     const long long items = chains * cnt;
                     prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, side->a>>>(p);
                     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-                    p.has_intra = 0; p.has_state = 1;
-                    if (Kb > 1) {
-                        p.scan_pass = 1;
-                        prefill_sp_kernel<<<(unsigned)(2 * (Kb - 1) * chains), kThreadsSp, kSmemSp, side->a>>>(p);
-                        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-                    }
-                    cudaEventRecord(side->ready[b], side->a);
-                    // the other: the states before its segments, then the walk with the outputs (and the stores to the peers)
-                    cudaStreamWaitEvent(side->b, side->ready[b], 0);
-                    SpParams q2 = p;
-                    if (b > 0) q2.state_in = q2.state_out;  // continue from the state the previous super-block left
-                    if (Kb > 1) {
-                        scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, side->b>>>(q2);
-                        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-                    }
-                    q2.scan_pass = 2;
-                    prefill_sp_kernel<<<(unsigned)(Kb * chains), kThreadsSp, kSmemSp, side->b>>>(q2);
+                    p.has_intra = 0; p.has_state = 1; p.scan_pass = 1;
+                    prefill_sp_kernel<<<(unsigned)(2 * Kb * chains), kThreadsSp, kSmemSp, side->a>>>(p);
                     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, side->a>>>(p);
+                    if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    cudaEventRecord(side->ready[b], side->a);
+                    // the other: the walks with the outputs (and the stores to the peers), super-block after super-block
+                    cudaStreamWaitEvent(side->b, side->ready[b], 0);
+                    p.scan_pass = 2;
+                    prefill_sp_kernel<<<(unsigned)(Kb * chains), kThreadsSp, kSmemSp, side->b>>>(p);
+                    if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+                    carry = p.scan_carry_out;
                 }
                 cudaEventRecord(side->join_a, side->a);
                 cudaEventRecord(side->join_b, side->b);
@@ -1221,6 +1231,8 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             p.scan_ab = reinterpret_cast<float*>(base + chains * need * kSlotBytes);
             p.scan_start = p.scan_ab + chains * (K - 1) * 2 * DV * DK;
             p.scan_open = 1;
+            p.scan_p1 = (int)K - 1;
+            p.scan_carry_in = nullptr; p.scan_carry_out = nullptr;
             p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
             const long long items = chains * need;
             prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, stream>>>(p);

@@ -758,7 +758,7 @@ def run_prefill(torch, dist, pkg, core, rank, world, tokens, passes, ws_chunks, 
     # fewer chains a workspace that holds every chunk of the sequence lets the kernel cut each chain into segments that
     # are walked at the same time (the scan over segments), which is what shortens the serial walk when heads are sharded.
     if ws_chunks > 0 and world > 1:
-        ws_chunks = (tokens + 63) // 64 + 128   # every chunk of the sequence, and the scan's states per super-block
+        ws_chunks = (tokens + 63) // 64 + 256   # every chunk of the sequence, and the scan's states per super-block
     ws = torch.empty(core.prefill_workspace_bytes(hl, 1, ws_chunks), dtype=torch.uint8, device="cuda") if ws_chunks > 0 else None
 
     def one_pass(gather):

@@ -966,34 +966,37 @@ __global__ void __launch_bounds__(kThreadsSp, 1) prefill_sp_kernel(const __grid_
 }
 
 // Between the two scan passes: the state before every segment, S_start[s + 1] = A_s S_start[s] + B_s in FP32, from the
-// caller's state.  A state's value columns never mix, so a block owns eight of them (held in shared memory across the
+// caller's state.  A state's value columns never mix, so a block owns two of them (held in shared memory across the
 // segments) and a thread one key channel: acc[v] += A_s[k][k'] S[k'][v] with A_s read along k (coalesced; A_s lies in
 // the state's layout, entry [k'][k]).
+constexpr int kComposeCols = 2;  // value columns per block: 64 blocks a chain (with eight columns, 16 blocks, a launch took 0.3 ms)
 __global__ void __launch_bounds__(128) scan_compose_kernel(const __grid_constant__ SpParams p) {
-    __shared__ float S[8][DK];
-    const int chain = blockIdx.x >> 4, v0 = (blockIdx.x & 15) * 8, k = threadIdx.x;
+    constexpr int kCols = kComposeCols;
+    __shared__ float S[kCols][DK];
+    const int chain = blockIdx.x / (DV / kCols), v0 = (blockIdx.x % (DV / kCols)) * kCols, k = threadIdx.x;
     const int b = chain / p.H, h = chain % p.H;
     const float* s0 = p.scan_carry_in != nullptr ? p.scan_carry_in + (size_t)chain * DV * DK
                                                  : reinterpret_cast<const float*>(p.state_in) + p.state_off[b] + (long long)h * DV * DK;
 #pragma unroll
-    for (int vi = 0; vi < 8; ++vi) S[vi][k] = s0[(v0 + vi) * DK + k];
+    for (int vi = 0; vi < kCols; ++vi) S[vi][k] = s0[(v0 + vi) * DK + k];
     __syncthreads();
     for (int sg = 0; sg < p.scan_p1; ++sg) {
         const float* B = p.scan_ab + ((size_t)chain * p.scan_p1 + sg) * 2 * DV * DK;
         const float* A = B + DV * DK;
-        float acc[8];
+        float acc[kCols];
 #pragma unroll
-        for (int vi = 0; vi < 8; ++vi) acc[vi] = B[(v0 + vi) * DK + k];
+        for (int vi = 0; vi < kCols; ++vi) acc[vi] = B[(v0 + vi) * DK + k];
+#pragma unroll 8
         for (int kp = 0; kp < DK; ++kp) {
             const float a = A[kp * DK + k];
 #pragma unroll
-            for (int vi = 0; vi < 8; ++vi) acc[vi] = fmaf(a, S[vi][kp], acc[vi]);
+            for (int vi = 0; vi < kCols; ++vi) acc[vi] = fmaf(a, S[vi][kp], acc[vi]);
         }
         __syncthreads();
         // the state before segment sg + 1, or, after the last segment (scan_p1 == K), the state after the launch's range
         float* out = sg + 1 < p.scan_k ? p.scan_start + ((size_t)chain * p.scan_k + sg + 1) * DV * DK : p.scan_carry_out + (size_t)chain * DV * DK;
 #pragma unroll
-        for (int vi = 0; vi < 8; ++vi) {
+        for (int vi = 0; vi < kCols; ++vi) {
             S[vi][k] = acc[vi];
             out[(v0 + vi) * DK + k] = acc[vi];
         }
@@ -1196,13 +1199,16 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
                     // role, both walks of every segment, the composition (which needs the previous super-block's, not its
                     // pass 2)
                     p.has_intra = 1; p.has_state = 0; p.scan_pass = 0;
-                    const long long items = chains * cnt;
-                    prefill_sp_kernel<<<(unsigned)(items < sms ? items : sms), kThreadsSp, kSmemSp, side->a>>>(p);
+                    // The intra blocks are persistent: on every SM they would keep the previous super-block's output pass,
+                    // which is ready about now, off the machine until they are done, and the links idle.  From the second
+                    // super-block on they leave that pass its SMs (measured on 8 GPUs: 28.6 -> see the bench's prefill leg).
+                    const long long items = chains * cnt, room = b == 0 ? sms : (sms - Kb * chains > sms / 2 ? sms - Kb * chains : sms / 2);
+                    prefill_sp_kernel<<<(unsigned)(items < room ? items : room), kThreadsSp, kSmemSp, side->a>>>(p);
                     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
                     p.has_intra = 0; p.has_state = 1; p.scan_pass = 1;
                     prefill_sp_kernel<<<(unsigned)(2 * Kb * chains), kThreadsSp, kSmemSp, side->a>>>(p);
                     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-                    scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, side->a>>>(p);
+                    scan_compose_kernel<<<(unsigned)(chains * (DV / kComposeCols)), 128, 0, side->a>>>(p);
                     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
                     cudaEventRecord(side->ready[b], side->a);
                     // the other: the walks with the outputs (and the stores to the peers), super-block after super-block
@@ -1240,7 +1246,7 @@ int core_prefill_sp_launch(int32_t heads, int32_t batch, const int32_t* cu_seqle
             p.has_intra = 0; p.has_state = 1; p.scan_pass = 1;
             prefill_sp_kernel<<<(unsigned)(2 * (K - 1) * chains), kThreadsSp, kSmemSp, stream>>>(p);
             if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-            scan_compose_kernel<<<(unsigned)(chains * 16), 128, 0, stream>>>(p);
+            scan_compose_kernel<<<(unsigned)(chains * (DV / kComposeCols)), 128, 0, stream>>>(p);
             if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
             p.scan_pass = 2;
             prefill_sp_kernel<<<(unsigned)(K * chains), kThreadsSp, kSmemSp, stream>>>(p);

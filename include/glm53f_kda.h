@@ -318,7 +318,13 @@ int glm53f_kda_core_prefill_varlen_ws(int32_t heads, int32_t batch, const int32_
  * over NVLink for a peer's buffer; no collective follows the launch).  `full` is a host array, read during the call.
  * `out` (the shard-local [rows][heads][128]) may be NULL.  The caller orders the ranks around the launch: no rank may
  * still read a full buffer when another rank's launch starts writing it, and a rank may read its buffer only after
- * every rank's launch has completed (a barrier on each side).  Not in the reference, which runs on one GPU. */
+ * every rank's launch has completed (a barrier on each side).  With more than one rank, 16 or fewer chains, FP32 states
+ * and a workspace for every chunk of the call (glm53f_kda_core_prefill_workspace_bytes(heads, batch, chunks + 256) is
+ * enough) the call scans the sequence in super-blocks on two streams of its own (made once per device on the first such
+ * call: host objects, no device memory), so that one super-block's stores run beside the next one's passes; `stream`
+ * waits for both before anything later on it runs, also under stream capture.  Calls of this kind on one device share
+ * those two streams and their events: issue them from one host thread at a time.  GLM53F_KDA_PREFILL_SUPERBLOCKS=1
+ * keeps everything on `stream`.  Not in the reference, which runs on one GPU. */
 int glm53f_kda_core_prefill_varlen_ws_gather(int32_t heads, int32_t batch, const int32_t* cu_seqlens, int32_t max_len,
                                              const glm53f_bf16* q, const glm53f_bf16* k, const glm53f_bf16* v,
                                              const float* g, const float* beta,

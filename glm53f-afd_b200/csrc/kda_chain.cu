@@ -1041,7 +1041,7 @@ int launch_small(const Params& p, cudaStream_t stream) {
 // here -- no shared memory, no barrier, the next row's inputs loaded into registers while the current row's delta rule
 // runs -- and 32 such warps are resident on an SM where the persistent kernel has one unit's 16.  Same delta_rule, same
 // rounding points (a bf16 state is rounded after every row), so the bits are the persistent kernel's and the
-// reference's.  Measured at 48 slots x 34 layers, accepted prefixes drawn from 0..16: see the bench's verify.commit.
+// reference's.  Measured at 48 slots x 34 layers, accepted prefixes drawn from 0..16: 3.63 ms a commit against 4.71 ms.
 struct ReplayRow {
     float4 k, g;
     float v, beta;

@@ -288,6 +288,30 @@ class StateType(enum.Enum):
         return self.value
 
 
+class Form(enum.IntEnum):
+    """Which form a layer entry point runs (additions of this library; process-wide switches of the C library):
+    EXACT leaves the reference kernels' bits and is the default, CHUNKED runs on the tensor cores and agrees to the
+    rounding of bf16 operands."""
+
+    EXACT = 0
+    CHUNKED = 1
+
+
+def set_prefill_form(form: Form) -> Form:
+    """glm53f_kda_prefill_mode: the form of glm53f_kda_prefill*; returns the form that was in force."""
+    return Form(ffi.load().glm53f_kda_prefill_mode(int(form)))
+
+
+def set_verify_form(form: Form) -> Form:
+    """glm53f_kda_verify_mode: the form of a verify call of glm53f_kda_chain_batch_bf16state (state not written, saves on)."""
+    return Form(ffi.load().glm53f_kda_verify_mode(int(form)))
+
+
+def set_commit_form(form: Form) -> Form:
+    """glm53f_kda_commit_mode: the form of the bf16-state replays."""
+    return Form(ffi.load().glm53f_kda_commit_mode(int(form)))
+
+
 def _check_saves(saves: Optional[Saves], heads: int, rows: int):
     if saves is None:
         return _NO_SAVES

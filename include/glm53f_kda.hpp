@@ -699,5 +699,17 @@ struct PrefillBatch {
     }
 };
 
+// ---- forms of the layer entry points (additions of this library; process-wide switches) -------------------------------
+// The exact forms are the defaults and leave the reference kernels' bits; the chunked forms run on the tensor cores and
+// agree to the rounding of bf16 operands (glm53f_kda_prefill_mode, glm53f_kda_verify_mode, glm53f_kda_commit_mode in
+// glm53f_kda.h say what each changes).  Each setter returns the form that was in force.
+enum class Form : int32_t { Exact = 0, Chunked = 1 };
+inline Form set_prefill_form(Form f) { return static_cast<Form>(glm53f_kda_prefill_mode(static_cast<int32_t>(f))); }
+inline Form set_verify_form(Form f) { return static_cast<Form>(glm53f_kda_verify_mode(static_cast<int32_t>(f))); }
+inline Form set_commit_form(Form f) { return static_cast<Form>(glm53f_kda_commit_mode(static_cast<int32_t>(f))); }
+inline Form prefill_form() { return static_cast<Form>(glm53f_kda_prefill_mode(-1)); }
+inline Form verify_form() { return static_cast<Form>(glm53f_kda_verify_mode(-1)); }
+inline Form commit_form() { return static_cast<Form>(glm53f_kda_commit_mode(-1)); }
+
 }  // namespace kda
 }  // namespace glm53f

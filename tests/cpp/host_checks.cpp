@@ -111,6 +111,11 @@ int main() {
         pbh.conv = &conv, pbh.state = &state, pbh.state_out = StateOut::skip(), pbh.out = RowView::dense(ob, h * DV), pbh.workspace = &ws;
         pbh.launch(meta, s);
     });
+    // the form switches: exact by default; each setter returns the form that was in force
+    CHECK(prefill_form() == Form::Exact && verify_form() == Form::Exact && commit_form() == Form::Exact);
+    CHECK(set_verify_form(Form::Chunked) == Form::Exact && verify_form() == Form::Chunked && set_verify_form(Form::Exact) == Form::Chunked);
+    CHECK(set_commit_form(Form::Chunked) == Form::Exact && commit_form() == Form::Chunked && set_commit_form(Form::Exact) == Form::Chunked);
+    CHECK(set_prefill_form(Form::Chunked) == Form::Exact && prefill_form() == Form::Chunked && set_prefill_form(Form::Exact) == Form::Chunked);
     std::printf(failures ? "%d FAILED\n" : "all host checks passed\n", failures);
     return failures ? 1 : 0;
 }

@@ -160,3 +160,13 @@ def test_prefill_rejections(K):
         K.Prefill(**dict(base, state_out=K.StateOut.Skip), value_blocks=0, workspace=ws).launch(s)
     with pytest.raises(K.Invalid, match="workspace for"):
         K.Prefill(**base, value_blocks=0, workspace=K.PrefillWorkspace.new(h + 1, 1, 16)).launch(s)
+
+
+def test_form_switches(K):
+    """The process-wide switches between the exact and the chunked forms: exact by default, each setter returns the
+    form that was in force (host-side state of the library: no GPU involved)."""
+    F = K.Form
+    for setter in (K.set_prefill_form, K.set_verify_form, K.set_commit_form):
+        assert setter(F.CHUNKED) is F.EXACT
+        assert setter(F.EXACT) is F.CHUNKED
+        assert setter(F.EXACT) is F.EXACT

@@ -105,10 +105,13 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
     // a block = four consecutive rows of one (request, head): neighbours share their predecessors in L1
     const int quads = p.pass_rows / 4;
     const long long unit = blockIdx.x / quads;
-    const int j = (int)(blockIdx.x % quads) * 4 + (threadIdx.x >> 5);  // row of the pass
+    const int j_first = (int)(blockIdx.x % quads) * 4 + (threadIdx.x >> 5);  // row of the pass
     const int h = (int)(unit % H), b = (int)(unit / H);
-    const int r0 = p.cu[b], n = min(max(p.cu[b + 1] - r0 - p.row_shift, 0), p.pass_rows);
-    if (j >= n) return;
+    // A prefill pass covers pass_rows rows of every request.  A verify window is meant to have at most 16 rows; should one be
+    // longer (the chunk kernel then reports status 122 and leaves the rows past 16 without outputs), its replay saves are
+    // still written for EVERY row, so that a commit of any prefix replays real values: the warp goes on in steps of 16.
+    const int r0 = p.cu[b], n_all = max(p.cu[b + 1] - r0 - p.row_shift, 0), n = VERIFY ? n_all : min(n_all, p.pass_rows);
+    for (int j = j_first; j < n; j += p.pass_rows) {
     const int c0 = lane * 4, jj = p.row_shift + j;  // row of the request
     const long long C = 3LL * H * DK, gr = (long long)r0 + jj;
     const uint16_t* window = p.conv + p.conv_off[b];
@@ -176,7 +179,7 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
     const float bt = bf16_round(sigmoid_<!VERIFY>(blogit));
     if constexpr (VERIFY) {
         const long long sv = (gr * H + h) * DK + c0;
-        *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);
+        if (j < p.pass_rows) *reinterpret_cast<uint2*>(p.q + gr * p.out_stride + (long long)h * DK + c0) = pack4_fp16(qn);  // rows past 16 get no output: leave theirs alone
         *reinterpret_cast<float4*>(p.k_save + sv) = make_float4(kn[0], kn[1], kn[2], kn[3]);
         *reinterpret_cast<uint2*>(p.v_save + sv) = pack4(act[2]);
         *reinterpret_cast<float4*>(p.g_save + sv) = make_float4(expf(lg[0]), expf(lg[1]), expf(lg[2]), expf(lg[3]));
@@ -188,6 +191,7 @@ __global__ void __launch_bounds__(128, 6) layer_prologue_kernel(const ProParams 
         *reinterpret_cast<uint2*>(p.v + at) = pack4(act[2]);
         *reinterpret_cast<float4*>(p.g + at) = make_float4(lg[0], lg[1], lg[2], lg[3]);
         if (lane == 0) p.beta[orow * H + h] = bt;
+    }
     }
 }
 

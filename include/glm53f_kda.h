@@ -412,8 +412,8 @@ int32_t glm53f_kda_prefill_mode(int32_t mode);
  *      still leaves the states of serial decode steps) and parks q, as fp16, in the output rows; the second reads the
  *      bf16 state once per (request, head) and overwrites the output rows with the gated, normalised outputs, which
  *      agree with the exact form's to the rounding of bf16 operands (the task's tolerances: 2e-2 max-abs, 5e-3 rel-L2
- *      before the norm).  A window longer than 16 rows records status 122 (glm53f_kda_device_status) and only its
- *      first 16 rows are computed.  Calls whose rows are not aligned for vector access (p, a, g, conv 8 bytes; out,
+ *      before the norm).  A window longer than 16 rows records status 122 (glm53f_kda_device_status): only its first
+ *      16 rows get outputs, while the replay saves are still written for every row.  Calls whose rows are not aligned for vector access (p, a, g, conv 8 bytes; out,
  *      the saves, the state base 16 bytes; strides multiples of 4, out_stride of 8 elements) run the exact form.
  * Any other value only queries.  Returns the mode that was in force.  The environment variable GLM53F_KDA_VERIFY=chunked
  * makes 1 the initial mode.  Process-wide; set it before the launches it should affect. */

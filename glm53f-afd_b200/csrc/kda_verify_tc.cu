@@ -433,11 +433,16 @@ __global__ void __launch_bounds__(kVThreads, 3) verify_tc_kernel(const __grid_co
 // chunk's state or is copied out.  Unlike the exact replay this rounds the state to bf16 once per chunk instead of
 // after every row, and its sums run in another order: the committed state agrees with serial decode steps to the last
 // bits of bf16, not bit for bit (glm53f_kda_commit_mode).
-constexpr int cS = 0, cKc = 32768, cKgb = cKc + 4096, cDT = cKgb + 4096, cKdT = cDT + 8192, cE = cKdT + 8192, cBeta = cE + 512;
+// Four blocks per SM (128 registers a thread, all 512 columns of tensor memory, 52.6 KB of shared memory each): the stages
+// of a unit are serial, so what overlaps one unit's waits is the other resident blocks' work.  To fit, the hi half of D^T
+// shares its 4 KB with Kc and L: Kc is read by the L^T product only, L by the forward substitution only, and D^T is written
+// after the (W S)^T product, which comes after both.
+constexpr int cS = 0, cDT = 32768, cKc = cDT, cKgb = cDT + 8192, cKdT = cKgb + 4096, cE = cKdT + 8192, cBeta = cE + 512;
 constexpr int cBar = cBeta + 64, cCtl = cBar + 16, kCSmem = cCtl + 16;
 constexpr int cW = cKgb, cL = cKc;                    // W replaces Kgb, L replaces Kc once L^T is done
 constexpr uint32_t kCCols = 128;                      // tensor memory: L^T, then (W S)^T, then the 128 x 128 update
-static_assert(kCSmem <= 75 * 1024, "three blocks per SM");
+constexpr int kCBlocks = 4;
+static_assert(kCBlocks * (kCSmem + 1024) <= 228 * 1024 && kCBlocks * kCCols <= 512, "four blocks per SM");
 
 struct CParams {
     int H, layers, rows1;
@@ -458,7 +463,7 @@ struct CParams {
 
 __device__ __forceinline__ int state_piece(int v, int pk) { return cS + (pk >> 3) * 16384 + v * 128 + (((pk & 7) ^ (v & 7)) << 4); }
 
-__global__ void __launch_bounds__(kVThreads, 3) commit_tc_kernel(const __grid_constant__ CParams p) {
+__global__ void __launch_bounds__(kVThreads, kCBlocks) commit_tc_kernel(const __grid_constant__ CParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + cBar);
     volatile uint32_t* ctl = reinterpret_cast<volatile uint32_t*>(smem + cCtl);
@@ -790,7 +795,7 @@ int commit_tc_launch(int32_t heads, int32_t layers, int32_t batch, const int32_t
     p.kv_stride = kv_stride; p.b_stride = b_stride;
     p.status = status_word();
     if (p.status == nullptr) return (int)cudaErrorUnknown;
-    const long long cap = 3LL * sm_count();
+    const long long cap = (long long)kCBlocks * sm_count();
     commit_tc_kernel<<<(unsigned)(p.units < cap ? p.units : cap), kVThreads, kCSmem, stream>>>(p);
     return (int)cudaGetLastError();
 }

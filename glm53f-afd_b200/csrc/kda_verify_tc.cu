@@ -669,19 +669,19 @@ __global__ void __launch_bounds__(kVThreads, kCBlocks) commit_tc_kernel(const __
 
             // ---- G. S <- E S + update, rounded to bf16, back into the tile (thread = value row) ------------------------------
 #pragma unroll 1
-            for (int cg = 0; cg < DK / 16; ++cg) {
-                uint32_t a16[16];
-                tc::tmem_ld16(tc::tmem_addr(tm, warp, cg * 16), a16);
+            for (int cg = 0; cg < DK / 32; ++cg) {
+                uint32_t a16[32];
+                tc::tmem_ld32(tc::tmem_addr(tm, warp, cg * 32), a16);
                 tc::tmem_ld_wait();
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    unsigned char* at = smem + state_piece(t, cg * 2 + half);
+                for (int half = 0; half < 4; ++half) {
+                    unsigned char* at = smem + state_piece(t, cg * 4 + half);
                     const uint4 sv = *reinterpret_cast<const uint4*>(at);
                     const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
                     uint32_t out[4];
 #pragma unroll
                     for (int x = 0; x < 4; ++x) {
-                        const int k = cg * 16 + half * 8 + 2 * x;
+                        const int k = cg * 32 + half * 8 + 2 * x;
                         const float2 e2 = *reinterpret_cast<const float2*>(&En[k]);
                         const float lo = fmaf(e2.x, __uint_as_float(sw[x] << 16), __uint_as_float(a16[half * 8 + 2 * x]));
                         const float hi = fmaf(e2.y, __uint_as_float(sw[x] & 0xffff0000u), __uint_as_float(a16[half * 8 + 2 * x + 1]));
